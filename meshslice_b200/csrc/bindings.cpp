@@ -1,0 +1,317 @@
+// Python bindings (pybind11, no torch headers): every function takes raw device pointers
+// (tensor.data_ptr()) and a stream handle (torch.cuda.current_stream().cuda_stream), so the
+// extension has no ABI coupling with the PyTorch build it is used with.
+#include <pybind11/pybind11.h>
+#include <pybind11/stl.h>
+
+#include <cstring>
+#include <stdexcept>
+#include <string>
+#include <vector>
+
+#include "comm/p2p.h"
+#include "gemm/sm100_gemm.h"
+#include "ops/ops.h"
+
+namespace py = pybind11;
+using namespace msb;
+
+namespace {
+
+void check(cudaError_t e, const char* what) {
+  if (e != cudaSuccess)
+    throw std::runtime_error(std::string(what) + ": " + cudaGetErrorString(e));
+}
+template <class T>
+T* P(uint64_t p) { return reinterpret_cast<T*>(static_cast<uintptr_t>(p)); }
+cudaStream_t S(uint64_t s) { return reinterpret_cast<cudaStream_t>(static_cast<uintptr_t>(s)); }
+
+int64_t geti(const py::dict& d, const char* k, int64_t def = 0) {
+  return d.contains(k) ? d[k].cast<int64_t>() : def;
+}
+uint64_t getp(const py::dict& d, const char* k) {
+  return d.contains(k) ? d[k].cast<uint64_t>() : 0;
+}
+
+BarrierArgs parse_barrier(const py::dict& d) {
+  BarrierArgs b;
+  std::memset(&b, 0, sizeof(b));
+  b.n_ranks = (int)geti(d, "n_ranks");
+  b.my_rank = (int)geti(d, "my_rank");
+  if (b.n_ranks > kMaxPeers) throw std::runtime_error("too many ranks");
+  if (b.n_ranks > 0) {
+    auto ef = d["entry_flags"].cast<std::vector<uint64_t>>();
+    auto xf = d["exit_flags"].cast<std::vector<uint64_t>>();
+    for (int i = 0; i < b.n_ranks; ++i) {
+      b.entry_flags[i] = P<uint32_t>(ef[i]);
+      b.exit_flags[i] = P<uint32_t>(xf[i]);
+    }
+  }
+  b.epoch = (uint32_t)geti(d, "epoch");
+  b.go_flag = P<uint32_t>(getp(d, "go_flag"));
+  b.done_counter = P<uint32_t>(getp(d, "done_counter"));
+  b.done_target = (uint32_t)geti(d, "done_target");
+  b.status = P<uint32_t>(getp(d, "status"));
+  b.timeout_ns = (uint64_t)geti(d, "timeout_ns", 5000000000LL);
+  return b;
+}
+
+// ---------------------------------------------------------------------------------------
+// GEMM
+// ---------------------------------------------------------------------------------------
+void gemm_run(const py::dict& d) {
+  GemmArgs a;
+  std::memset(&a, 0, sizeof(a));
+  a.M = (int)geti(d, "M");
+  a.N = (int)geti(d, "N");
+  a.K = (int)geti(d, "K");
+  if (a.M <= 0 || a.N <= 0 || a.K <= 0) throw std::runtime_error("gemm: empty problem");
+  a.a_mn_major = (int)geti(d, "a_mn_major");
+  a.b_mn_major = (int)geti(d, "b_mn_major");
+  const uint64_t A = getp(d, "A"), B = getp(d, "B");
+  const int64_t lda = geti(d, "lda"), ldb = geti(d, "ldb");
+  if ((lda % 8) || (ldb % 8) || (A & 15) || (B & 15))
+    throw std::runtime_error("gemm: operands need 16-byte aligned bases and pitches");
+  a.C = P<void>(getp(d, "C"));
+  a.ldc = geti(d, "ldc");
+  a.c_fp32 = (int)geti(d, "c_fp32");
+  a.accumulate = (int)geti(d, "accumulate");
+  a.bias = P<void>(getp(d, "bias"));
+  a.act = (int)geti(d, "act");
+  a.C_pre = P<void>(getp(d, "C_pre"));
+  if (a.ldc % 8) throw std::runtime_error("gemm: ldc must be a multiple of 8");
+  a.tiles_m = (a.M + kBM - 1) / kBM;
+  a.tiles_n = (a.N + kBN - 1) / kBN;
+  a.slice_dim = (int)geti(d, "slice_dim");
+  a.n_slices = (int)geti(d, "n_slices", 1);
+  a.group = (int)geti(d, "group", 8);
+  const int tiles_s = a.slice_dim == 0 ? a.tiles_m : a.tiles_n;
+  a.cyc = (int)geti(d, "cyc", 1);
+  if (a.cyc < 1) a.cyc = 1;
+  if (a.n_slices < 1 || tiles_s % (a.n_slices * a.cyc) != 0)
+    throw std::runtime_error("gemm: n_slices must divide the tile count of the sliced dimension");
+  if (a.group < 1) a.group = 1;
+  if (geti(d, "no_tiles")) a.tiles_m = 0;  // reduce phase only
+  // pull side
+  a.jobs = P<const CopyJob>(getp(d, "jobs"));
+  a.chunk_job_begin = P<const int>(getp(d, "chunk_job_begin"));
+  a.n_chunks = (int)geti(d, "n_chunks");
+  a.chunk_flags = P<uint32_t>(getp(d, "chunk_flags"));
+  a.chunk_target = (uint32_t)geti(d, "chunk_target");
+  a.a_flag_mode = (int)geti(d, "a_flag_mode");
+  a.a_flag_base = (int)geti(d, "a_flag_base");
+  a.a_flag_count = (int)geti(d, "a_flag_count");
+  a.b_flag_mode = (int)geti(d, "b_flag_mode");
+  a.b_flag_base = (int)geti(d, "b_flag_base");
+  a.b_flag_count = (int)geti(d, "b_flag_count");
+  // push side
+  a.push_n = (int)geti(d, "push_n");
+  if (a.push_n > kMaxPeers) throw std::runtime_error("gemm: too many owners");
+  a.push_dim = (int)geti(d, "push_dim");
+  a.push_extent = (int)geti(d, "push_extent", 1);
+  a.push_ld = geti(d, "push_ld");
+  if (a.push_n > 0) {
+    auto pb = d["push_base"].cast<std::vector<uint64_t>>();
+    auto pc = d["push_counter"].cast<std::vector<uint64_t>>();
+    for (int i = 0; i < a.push_n; ++i) {
+      a.push_base[i] = P<void>(pb[i]);
+      a.push_counter[i] = P<uint32_t>(pc[i]);
+    }
+    const int tile = a.push_dim == 0 ? kBM : kBN;
+    if (a.push_extent % tile != 0 || a.push_ld % 8 != 0)
+      throw std::runtime_error("gemm: owner extent must be a multiple of the tile size");
+  }
+  a.red_n = (int)geti(d, "red_n");
+  a.red_slots = P<const void>(getp(d, "red_slots"));
+  a.red_rows = (int)geti(d, "red_rows");
+  a.red_cols = (int)geti(d, "red_cols");
+  a.red_ld = geti(d, "red_ld");
+  a.red_counter = P<const uint32_t>(getp(d, "red_counter"));
+  a.red_target = (uint32_t)geti(d, "red_target");
+  a.red_slice_dim = (int)geti(d, "red_slice_dim");
+  if (a.red_n > 0) {
+    const int rt = a.red_slice_dim == 0 ? (a.red_rows + kBM - 1) / kBM : (a.red_cols + kBN - 1) / kBN;
+    if (rt % (a.n_slices * a.cyc) != 0 || a.red_cols % 8 != 0 || a.red_ld % 8 != 0)
+      throw std::runtime_error("gemm: reduce phase shape not divisible by the slice count");
+  }
+  // barriers
+  BarrierArgs b = parse_barrier(d);
+  a.n_ranks = b.n_ranks;
+  a.my_rank = b.my_rank;
+  for (int i = 0; i < kMaxPeers; ++i) {
+    a.entry_flags[i] = b.entry_flags[i];
+    a.exit_flags[i] = b.exit_flags[i];
+  }
+  a.epoch = b.epoch;
+  a.exit_barrier = (int)geti(d, "exit_barrier");
+  a.go_flag = b.go_flag;
+  a.done_counter = b.done_counter;
+  a.done_target = b.done_target;
+  a.status = b.status;
+  a.timeout_ns = b.timeout_ns;
+  if (a.status == nullptr) throw std::runtime_error("gemm: status pointer required");
+
+  CUtensorMap ta, tb;
+  int r;
+  if (!a.a_mn_major) r = make_tensor_map_2d(&ta, P<void>(A), a.K, a.M, lda * 2, kBK, kBM);
+  else r = make_tensor_map_2d(&ta, P<void>(A), a.M, a.K, lda * 2, 64, kBK);
+  if (r != 0) throw std::runtime_error("gemm: tensor map for A failed, code " + std::to_string(r));
+  if (!a.b_mn_major) r = make_tensor_map_2d(&tb, P<void>(B), a.K, a.N, ldb * 2, kBK, kBN);
+  else r = make_tensor_map_2d(&tb, P<void>(B), a.N, a.K, ldb * 2, 64, kBK);
+  if (r != 0) throw std::runtime_error("gemm: tensor map for B failed, code " + std::to_string(r));
+
+  int grid = (int)geti(d, "grid", 148);
+  const int ntiles = a.tiles_m * a.tiles_n;
+  const bool needs_all = a.n_chunks > 0 || a.n_ranks > 0 || a.red_n > 0;
+  if (!needs_all && grid > ntiles) grid = ntiles;
+  check(launch_sm100_gemm(ta, tb, a, grid, S(getp(d, "stream"))), "sm100_gemm launch");
+}
+
+// ---------------------------------------------------------------------------------------
+// runtime: IPC-shared device memory, host-mapped status words
+// ---------------------------------------------------------------------------------------
+py::tuple symm_alloc(size_t bytes) {
+  void* p = nullptr;
+  check(cudaMalloc(&p, bytes), "cudaMalloc(symmetric heap)");
+  cudaIpcMemHandle_t h;
+  check(cudaIpcGetMemHandle(&h, p), "cudaIpcGetMemHandle");
+  return py::make_tuple((uint64_t)(uintptr_t)p,
+                        py::bytes(reinterpret_cast<const char*>(&h), sizeof(h)));
+}
+uint64_t symm_open(const py::bytes& handle) {
+  std::string s = handle;
+  if (s.size() != sizeof(cudaIpcMemHandle_t)) throw std::runtime_error("bad IPC handle size");
+  cudaIpcMemHandle_t h;
+  std::memcpy(&h, s.data(), sizeof(h));
+  void* p = nullptr;
+  check(cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess), "cudaIpcOpenMemHandle");
+  return (uint64_t)(uintptr_t)p;
+}
+void symm_close(uint64_t p) { check(cudaIpcCloseMemHandle(P<void>(p)), "cudaIpcCloseMemHandle"); }
+void symm_free(uint64_t p) { check(cudaFree(P<void>(p)), "cudaFree"); }
+
+py::tuple status_alloc() {
+  void* h = nullptr;
+  check(cudaHostAlloc(&h, 64, cudaHostAllocMapped | cudaHostAllocPortable), "cudaHostAlloc");
+  std::memset(h, 0, 64);
+  void* dptr = nullptr;
+  check(cudaHostGetDevicePointer(&dptr, h, 0), "cudaHostGetDevicePointer");
+  return py::make_tuple((uint64_t)(uintptr_t)h, (uint64_t)(uintptr_t)dptr);
+}
+py::tuple status_read(uint64_t host_ptr) {
+  volatile uint32_t* s = P<volatile uint32_t>(host_ptr);
+  return py::make_tuple(s[0], s[1], s[2], s[3]);
+}
+void status_clear(uint64_t host_ptr) { std::memset(P<void>(host_ptr), 0, 64); }
+
+void memset_zero(uint64_t ptr, size_t bytes, uint64_t stream) {
+  check(cudaMemsetAsync(P<void>(ptr), 0, bytes, S(stream)), "cudaMemsetAsync");
+}
+
+}  // namespace
+
+PYBIND11_MODULE(_C, m) {
+  m.doc() = "meshslice_b200 native kernels (sm_100a)";
+  m.attr("BM") = kBM;
+  m.attr("BN") = kBN;
+  m.attr("BK") = kBK;
+  m.attr("MAX_PEERS") = kMaxPeers;
+  m.attr("COPY_JOB_BYTES") = (int)sizeof(CopyJob);
+
+  m.def("gemm_run", &gemm_run, "persistent tcgen05 GEMM with optional fused pull / push");
+  m.def("symm_alloc", &symm_alloc);
+  m.def("symm_open", &symm_open);
+  m.def("symm_close", &symm_close);
+  m.def("symm_free", &symm_free);
+  m.def("status_alloc", &status_alloc);
+  m.def("status_read", &status_read);
+  m.def("status_clear", &status_clear);
+  m.def("memset_zero", &memset_zero);
+
+  m.def("p2p_copy", [](uint64_t jobs, int n_jobs, const py::dict& bar, int grid, uint64_t stream) {
+    check(p2p_copy(P<const CopyJob>(jobs), n_jobs, parse_barrier(bar), grid, S(stream)), "p2p_copy");
+  });
+  m.def("p2p_reduce", [](std::vector<uint64_t> src, int64_t src_pitch, uint64_t out, int64_t out_pitch,
+                         int rows, int cols, const py::dict& bar, int grid, uint64_t stream) {
+    ReduceArgs r;
+    std::memset(&r, 0, sizeof(r));
+    if ((int)src.size() > kMaxPeers) throw std::runtime_error("p2p_reduce: too many sources");
+    r.n_src = (int)src.size();
+    for (int i = 0; i < r.n_src; ++i) r.src[i] = P<const void>(src[i]);
+    r.src_pitch = src_pitch;
+    r.out = P<void>(out);
+    r.out_pitch = out_pitch;
+    r.rows = rows;
+    r.cols = cols;
+    check(p2p_reduce(r, parse_barrier(bar), grid, S(stream)), "p2p_reduce");
+  });
+  m.def("p2p_barrier", [](const py::dict& bar, uint64_t stream) {
+    check(p2p_barrier(parse_barrier(bar), S(stream)), "p2p_barrier");
+  });
+  m.def("bounded_wait_probe", [](uint64_t flag, uint32_t target, uint64_t timeout_ns, uint64_t status,
+                                 uint64_t stream) {
+    check(bounded_wait_probe(P<const uint32_t>(flag), target, timeout_ns, P<uint32_t>(status), S(stream)),
+          "bounded_wait_probe");
+  });
+
+  // ---- ops ----
+  m.def("ln_fwd", [](int mode, uint64_t x, uint64_t res, uint64_t h_out, uint64_t y, uint64_t gamma,
+                     uint64_t beta, uint64_t stats, uint64_t mean_rstd, int rows, int cols,
+                     int total_cols, float eps, uint64_t stream) {
+    check(ln_fwd(mode, P<void>(x), P<void>(res), P<void>(h_out), P<void>(y), P<void>(gamma),
+                 P<void>(beta), P<float>(stats), P<float>(mean_rstd), rows, cols, total_cols, eps,
+                 S(stream)), "ln_fwd");
+  });
+  m.def("ln_bwd", [](int mode, uint64_t dy, uint64_t h, uint64_t gamma, uint64_t mean_rstd,
+                     uint64_t dres, uint64_t dx, uint64_t stats, uint64_t dgamma, uint64_t dbeta,
+                     int rows, int cols, int total_cols, uint64_t stream) {
+    check(ln_bwd(mode, P<void>(dy), P<void>(h), P<void>(gamma), P<float>(mean_rstd), P<void>(dres),
+                 P<void>(dx), P<float>(stats), P<float>(dgamma), P<float>(dbeta), rows, cols,
+                 total_cols, S(stream)), "ln_bwd");
+  });
+  m.def("gelu_fwd", [](uint64_t x, uint64_t y, int64_t n, uint64_t stream) {
+    check(gelu_fwd(P<void>(x), P<void>(y), n, S(stream)), "gelu_fwd");
+  });
+  m.def("gelu_bwd", [](uint64_t dy, uint64_t x, uint64_t dx, int64_t n, uint64_t stream) {
+    check(gelu_bwd(P<void>(dy), P<void>(x), P<void>(dx), n, S(stream)), "gelu_bwd");
+  });
+  m.def("add_bf16", [](uint64_t a, uint64_t b, uint64_t o, int64_t n, uint64_t stream) {
+    check(add_bf16(P<void>(a), P<void>(b), P<void>(o), n, S(stream)), "add_bf16");
+  });
+  m.def("cast_f32_to_bf16", [](uint64_t in, uint64_t out, int64_t n, int accumulate, uint64_t stream) {
+    check(cast_f32_to_bf16(P<float>(in), P<void>(out), n, accumulate, S(stream)), "cast_f32_to_bf16");
+  });
+  m.def("adamw_step", [](uint64_t param, uint64_t master, uint64_t mm, uint64_t vv, uint64_t grad,
+                         int grad_fp32, int64_t n, float lr, float b1, float b2, float eps, float wd,
+                         float bc1, float bc2, uint64_t grad_scale, uint64_t stream) {
+    check(adamw_step(P<void>(param), P<float>(master), P<float>(mm), P<float>(vv), P<void>(grad),
+                     grad_fp32, n, lr, b1, b2, eps, wd, bc1, bc2, P<float>(grad_scale), S(stream)),
+          "adamw_step");
+  });
+  m.def("sumsq", [](uint64_t x, int is_fp32, int64_t n, uint64_t out, uint64_t stream) {
+    check(sumsq(P<void>(x), is_fp32, n, P<float>(out), S(stream)), "sumsq");
+  });
+  m.def("ce_partial", [](uint64_t logits, int64_t ld, uint64_t targets, int rows, int cols,
+                         int col_offset, int vocab, uint64_t row_max, uint64_t row_sumexp,
+                         uint64_t tgt_logit, uint64_t stream) {
+    check(ce_partial(P<void>(logits), ld, P<int64_t>(targets), rows, cols, col_offset, vocab,
+                     P<float>(row_max), P<float>(row_sumexp), P<float>(tgt_logit), S(stream)),
+          "ce_partial");
+  });
+  m.def("ce_grad", [](uint64_t logits, int64_t ld, uint64_t targets, int rows, int cols,
+                      int col_offset, int vocab, uint64_t gmax, uint64_t gsum, float scale,
+                      uint64_t stream) {
+    check(ce_grad(P<void>(logits), ld, P<int64_t>(targets), rows, cols, col_offset, vocab,
+                  P<float>(gmax), P<float>(gsum), scale, S(stream)), "ce_grad");
+  });
+  m.def("embedding_fwd", [](uint64_t tokens, uint64_t tok, uint64_t pos, uint64_t out, int n_tokens,
+                            int seq, int cols, uint64_t stream) {
+    check(embedding_fwd(P<int64_t>(tokens), P<void>(tok), P<void>(pos), P<void>(out), n_tokens, seq,
+                        cols, S(stream)), "embedding_fwd");
+  });
+  m.def("embedding_bwd", [](uint64_t tokens, uint64_t dout, uint64_t dtok, uint64_t dpos,
+                            int n_tokens, int seq, int cols, uint64_t stream) {
+    check(embedding_bwd(P<int64_t>(tokens), P<void>(dout), P<float>(dtok), P<float>(dpos), n_tokens,
+                        seq, cols, S(stream)), "embedding_bwd");
+  });
+}

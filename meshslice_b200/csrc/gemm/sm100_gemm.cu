@@ -1,0 +1,692 @@
+// Persistent, warp-specialised tcgen05 GEMM for sm_100a with fused mesh collectives.
+// See sm100_gemm.h for the interface and the role of each argument.
+//
+// CTA layout (224 threads, one CTA per SM, static round-robin tile schedule):
+//   warp 0      TMA producer: waits for the chunk flags a tile depends on, then fills a
+//               4-stage ring of (A 128x64, B 256x64) bf16 tiles in 128-byte-swizzled smem
+//   warp 1      MMA issuer: one elected thread issues tcgen05.mma (M=128, N=256, K=16) into
+//               one of two 256-column fp32 accumulators in TMEM
+//   warps 2..5  epilogue: tcgen05.ld the finished accumulator (one TMEM lane quarter per
+//               warp), apply bias/GeLU, store to local memory or to the owner GPU's slot
+//   warp 6      communication: cross-GPU entry/exit barrier (CTA 0) and the pull side's
+//               bulk copies peer -> smem -> local staging, one flag per chunk
+// After its tiles every CTA joins the reduce phase, which sums the partial tiles that peers
+// pushed into this GPU's slots.
+//
+// Every wait is bounded (ptx.cuh); on expiry the kernel records a code in `status`, leaves
+// its loops, frees TMEM and returns.
+#include "sm100_gemm.h"
+
+#include <cuda_bf16.h>
+
+#include "../common/ptx.cuh"
+
+namespace msb {
+
+namespace {
+
+constexpr uint32_t kAStageBytes = kBM * kBK * 2;  // 16 KiB
+constexpr uint32_t kBStageBytes = kBN * kBK * 2;  // 32 KiB
+constexpr uint32_t kSmemA = 0;
+constexpr uint32_t kSmemB = kSmemA + kStages * kAStageBytes;
+constexpr uint32_t kSmemComm = kSmemB + kStages * kBStageBytes;
+constexpr uint32_t kSmemBar = kSmemComm + kCommBufs * kCommBufBytes;
+constexpr uint32_t kSmemTotal = kSmemBar + 256;
+constexpr uint32_t kSmemAlloc = kSmemTotal + 1024;  // slack for manual 1024-byte alignment
+constexpr uint32_t kTmemCols = 512;
+constexpr int kEpiThreads = 128;
+
+struct TileCoord {
+  int m_blk, n_blk, slice;
+};
+
+__device__ __forceinline__ TileCoord tile_coord(int t, const GemmArgs& a) {
+  const int tiles_s = a.slice_dim == 0 ? a.tiles_m : a.tiles_n;
+  const int tiles_o = a.slice_dim == 0 ? a.tiles_n : a.tiles_m;
+  const int S = a.n_slices;
+  const int nb = tiles_s / S;
+  const int per_slice = nb * tiles_o;
+  const int s = t / per_slice;
+  const int r = t - s * per_slice;
+  const int g_span = a.group * tiles_o;
+  const int g = r / g_span;
+  const int rr = r - g * g_span;
+  const int g0 = g * a.group;
+  const int geff = min(a.group, nb - g0);
+  const int o = rr / geff;
+  const int w = rr - o * geff;
+  const int jj = g0 + w;
+  const int cg = jj / a.cyc;
+  const int blk_s = (cg * S + s) * a.cyc + (jj - cg * a.cyc);
+  TileCoord c;
+  c.m_blk = a.slice_dim == 0 ? blk_s : o;
+  c.n_blk = a.slice_dim == 0 ? o : blk_s;
+  c.slice = s;
+  return c;
+}
+
+__device__ __forceinline__ void report(const GemmArgs& a, uint32_t code, uint32_t d0, uint32_t d1) {
+  if (atomicCAS(a.status, 0u, code) == 0u) {
+    a.status[1] = blockIdx.x;
+    a.status[2] = d0;
+    a.status[3] = d1;
+  }
+}
+
+__device__ __forceinline__ float gelu_tanh(float x) {
+  const float k0 = 0.7978845608028654f, k1 = 0.044715f;
+  float u = k0 * (x + k1 * x * x * x);
+  float t;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(u));
+  return 0.5f * x * (1.0f + t);
+}
+
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+__device__ __forceinline__ float bf16_lo(uint32_t v) { return __uint_as_float(v << 16); }
+__device__ __forceinline__ float bf16_hi(uint32_t v) { return __uint_as_float(v & 0xffff0000u); }
+
+// Waits for the chunk flags of one operand.  Returns false on timeout.
+__device__ __forceinline__ bool wait_operand(const GemmArgs& a, int mode, int base, int count,
+                                             int slice, uint64_t tmo) {
+  if (mode == 0) return true;
+  if (mode == 1) return wait_flag_geq_gpu(a.chunk_flags + base + slice, a.chunk_target, tmo);
+  for (int i = 0; i < count; ++i)
+    if (!wait_flag_geq_gpu(a.chunk_flags + base + i, a.chunk_target, tmo)) return false;
+  return true;
+}
+
+// ------------------------------------------------------------------------------------------
+// communication warp: one piece = at most kCommBufBytes
+// ------------------------------------------------------------------------------------------
+struct Piece {
+  const char* src;
+  char* dst;
+  uint32_t rows;
+  uint32_t row_bytes;
+  uint64_t sp, dp;
+};
+
+struct PieceCursor {
+  const CopyJob* jobs;
+  int job, job_end;
+  uint32_t next_in_job;   // next piece index of this CTA inside the current job
+  uint32_t pieces_in_job;
+  uint32_t rows_per_piece, segs_per_row;
+  uint32_t running;       // pieces of earlier jobs of the chunk (for the round-robin)
+  __device__ void open_job() {
+    while (job < job_end) {
+      const CopyJob& j = jobs[job];
+      if (j.row_bytes >= (uint32_t)kCommBufBytes) {
+        segs_per_row = (j.row_bytes + kCommBufBytes - 1) / kCommBufBytes;
+        rows_per_piece = 1;
+        pieces_in_job = j.rows * segs_per_row;
+      } else {
+        segs_per_row = 1;
+        rows_per_piece = kCommBufBytes / j.row_bytes;
+        pieces_in_job = (j.rows + rows_per_piece - 1) / rows_per_piece;
+      }
+      const uint32_t g = gridDim.x;
+      next_in_job = (blockIdx.x + g - (running % g)) % g;
+      if (next_in_job < pieces_in_job) return;
+      running += pieces_in_job;
+      ++job;
+    }
+  }
+  __device__ void init(const CopyJob* js, int jb, int je) {
+    jobs = js;
+    job = jb;
+    job_end = je;
+    running = 0;
+    open_job();
+  }
+  __device__ bool next(Piece& p) {
+    if (job >= job_end) return false;
+    const CopyJob& j = jobs[job];
+    const uint32_t idx = next_in_job;
+    if (segs_per_row > 1) {
+      const uint32_t row = idx / segs_per_row, seg = idx - row * segs_per_row;
+      const uint32_t off = seg * kCommBufBytes;
+      p.src = j.src + (uint64_t)row * j.src_pitch + off;
+      p.dst = j.dst + (uint64_t)row * j.dst_pitch + off;
+      p.rows = 1;
+      p.row_bytes = min((uint32_t)kCommBufBytes, j.row_bytes - off);
+    } else {
+      const uint32_t row0 = idx * rows_per_piece;
+      p.src = j.src + (uint64_t)row0 * j.src_pitch;
+      p.dst = j.dst + (uint64_t)row0 * j.dst_pitch;
+      p.rows = min(rows_per_piece, j.rows - row0);
+      p.row_bytes = j.row_bytes;
+    }
+    p.sp = j.src_pitch;
+    p.dp = j.dst_pitch;
+    next_in_job += gridDim.x;
+    if (next_in_job >= pieces_in_job) {
+      running += pieces_in_job;
+      ++job;
+      open_job();
+    }
+    return true;
+  }
+};
+
+__device__ void comm_warp_main(const GemmArgs& a, uint8_t* comm_smem, uint64_t* comm_bar) {
+  const int lane = threadIdx.x & 31;
+  const uint64_t tmo = a.timeout_ns;
+  bool ok = true;
+
+  // ---- entry barrier: CTA 0 tells every rank that this GPU's earlier work is complete and
+  //      waits for the same message from every rank, then releases the local CTAs.
+  if (a.n_ranks > 0) {
+    if (blockIdx.x == 0) {
+      if (lane < a.n_ranks && lane != a.my_rank) {
+        st_release_sys(a.entry_flags[lane] + a.my_rank, a.epoch);
+        if (!wait_flag_geq_sys(a.entry_flags[a.my_rank] + lane, a.epoch, tmo)) {
+          report(a, kTimeoutEntry, lane, a.epoch);
+          ok = false;
+        }
+      }
+      ok = __all_sync(0xffffffffu, ok);
+      if (lane == 0 && ok) st_release_gpu(a.go_flag, a.epoch);
+    } else {
+      if (lane == 0) {
+        if (!wait_flag_geq_gpu(a.go_flag, a.epoch, 2 * tmo)) {
+          report(a, kTimeoutGo, 0, a.epoch);
+          ok = false;
+        }
+      }
+      ok = __all_sync(0xffffffffu, ok);
+    }
+  }
+
+  // ---- pull side
+  if (lane == 0 && ok && a.n_chunks > 0) {
+    uint32_t issued = 0, stored = 0;
+    Piece q[kCommBufs];
+    for (int c = 0; c < a.n_chunks && ok; ++c) {
+      PieceCursor cur;
+      cur.init(a.jobs, a.chunk_job_begin[c], a.chunk_job_begin[c + 1]);
+      bool more = true;
+      while (ok) {
+        while (more && issued - stored < 2) {
+          Piece p;
+          more = cur.next(p);
+          if (!more) break;
+          bulk_wait_read<2>();  // the store that last read this buffer has finished
+          const uint32_t b = issued % kCommBufs;
+          uint8_t* buf = comm_smem + b * kCommBufBytes;
+          const uint32_t total = p.rows * p.row_bytes;
+          mbar_expect_tx(comm_bar + b, total);
+          if (p.rows == 1 || p.sp == p.row_bytes) {
+            bulk_g2s(buf, p.src, total, comm_bar + b);
+          } else {
+            for (uint32_t r = 0; r < p.rows; ++r)
+              bulk_g2s(buf + r * p.row_bytes, p.src + r * p.sp, p.row_bytes, comm_bar + b);
+          }
+          q[b] = p;
+          ++issued;
+        }
+        if (stored == issued) break;
+        const uint32_t b = stored % kCommBufs;
+        if (!mbar_wait(comm_bar + b, (stored / kCommBufs) & 1, tmo)) {
+          report(a, kTimeoutComm, c, stored);
+          ok = false;
+          break;
+        }
+        const Piece& p = q[b];
+        const uint8_t* buf = comm_smem + b * kCommBufBytes;
+        if (p.rows == 1 || p.dp == p.row_bytes) {
+          bulk_s2g(p.dst, buf, p.rows * p.row_bytes);
+        } else {
+          for (uint32_t r = 0; r < p.rows; ++r)
+            bulk_s2g(p.dst + r * p.dp, buf + r * p.row_bytes, p.row_bytes);
+        }
+        bulk_commit();
+        ++stored;
+      }
+      bulk_wait_all<0>();
+      fence_proxy_async();
+      __threadfence();
+      if (ok) red_add_release_gpu(a.chunk_flags + c, 1u);
+    }
+    bulk_wait_all<0>();
+  }
+
+  // ---- exit barrier: peers may overwrite their shards only after everybody stopped pulling
+  if (a.n_ranks > 0 && a.exit_barrier) {
+    if (lane == 0) red_add_release_gpu(a.done_counter, 1u);
+    if (blockIdx.x == 0) {
+      bool ok2 = ok;
+      if (lane == 0 && ok2) {
+        if (!wait_flag_geq_gpu(a.done_counter, a.done_target, 6 * tmo)) {
+          report(a, kTimeoutExit, 0xffffffffu, a.epoch);
+          ok2 = false;
+        }
+      }
+      ok2 = __all_sync(0xffffffffu, ok2);
+      if (ok2 && lane < a.n_ranks && lane != a.my_rank) {
+        st_release_sys(a.exit_flags[lane] + a.my_rank, a.epoch);
+        if (!wait_flag_geq_sys(a.exit_flags[a.my_rank] + lane, a.epoch, 6 * tmo))
+          report(a, kTimeoutExit, lane, a.epoch);
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// epilogue helpers
+// ------------------------------------------------------------------------------------------
+// Stores 32 consecutive columns of one row.  `v` holds fp32 accumulators.
+__device__ __forceinline__ void store_row32(const GemmArgs& a, void* base, int64_t ld, bool fp32,
+                                            bool accumulate, int64_t row, int col0, int ncols_valid,
+                                            float (&v)[32]) {
+  if (fp32) {
+    float* p = reinterpret_cast<float*>(base) + row * ld + col0;
+    if (ncols_valid == 32) {
+#pragma unroll
+      for (int i = 0; i < 32; i += 4) {
+        float4 o = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+        if (accumulate) {
+          float4 c = *reinterpret_cast<const float4*>(p + i);
+          o.x += c.x; o.y += c.y; o.z += c.z; o.w += c.w;
+        }
+        *reinterpret_cast<float4*>(p + i) = o;
+      }
+    } else {
+      for (int i = 0; i < ncols_valid; ++i) p[i] = accumulate ? p[i] + v[i] : v[i];
+    }
+  } else {
+    __nv_bfloat16* p = reinterpret_cast<__nv_bfloat16*>(base) + row * ld + col0;
+    if (ncols_valid == 32) {
+#pragma unroll
+      for (int i = 0; i < 32; i += 8) {
+        uint4 o;
+        if (accumulate) {
+          uint4 c = *reinterpret_cast<const uint4*>(p + i);
+          o.x = pack_bf16(v[i] + bf16_lo(c.x), v[i + 1] + bf16_hi(c.x));
+          o.y = pack_bf16(v[i + 2] + bf16_lo(c.y), v[i + 3] + bf16_hi(c.y));
+          o.z = pack_bf16(v[i + 4] + bf16_lo(c.z), v[i + 5] + bf16_hi(c.z));
+          o.w = pack_bf16(v[i + 6] + bf16_lo(c.w), v[i + 7] + bf16_hi(c.w));
+        } else {
+          o.x = pack_bf16(v[i], v[i + 1]);
+          o.y = pack_bf16(v[i + 2], v[i + 3]);
+          o.z = pack_bf16(v[i + 4], v[i + 5]);
+          o.w = pack_bf16(v[i + 6], v[i + 7]);
+        }
+        *reinterpret_cast<uint4*>(p + i) = o;
+      }
+    } else {
+      for (int i = 0; i < ncols_valid; ++i) {
+        float x = v[i];
+        if (accumulate) x += __bfloat162float(p[i]);
+        p[i] = __float2bfloat16_rn(x);
+      }
+    }
+  }
+}
+
+}  // namespace
+
+// ------------------------------------------------------------------------------------------
+// kernel
+// ------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(kGemmThreads, 1)
+sm100_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+                  const __grid_constant__ GemmArgs a) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* sA = smem + kSmemA;
+  uint8_t* sB = smem + kSmemB;
+  uint8_t* sComm = smem + kSmemComm;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kSmemBar);
+  uint64_t* full_bar = bars;                   // [kStages]
+  uint64_t* empty_bar = bars + kStages;        // [kStages]
+  uint64_t* tfull_bar = bars + 2 * kStages;    // [2]
+  uint64_t* tempty_bar = tfull_bar + 2;        // [2]
+  uint64_t* comm_bar = tempty_bar + 2;         // [kCommBufs]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(comm_bar + kCommBufs);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint64_t tmo = a.timeout_ns;
+  const int num_tiles = a.tiles_m * a.tiles_n;
+  const int kblocks = (a.K + kBK - 1) / kBK;
+
+  if (warp == 0 && lane == 0) {
+    tma_prefetch_desc(&tma_a);
+    tma_prefetch_desc(&tma_b);
+    for (int i = 0; i < kStages; ++i) {
+      mbar_init(full_bar + i, 1);
+      mbar_init(empty_bar + i, 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(tfull_bar + i, 1);
+      mbar_init(tempty_bar + i, kEpiThreads);
+    }
+    for (int i = 0; i < kCommBufs; ++i) mbar_init(comm_bar + i, 1);
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ===================== TMA producer =====================
+    if (lane == 0) {
+      bool ok = true;
+      if (a.n_ranks > 0 && num_tiles > 0) {
+        if (!wait_flag_geq_gpu(a.go_flag, a.epoch, 2 * tmo)) {
+          report(a, kTimeoutGo, 1, a.epoch);
+          ok = false;
+        }
+      }
+      uint32_t stage = 0, phase = 0;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        const TileCoord tc = tile_coord(t, a);
+        if (a.a_flag_mode | a.b_flag_mode) {
+          if (!wait_operand(a, a.a_flag_mode, a.a_flag_base, a.a_flag_count, tc.slice, 3 * tmo) ||
+              !wait_operand(a, a.b_flag_mode, a.b_flag_base, a.b_flag_count, tc.slice, 3 * tmo)) {
+            report(a, kTimeoutChunk, t, tc.slice);
+            ok = false;
+            break;
+          }
+          fence_proxy_async();
+        }
+        for (int kb = 0; kb < kblocks; ++kb) {
+          if (!mbar_wait(empty_bar + stage, phase ^ 1, 5 * tmo)) {
+            report(a, kTimeoutEmpty, t, kb);
+            ok = false;
+            break;
+          }
+          mbar_expect_tx(full_bar + stage, kAStageBytes + kBStageBytes);
+          uint8_t* da = sA + stage * kAStageBytes;
+          uint8_t* db = sB + stage * kBStageBytes;
+          if (!a.a_mn_major) {
+            tma_load_2d(da, &tma_a, full_bar + stage, kb * kBK, tc.m_blk * kBM);
+          } else {
+#pragma unroll
+            for (int j = 0; j < kBM / 64; ++j)
+              tma_load_2d(da + j * (kBK * 128), &tma_a, full_bar + stage, tc.m_blk * kBM + j * 64,
+                          kb * kBK);
+          }
+          if (!a.b_mn_major) {
+            tma_load_2d(db, &tma_b, full_bar + stage, kb * kBK, tc.n_blk * kBN);
+          } else {
+#pragma unroll
+            for (int j = 0; j < kBN / 64; ++j)
+              tma_load_2d(db + j * (kBK * 128), &tma_b, full_bar + stage, tc.n_blk * kBN + j * 64,
+                          kb * kBK);
+          }
+          if (++stage == kStages) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ===================== MMA issuer =====================
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc_bf16(kBM, kBN, a.a_mn_major, a.b_mn_major);
+      const uint32_t a_lbo = a.a_mn_major ? kBK * 128 : 16;
+      const uint32_t b_lbo = a.b_mn_major ? kBK * 128 : 16;
+      const uint32_t a_kstep = a.a_mn_major ? 16 * 128 : 32;  // bytes per K=16 step
+      const uint32_t b_kstep = a.b_mn_major ? 16 * 128 : 32;
+      uint32_t stage = 0, phase = 0;
+      bool ok = true;
+      int it = 0;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++it) {
+        const uint32_t acc = it & 1, acc_phase = (it >> 1) & 1;
+        if (!mbar_wait(tempty_bar + acc, acc_phase ^ 1, 6 * tmo)) {
+          report(a, kTimeoutTmemEmpty, t, acc);
+          ok = false;
+          break;
+        }
+        tc_fence_after_sync();
+        const uint32_t tmem_d = tmem_base + acc * kBN;
+        for (int kb = 0; kb < kblocks; ++kb) {
+          if (!mbar_wait(full_bar + stage, phase, 4 * tmo)) {
+            report(a, kTimeoutFull, t, kb);
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          const uint32_t sa = smem_u32(sA + stage * kAStageBytes);
+          const uint32_t sb = smem_u32(sB + stage * kBStageBytes);
+#pragma unroll
+          for (int k = 0; k < kBK / 16; ++k) {
+            const uint64_t da = make_smem_desc(sa + k * a_kstep, a_lbo, 1024);
+            const uint64_t db = make_smem_desc(sb + k * b_kstep, b_lbo, 1024);
+            umma_f16(tmem_d, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit(empty_bar + stage);
+          if (++stage == kStages) { stage = 0; phase ^= 1; }
+        }
+        if (ok) umma_commit(tfull_bar + acc);
+      }
+    }
+  } else if (warp < 6) {
+    // ===================== epilogue =====================
+    const int q = warp & 3;  // TMEM lane quarter this warp may read
+    const __nv_bfloat16* bias = reinterpret_cast<const __nv_bfloat16*>(a.bias);
+    bool ok = true;
+    int it = 0;
+    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++it) {
+      const TileCoord tc = tile_coord(t, a);
+      const uint32_t acc = it & 1, acc_phase = (it >> 1) & 1;
+      // lane 0 does the bounded wait and the warp follows its verdict, so the warp-wide
+      // tcgen05.ld below is never reached by only some of the lanes
+      int okw = 1;
+      if (lane == 0) okw = mbar_wait(tfull_bar + acc, acc_phase, 7 * tmo) ? 1 : 0;
+      okw = __shfl_sync(0xffffffffu, okw, 0);
+      if (!okw) {
+        if (lane == 0) report(a, kTimeoutTmemFull, t, acc);
+        ok = false;
+        break;
+      }
+      mbar_wait(tfull_bar + acc, acc_phase, tmo);  // already complete: orders this lane's reads
+      tc_fence_after_sync();
+      const int64_t row = (int64_t)tc.m_blk * kBM + q * 32 + lane;
+      const bool row_ok = row < a.M;
+      // destination of this tile
+      void* out = a.C;
+      int64_t ld = a.ldc;
+      bool out_fp32 = a.c_fp32 != 0, accum = a.accumulate != 0;
+      int64_t orow = row;
+      int ocol_shift = 0;
+      int owner = 0;
+      if (a.push_n > 0) {
+        const int c0 = a.push_dim == 0 ? tc.m_blk * kBM : tc.n_blk * kBN;
+        owner = c0 / a.push_extent;
+        out = a.push_base[owner];
+        ld = a.push_ld;
+        out_fp32 = false;
+        accum = false;
+        if (a.push_dim == 0) orow = row - (int64_t)owner * a.push_extent;
+        else ocol_shift = owner * a.push_extent;
+      }
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * kBN;
+#pragma unroll 1
+      for (int c = 0; c < kBN / 32; ++c) {
+        uint32_t r[32];
+        __syncwarp();
+        tmem_ld_32x32(taddr + c * 32, r);
+        tmem_ld_wait();
+        if (c == kBN / 32 - 1) {
+          // accumulator fully read: hand it back to the MMA warp
+          tc_fence_before_sync();
+          mbar_arrive(tempty_bar + acc);
+        }
+        const int col0 = tc.n_blk * kBN + c * 32;
+        const int nvalid = min(32, a.N - col0);
+        if (row_ok && nvalid > 0) {
+          float v[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+          if (a.push_n == 0) {
+            if (bias != nullptr) {
+              for (int i = 0; i < 32; ++i)
+                if (i < nvalid) v[i] += __bfloat162float(bias[col0 + i]);
+            }
+            if (a.act == 1) {
+              if (a.C_pre != nullptr)
+                store_row32(a, a.C_pre, ld, false, false, orow, col0, nvalid, v);
+#pragma unroll
+              for (int i = 0; i < 32; ++i) v[i] = gelu_tanh(v[i]);
+            }
+          }
+          store_row32(a, out, ld, out_fp32, accum, orow, col0 - ocol_shift, nvalid, v);
+        }
+      }
+      if (a.push_n > 0) {
+        // make this warp's part of the tile visible to the owner, then count it there
+        // (four counts per tile: one per epilogue warp, so no CTA-wide barrier is needed)
+        __threadfence_system();
+        __syncwarp();
+        if (lane == 0) red_add_release_sys(a.push_counter[owner] + tc.slice, 1u);
+      }
+    }
+  } else {
+    // ===================== communication warp =====================
+    comm_warp_main(a, sComm, comm_bar);
+  }
+
+  // ---- all roles of this CTA are done with TMEM and the pipeline
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  if (warp == 1) tmem_dealloc(tmem_base, kTmemCols);
+
+  // ===================== reduce phase =====================
+  if (a.red_n > 0) {
+    const int tiles_r = (a.red_rows + kBM - 1) / kBM;
+    const int tiles_c = (a.red_cols + kBN - 1) / kBN;
+    const int tiles_s = a.red_slice_dim == 0 ? tiles_r : tiles_c;
+    const int tiles_o = a.red_slice_dim == 0 ? tiles_c : tiles_r;
+    const int S = a.n_slices;
+    const int nb = tiles_s / S;
+    const int n_items = tiles_r * tiles_c;
+    const __nv_bfloat16* slots = reinterpret_cast<const __nv_bfloat16*>(a.red_slots);
+    const __nv_bfloat16* bias = reinterpret_cast<const __nv_bfloat16*>(a.bias);
+    const int64_t slot_stride = (int64_t)a.red_rows * a.red_ld;
+    for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
+      // slice-major order so that early slices are summed while late ones are in flight
+      const int s = item / (nb * tiles_o);
+      const int r = item - s * (nb * tiles_o);
+      const int j = r / tiles_o, o = r - j * tiles_o;
+      const int cg = j / a.cyc;
+      const int blk_s = (cg * S + s) * a.cyc + (j - cg * a.cyc);
+      const int rb = a.red_slice_dim == 0 ? blk_s : o;
+      const int cb = a.red_slice_dim == 0 ? o : blk_s;
+      int ok = 1;
+      if (threadIdx.x == 0) {
+        if (!wait_flag_geq_sys(a.red_counter + s, a.red_target, 8 * tmo)) {
+          report(a, kTimeoutReduce, s, item);
+          ok = 0;
+        }
+      }
+      ok = __syncthreads_and(ok);
+      if (!ok) break;
+      // 128 x 256 block, 8 bf16 per vector
+      for (int vi = threadIdx.x; vi < kBM * (kBN / 8); vi += kGemmThreads) {
+        const int rr = vi / (kBN / 8), cv = vi - rr * (kBN / 8);
+        const int64_t row = (int64_t)rb * kBM + rr;
+        const int col = cb * kBN + cv * 8;
+        if (row >= a.red_rows || col >= a.red_cols) continue;
+        float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        for (int sl = 0; sl < a.red_n; ++sl) {
+          const uint4 x = *reinterpret_cast<const uint4*>(slots + sl * slot_stride + row * a.red_ld + col);
+          acc[0] += bf16_lo(x.x); acc[1] += bf16_hi(x.x);
+          acc[2] += bf16_lo(x.y); acc[3] += bf16_hi(x.y);
+          acc[4] += bf16_lo(x.z); acc[5] += bf16_hi(x.z);
+          acc[6] += bf16_lo(x.w); acc[7] += bf16_hi(x.w);
+        }
+        if (bias != nullptr) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) acc[i] += __bfloat162float(bias[col + i]);
+        }
+        if (a.c_fp32) {
+          float* p = reinterpret_cast<float*>(a.C) + row * a.ldc + col;
+          float4 lo = make_float4(acc[0], acc[1], acc[2], acc[3]);
+          float4 hi = make_float4(acc[4], acc[5], acc[6], acc[7]);
+          if (a.accumulate) {
+            const float4 c0 = *reinterpret_cast<const float4*>(p);
+            const float4 c1 = *reinterpret_cast<const float4*>(p + 4);
+            lo.x += c0.x; lo.y += c0.y; lo.z += c0.z; lo.w += c0.w;
+            hi.x += c1.x; hi.y += c1.y; hi.z += c1.z; hi.w += c1.w;
+          }
+          *reinterpret_cast<float4*>(p) = lo;
+          *reinterpret_cast<float4*>(p + 4) = hi;
+        } else {
+          __nv_bfloat16* p = reinterpret_cast<__nv_bfloat16*>(a.C) + row * a.ldc + col;
+          if (a.accumulate) {
+            const uint4 c = *reinterpret_cast<const uint4*>(p);
+            acc[0] += bf16_lo(c.x); acc[1] += bf16_hi(c.x);
+            acc[2] += bf16_lo(c.y); acc[3] += bf16_hi(c.y);
+            acc[4] += bf16_lo(c.z); acc[5] += bf16_hi(c.z);
+            acc[6] += bf16_lo(c.w); acc[7] += bf16_hi(c.w);
+          }
+          uint4 o4;
+          o4.x = pack_bf16(acc[0], acc[1]);
+          o4.y = pack_bf16(acc[2], acc[3]);
+          o4.z = pack_bf16(acc[4], acc[5]);
+          o4.w = pack_bf16(acc[6], acc[7]);
+          *reinterpret_cast<uint4*>(p) = o4;
+        }
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// host side
+// ------------------------------------------------------------------------------------------
+size_t sm100_gemm_smem_bytes() { return kSmemAlloc; }
+
+cudaError_t launch_sm100_gemm(const CUtensorMap& tma_a, const CUtensorMap& tma_b,
+                              const GemmArgs& args, int grid, cudaStream_t stream) {
+  static bool configured[64] = {false};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (dev < 64 && !configured[dev]) {
+    e = cudaFuncSetAttribute(sm100_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)kSmemAlloc);
+    if (e != cudaSuccess) return e;
+    configured[dev] = true;
+  }
+  sm100_gemm_kernel<<<grid, kGemmThreads, kSmemAlloc, stream>>>(tma_a, tma_b, args);
+  return cudaGetLastError();
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+int make_tensor_map_2d(CUtensorMap* map, const void* base, uint64_t inner, uint64_t outer,
+                       uint64_t pitch_bytes, uint32_t box_inner, uint32_t box_outer) {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres);
+    if (e != cudaSuccess || p == nullptr) return -1;
+    fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  cuuint64_t dims[2] = {inner, outer};
+  cuuint64_t strides[1] = {pitch_bytes};
+  cuuint32_t box[2] = {box_inner, box_outer};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides,
+                  box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : (int)r;
+}
+
+}  // namespace msb

@@ -1,0 +1,127 @@
+// Host-visible interface of the persistent tcgen05 GEMM with fused mesh collectives.
+//
+// One kernel computes  C[M,N] = op(A) * op(B)  (bf16 inputs, fp32 accumulation in TMEM) and,
+// when asked to, also moves the data of the surrounding 2-D tensor-parallel collectives:
+//   * "pull" side (all-gather -> GEMM): a communication warp in every CTA copies chunks of
+//     peer shards into this GPU's staging buffer with untiled bulk copies and publishes one
+//     flag per chunk; the TMA producer warp waits for the flag of the chunk a tile needs.
+//   * "push" side (GEMM -> reduce-scatter): the epilogue stores each partial tile straight
+//     into the slot buffer of the GPU that owns it (peer stores over NVLink), bumps a
+//     per-slice counter there, and a trailing phase on the owner sums the slots.
+// This covers the three MeshSlice dataflows of the reference (TensorParallel.py:153-214):
+// OS = pull A and B, LS = pull B and push over columns, RS = pull A and push over rows.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace msb {
+
+constexpr int kBM = 128;
+constexpr int kBN = 256;
+constexpr int kBK = 64;
+constexpr int kStages = 4;
+constexpr int kMaxPeers = 8;
+constexpr int kGemmThreads = 224;  // 7 warps: TMA, MMA, 4x epilogue, communication
+constexpr int kCommBufBytes = 8192;
+constexpr int kCommBufs = 4;
+
+// Error codes written to the status word (first error wins).
+enum GemmStatus : uint32_t {
+  kOk = 0,
+  kTimeoutEmpty = 1,      // producer waited too long for a free pipeline stage
+  kTimeoutFull = 2,       // MMA warp waited too long for TMA data
+  kTimeoutTmemEmpty = 3,  // MMA warp waited too long for the epilogue to drain TMEM
+  kTimeoutTmemFull = 4,   // epilogue waited too long for the accumulator
+  kTimeoutChunk = 5,      // producer waited too long for a gathered chunk
+  kTimeoutComm = 6,       // communication warp waited too long for a bulk copy
+  kTimeoutEntry = 7,      // entry barrier with peers timed out
+  kTimeoutExit = 8,       // exit barrier with peers timed out
+  kTimeoutReduce = 9,     // reduce phase waited too long for peers' partial tiles
+  kTimeoutGo = 10,        // CTA waited too long for the local "peers are ready" flag
+};
+
+// One 2-D copy of the pull side.  All addresses 16-byte aligned, row_bytes % 16 == 0.
+struct CopyJob {
+  const char* src;  // peer (or local) memory
+  char* dst;        // local staging
+  uint32_t rows;
+  uint32_t row_bytes;
+  uint64_t src_pitch;
+  uint64_t dst_pitch;
+};
+
+struct GemmArgs {
+  // ---- problem ----
+  int M, N, K;
+  int a_mn_major;  // 0: A stored [M,K] row-major; 1: A stored [K,M] row-major
+  int b_mn_major;  // 0: B stored [N,K] row-major; 1: B stored [K,N] row-major
+  // ---- local epilogue (used when push_n == 0) ----
+  void* C;
+  int64_t ldc;
+  int c_fp32;          // 1: C is float, 0: C is bf16
+  int accumulate;      // 1: C += result
+  const void* bias;    // bf16 [N] or null
+  int act;             // 0: none, 1: tanh-GeLU
+  void* C_pre;         // bf16, same layout as C: pre-activation copy (act != 0), may be null
+  // ---- tile order ----
+  int tiles_m, tiles_n;
+  int slice_dim;       // 0: slices over M blocks, 1: slices over N blocks
+  int n_slices;        // block-cyclic slices of the sliced dimension (divides its tile count)
+  int group;           // raster group size along the sliced dimension
+  int cyc;             // tiles per cyclic block: slice s holds blocks (g*n_slices + s)*cyc + w
+  // ---- pull side ----
+  const CopyJob* jobs;
+  const int* chunk_job_begin;  // [n_chunks + 1]
+  int n_chunks;
+  uint32_t* chunk_flags;       // [n_chunks] monotonic; each launch adds gridDim.x to each
+  uint32_t chunk_target;       // value that marks "complete" for this launch
+  int a_flag_mode;             // 0: none, 1: flag a_flag_base + slice(tile), 2: all of [base, base+count)
+  int a_flag_base, a_flag_count;
+  int b_flag_mode;
+  int b_flag_base, b_flag_count;
+  // ---- push side ----
+  int push_n;                  // number of owners (0: local epilogue)
+  int push_dim;                // 0: owners split M, 1: owners split N
+  int push_extent;             // rows (or columns) owned by each owner
+  void* push_base[kMaxPeers];  // owner o's slot for this source (bf16 [rows_local, ld])
+  int64_t push_ld;
+  uint32_t* push_counter[kMaxPeers];  // owner o's per-slice arrival counters
+  // ---- reduce phase (runs on the owner after its tiles) ----
+  int red_n;                   // number of source slots to sum (0: no reduce phase)
+  const void* red_slots;       // bf16 [red_n][red_rows][red_ld]
+  int red_rows, red_cols;
+  int64_t red_ld;
+  const uint32_t* red_counter; // local per-slice counters
+  uint32_t red_target;         // counter value once every partial tile of a slice has arrived
+                               // (each tile counts 4: one per epilogue warp of the sender)
+  int red_slice_dim;           // 0: slice = block-cyclic row blocks (kBM), 1: column blocks (kBN)
+  // the reduce phase writes to C / ldc / c_fp32 / accumulate / bias as the local epilogue does
+  // ---- cross-GPU barriers ----
+  int n_ranks;                 // ranks taking part (0: no barriers)
+  int my_rank;
+  uint32_t* entry_flags[kMaxPeers];  // rank r's entry flag array (index: source rank)
+  uint32_t* exit_flags[kMaxPeers];   // rank r's exit flag array
+  uint32_t epoch;              // value for this launch (monotonic per workspace)
+  int exit_barrier;            // 1: wait for all peers to finish pulling before leaving
+  uint32_t* go_flag;           // local: set to epoch by CTA 0 once all peers have arrived
+  uint32_t* done_counter;      // local: CTAs that finished pulling (monotonic)
+  uint32_t done_target;
+  // ---- status ----
+  uint32_t* status;            // [4]: code, blockIdx, detail, detail2
+  uint64_t timeout_ns;
+};
+
+// Launch on `stream`.  Tensor maps must describe A and B with 128-byte swizzle and boxes
+// {64, kBM} / {64, kBN} (K-major) or {64, kBK} (MN-major).
+cudaError_t launch_sm100_gemm(const CUtensorMap& tma_a, const CUtensorMap& tma_b,
+                              const GemmArgs& args, int grid, cudaStream_t stream);
+
+// Builds a 2-D bf16 tensor map with 128-byte swizzle.  `inner` is the contiguous extent,
+// `outer` the number of rows, `pitch_bytes` the row pitch.  Returns 0 on success.
+int make_tensor_map_2d(CUtensorMap* map, const void* base, uint64_t inner, uint64_t outer,
+                       uint64_t pitch_bytes, uint32_t box_inner, uint32_t box_outer);
+
+size_t sm100_gemm_smem_bytes();
+
+}  // namespace msb

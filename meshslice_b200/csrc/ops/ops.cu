@@ -1,0 +1,597 @@
+// Memory-bound kernels of the GPT block: LayerNorm (+ residual) over column-sharded features,
+// GeLU, AdamW, vocab-parallel cross-entropy, embedding, gradient norm.  All of them stream
+// 16-byte vectors (8 bf16) and keep statistics in fp32.
+#include "ops.h"
+
+#include <cuda_bf16.h>
+
+namespace msb {
+
+namespace {
+
+constexpr int kLnThreads = 256;
+
+__device__ __forceinline__ float bf_lo(uint32_t v) { return __uint_as_float(v << 16); }
+__device__ __forceinline__ float bf_hi(uint32_t v) { return __uint_as_float(v & 0xffff0000u); }
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+__device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {
+  f[0] = bf_lo(u.x); f[1] = bf_hi(u.x); f[2] = bf_lo(u.y); f[3] = bf_hi(u.y);
+  f[4] = bf_lo(u.z); f[5] = bf_hi(u.z); f[6] = bf_lo(u.w); f[7] = bf_hi(u.w);
+}
+__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
+  uint4 u;
+  u.x = pack2(f[0], f[1]); u.y = pack2(f[2], f[3]); u.z = pack2(f[4], f[5]); u.w = pack2(f[6], f[7]);
+  return u;
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+// Sum of two values over the CTA; every thread gets the result.  `red` holds 2 * 32 floats.
+__device__ __forceinline__ void block_sum2(float& a, float& b, float* red) {
+  a = warp_sum(a);
+  b = warp_sum(b);
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31, nw = blockDim.x >> 5;
+  __syncthreads();
+  if (l == 0) { red[w] = a; red[32 + w] = b; }
+  __syncthreads();
+  a = l < nw ? red[l] : 0.f;
+  b = l < nw ? red[32 + l] : 0.f;
+  a = warp_sum(a);
+  b = warp_sum(b);
+}
+__device__ __forceinline__ float block_max(float a, float* red) {
+  a = warp_max(a);
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31, nw = blockDim.x >> 5;
+  __syncthreads();
+  if (l == 0) red[w] = a;
+  __syncthreads();
+  a = l < nw ? red[l] : -INFINITY;
+  return warp_max(a);
+}
+
+__device__ __forceinline__ float gelu_f(float x) {
+  const float k0 = 0.7978845608028654f, k1 = 0.044715f;
+  return 0.5f * x * (1.0f + tanhf(k0 * (x + k1 * x * x * x)));
+}
+__device__ __forceinline__ float gelu_grad_f(float x) {
+  const float k0 = 0.7978845608028654f, k1 = 0.044715f;
+  const float u = k0 * (x + k1 * x * x * x);
+  const float t = tanhf(u);
+  const float du = k0 * (1.0f + 3.0f * k1 * x * x);
+  return 0.5f * (1.0f + t) + 0.5f * x * (1.0f - t * t) * du;
+}
+
+// ------------------------------------------------------------------------------------------
+// LayerNorm forward.  One CTA per row (grid-stride), row cached in registers.
+// ------------------------------------------------------------------------------------------
+template <int MAXV>
+__global__ void __launch_bounds__(kLnThreads)
+ln_fwd_kernel(int mode, const uint4* __restrict__ x, const uint4* __restrict__ res,
+              uint4* __restrict__ h_out, uint4* __restrict__ y, const uint4* __restrict__ gamma,
+              const uint4* __restrict__ beta, float* __restrict__ stats,
+              float* __restrict__ mean_rstd, int rows, int cols, int total_cols, float eps) {
+  __shared__ float red[64];
+  const int nvec = cols >> 3;
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    float vals[MAXV][8];
+    float s = 0.f, ss = 0.f;
+    const int64_t base = (int64_t)row * nvec;
+#pragma unroll
+    for (int k = 0; k < MAXV; ++k) {
+      const int v = threadIdx.x + k * kLnThreads;
+      if (v < nvec) {
+        unpack8(x[base + v], vals[k]);
+        if (mode != 2 && res != nullptr) {
+          float r[8];
+          unpack8(res[base + v], r);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) vals[k][i] += r[i];
+        }
+        if (mode != 2 && h_out != nullptr) {
+          const uint4 hp = pack8(vals[k]);
+          h_out[base + v] = hp;
+          unpack8(hp, vals[k]);  // statistics of the rounded values the backward pass sees
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) { s += vals[k][i]; ss += vals[k][i] * vals[k][i]; }
+      }
+    }
+    float mean, rstd;
+    if (mode == 2) {
+      s = stats[2 * row];
+      ss = stats[2 * row + 1];
+    } else {
+      block_sum2(s, ss, red);
+      if (mode == 1) {
+        if (threadIdx.x == 0) { stats[2 * row] = s; stats[2 * row + 1] = ss; }
+        continue;
+      }
+    }
+    mean = s / (float)total_cols;
+    rstd = rsqrtf(fmaxf(ss / (float)total_cols - mean * mean, 0.f) + eps);
+    if (threadIdx.x == 0 && mean_rstd != nullptr) {
+      mean_rstd[2 * row] = mean;
+      mean_rstd[2 * row + 1] = rstd;
+    }
+#pragma unroll
+    for (int k = 0; k < MAXV; ++k) {
+      const int v = threadIdx.x + k * kLnThreads;
+      if (v < nvec) {
+        float g[8], b[8], o[8];
+        if (gamma != nullptr) unpack8(gamma[v], g);
+        if (beta != nullptr) unpack8(beta[v], b);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          float t = (vals[k][i] - mean) * rstd;
+          if (gamma != nullptr) t *= g[i];
+          if (beta != nullptr) t += b[i];
+          o[i] = t;
+        }
+        y[base + v] = pack8(o);
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// LayerNorm backward
+// ------------------------------------------------------------------------------------------
+template <int MAXV>
+__global__ void __launch_bounds__(kLnThreads)
+ln_bwd_kernel(int mode, const uint4* __restrict__ dy, const uint4* __restrict__ h,
+              const uint4* __restrict__ gamma, const float* __restrict__ mean_rstd,
+              const uint4* __restrict__ dres, uint4* __restrict__ dx, float* __restrict__ stats,
+              float* __restrict__ dgamma, float* __restrict__ dbeta, int rows, int cols,
+              int total_cols) {
+  __shared__ float red[64];
+  const int nvec = cols >> 3;
+  float accg[MAXV][8], accb[MAXV][8];
+#pragma unroll
+  for (int k = 0; k < MAXV; ++k)
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { accg[k][i] = 0.f; accb[k][i] = 0.f; }
+  const bool want_param_grads = mode != 2 && dgamma != nullptr;
+
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    const float mean = mean_rstd[2 * row], rstd = mean_rstd[2 * row + 1];
+    const int64_t base = (int64_t)row * nvec;
+    float g[MAXV][8], xh[MAXV][8];
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int k = 0; k < MAXV; ++k) {
+      const int v = threadIdx.x + k * kLnThreads;
+      if (v < nvec) {
+        float d[8], hv[8], gm[8];
+        unpack8(dy[base + v], d);
+        unpack8(h[base + v], hv);
+        if (gamma != nullptr) unpack8(gamma[v], gm);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          xh[k][i] = (hv[i] - mean) * rstd;
+          g[k][i] = gamma != nullptr ? d[i] * gm[i] : d[i];
+          s1 += g[k][i];
+          s2 += g[k][i] * xh[k][i];
+          if (want_param_grads) { accg[k][i] += d[i] * xh[k][i]; accb[k][i] += d[i]; }
+        }
+      }
+    }
+    if (mode == 2) {
+      s1 = stats[2 * row];
+      s2 = stats[2 * row + 1];
+    } else {
+      block_sum2(s1, s2, red);
+      if (mode == 1) {
+        if (threadIdx.x == 0) { stats[2 * row] = s1; stats[2 * row + 1] = s2; }
+        continue;
+      }
+    }
+    const float m1 = s1 / (float)total_cols, m2 = s2 / (float)total_cols;
+#pragma unroll
+    for (int k = 0; k < MAXV; ++k) {
+      const int v = threadIdx.x + k * kLnThreads;
+      if (v < nvec) {
+        float o[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o[i] = rstd * (g[k][i] - m1 - xh[k][i] * m2);
+        if (dres != nullptr) {
+          float r[8];
+          unpack8(dres[base + v], r);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) o[i] += r[i];
+        }
+        dx[base + v] = pack8(o);
+      }
+    }
+  }
+  if (want_param_grads) {
+#pragma unroll
+    for (int k = 0; k < MAXV; ++k) {
+      const int v = threadIdx.x + k * kLnThreads;
+      if (v < nvec) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          atomicAdd(dgamma + v * 8 + i, accg[k][i]);
+          if (dbeta != nullptr) atomicAdd(dbeta + v * 8 + i, accb[k][i]);
+        }
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// elementwise
+// ------------------------------------------------------------------------------------------
+__global__ void gelu_fwd_kernel(const uint4* __restrict__ x, uint4* __restrict__ y, int64_t nvec) {
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < nvec;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    float f[8];
+    unpack8(x[i], f);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) f[k] = gelu_f(f[k]);
+    y[i] = pack8(f);
+  }
+}
+__global__ void gelu_bwd_kernel(const uint4* __restrict__ dy, const uint4* __restrict__ x,
+                                uint4* __restrict__ dx, int64_t nvec) {
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < nvec;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    float f[8], d[8];
+    unpack8(x[i], f);
+    unpack8(dy[i], d);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) d[k] *= gelu_grad_f(f[k]);
+    dx[i] = pack8(d);
+  }
+}
+__global__ void add_kernel(const uint4* __restrict__ a, const uint4* __restrict__ b,
+                           uint4* __restrict__ o, int64_t nvec) {
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < nvec;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    float f[8], g[8];
+    unpack8(a[i], f);
+    unpack8(b[i], g);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) f[k] += g[k];
+    o[i] = pack8(f);
+  }
+}
+__global__ void cast_kernel(const float4* __restrict__ in, uint2* __restrict__ out, int64_t nvec,
+                            int accumulate) {
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < nvec;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    float4 f = in[i];
+    if (accumulate) {
+      const uint2 c = out[i];
+      f.x += bf_lo(c.x); f.y += bf_hi(c.x); f.z += bf_lo(c.y); f.w += bf_hi(c.y);
+    }
+    uint2 o;
+    o.x = pack2(f.x, f.y);
+    o.y = pack2(f.z, f.w);
+    out[i] = o;
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// AdamW: 4 elements per thread
+// ------------------------------------------------------------------------------------------
+__global__ void adamw_kernel(uint2* __restrict__ param, float4* __restrict__ master,
+                             float4* __restrict__ m, float4* __restrict__ v,
+                             const void* __restrict__ grad, int grad_fp32, int64_t nvec, float lr,
+                             float beta1, float beta2, float eps, float wd, float bc1, float bc2,
+                             const float* __restrict__ grad_scale) {
+  const float gs = grad_scale != nullptr ? *grad_scale : 1.0f;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < nvec;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    float g[4];
+    if (grad_fp32) {
+      const float4 gg = reinterpret_cast<const float4*>(grad)[i];
+      g[0] = gg.x; g[1] = gg.y; g[2] = gg.z; g[3] = gg.w;
+    } else {
+      const uint2 gg = reinterpret_cast<const uint2*>(grad)[i];
+      g[0] = bf_lo(gg.x); g[1] = bf_hi(gg.x); g[2] = bf_lo(gg.y); g[3] = bf_hi(gg.y);
+    }
+    float4 p4 = master[i], m4 = m[i], v4 = v[i];
+    float p[4] = {p4.x, p4.y, p4.z, p4.w};
+    float mm[4] = {m4.x, m4.y, m4.z, m4.w};
+    float vv[4] = {v4.x, v4.y, v4.z, v4.w};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float gk = g[k] * gs;
+      mm[k] = beta1 * mm[k] + (1.f - beta1) * gk;
+      vv[k] = beta2 * vv[k] + (1.f - beta2) * gk * gk;
+      const float mh = mm[k] / bc1, vh = vv[k] / bc2;
+      p[k] = p[k] - lr * (mh / (sqrtf(vh) + eps) + wd * p[k]);
+    }
+    master[i] = make_float4(p[0], p[1], p[2], p[3]);
+    m[i] = make_float4(mm[0], mm[1], mm[2], mm[3]);
+    v[i] = make_float4(vv[0], vv[1], vv[2], vv[3]);
+    uint2 o;
+    o.x = pack2(p[0], p[1]);
+    o.y = pack2(p[2], p[3]);
+    param[i] = o;
+  }
+}
+
+__global__ void sumsq_kernel(const void* __restrict__ x, int is_fp32, int64_t nvec,
+                             float* __restrict__ out) {
+  __shared__ float red[64];
+  float s = 0.f, dummy = 0.f;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < nvec;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    if (is_fp32) {
+      const float4 g = reinterpret_cast<const float4*>(x)[i];
+      s += g.x * g.x + g.y * g.y + g.z * g.z + g.w * g.w;
+    } else {
+      const uint2 g = reinterpret_cast<const uint2*>(x)[i];
+      const float a = bf_lo(g.x), b = bf_hi(g.x), c = bf_lo(g.y), d = bf_hi(g.y);
+      s += a * a + b * b + c * c + d * d;
+    }
+  }
+  block_sum2(s, dummy, red);
+  if (threadIdx.x == 0) atomicAdd(out, s);
+}
+
+// ------------------------------------------------------------------------------------------
+// vocab-parallel cross-entropy: one CTA per row
+// ------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+ce_partial_kernel(const __nv_bfloat16* __restrict__ logits, int64_t ld,
+                  const int64_t* __restrict__ targets, int rows, int cols, int col_offset,
+                  int vocab, float* __restrict__ row_max, float* __restrict__ row_sumexp,
+                  float* __restrict__ tgt_logit) {
+  __shared__ float red[64];
+  const int valid = max(0, min(cols, vocab - col_offset));
+  const int nvec = valid >> 3;
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    const __nv_bfloat16* p = logits + (int64_t)row * ld;
+    const uint4* pv = reinterpret_cast<const uint4*>(p);
+    float mx = -INFINITY;
+    for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
+      float f[8];
+      unpack8(pv[v], f);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) mx = fmaxf(mx, f[i]);
+    }
+    for (int c = nvec * 8 + threadIdx.x; c < valid; c += blockDim.x)
+      mx = fmaxf(mx, __bfloat162float(p[c]));
+    mx = block_max(mx, red);
+    float s = 0.f, dummy = 0.f;
+    if (valid > 0) {
+      for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
+        float f[8];
+        unpack8(pv[v], f);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) s += __expf(f[i] - mx);
+      }
+      for (int c = nvec * 8 + threadIdx.x; c < valid; c += blockDim.x)
+        s += __expf(__bfloat162float(p[c]) - mx);
+    }
+    block_sum2(s, dummy, red);
+    if (threadIdx.x == 0) {
+      row_max[row] = mx;
+      row_sumexp[row] = s;
+      const int64_t t = targets[row] - col_offset;
+      tgt_logit[row] = (t >= 0 && t < valid) ? __bfloat162float(p[t]) : 0.f;
+    }
+  }
+}
+
+__global__ void __launch_bounds__(256)
+ce_grad_kernel(__nv_bfloat16* __restrict__ logits, int64_t ld, const int64_t* __restrict__ targets,
+               int rows, int cols, int col_offset, int vocab, const float* __restrict__ gmax,
+               const float* __restrict__ gsumexp, float scale) {
+  const int nvec = cols >> 3;
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    __nv_bfloat16* p = logits + (int64_t)row * ld;
+    uint4* pv = reinterpret_cast<uint4*>(p);
+    const float mx = gmax[row], inv = scale / gsumexp[row];
+    const int64_t t = targets[row] - col_offset;
+    for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
+      float f[8];
+      unpack8(pv[v], f);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int c = v * 8 + i;
+        float gsm = (c + col_offset < vocab) ? __expf(f[i] - mx) * inv : 0.f;
+        if (c == t) gsm -= scale;
+        f[i] = gsm;
+      }
+      pv[v] = pack8(f);
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// embedding
+// ------------------------------------------------------------------------------------------
+__global__ void embedding_fwd_kernel(const int64_t* __restrict__ tokens,
+                                     const uint4* __restrict__ tok_table,
+                                     const uint4* __restrict__ pos_table, uint4* __restrict__ out,
+                                     int n_tokens, int seq, int nvec) {
+  for (int t = blockIdx.x; t < n_tokens; t += gridDim.x) {
+    const int64_t tok = tokens[t];
+    const int pos = t % seq;
+    for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
+      float a[8], b[8];
+      unpack8(tok_table[tok * nvec + v], a);
+      unpack8(pos_table[(int64_t)pos * nvec + v], b);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) a[i] += b[i];
+      out[(int64_t)t * nvec + v] = pack8(a);
+    }
+  }
+}
+// token table: scatter-add with fp32 vector atomics; position table: plain sum over the batch
+__global__ void embedding_bwd_tok_kernel(const int64_t* __restrict__ tokens,
+                                         const uint4* __restrict__ dout, float* __restrict__ dtok,
+                                         int n_tokens, int nvec) {
+  for (int t = blockIdx.x; t < n_tokens; t += gridDim.x) {
+    const int64_t tok = tokens[t];
+    for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
+      float a[8];
+      unpack8(dout[(int64_t)t * nvec + v], a);
+      float4* dst = reinterpret_cast<float4*>(dtok + (tok * nvec + v) * 8);
+      atomicAdd(dst, make_float4(a[0], a[1], a[2], a[3]));
+      atomicAdd(dst + 1, make_float4(a[4], a[5], a[6], a[7]));
+    }
+  }
+}
+__global__ void embedding_bwd_pos_kernel(const uint4* __restrict__ dout, float* __restrict__ dpos,
+                                         int n_tokens, int seq, int nvec) {
+  const int64_t total = (int64_t)seq * nvec;
+  const int nb = n_tokens / seq;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t pos = i / nvec, v = i - pos * nvec;
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (int b = 0; b < nb; ++b) {
+      float a[8];
+      unpack8(dout[((int64_t)b * seq + pos) * nvec + v], a);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) acc[k] += a[k];
+    }
+    float* dst = dpos + i * 8;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) dst[k] += acc[k];
+  }
+}
+
+inline int grid_for(int64_t n, int threads, int cap = 148 * 16) {
+  int64_t g = (n + threads - 1) / threads;
+  if (g > cap) g = cap;
+  if (g < 1) g = 1;
+  return (int)g;
+}
+
+}  // namespace
+
+// ------------------------------------------------------------------------------------------
+// launchers
+// ------------------------------------------------------------------------------------------
+cudaError_t ln_fwd(int mode, const void* x, const void* res, void* h_out, void* y,
+                   const void* gamma, const void* beta, float* stats, float* mean_rstd, int rows,
+                   int cols, int total_cols, float eps, cudaStream_t stream) {
+  if (cols % 8 != 0 || cols > 8 * kLnThreads * 8) return cudaErrorInvalidValue;
+  const int grid = rows < 148 * 8 ? rows : 148 * 8;
+  auto X = reinterpret_cast<const uint4*>(x);
+  auto R = reinterpret_cast<const uint4*>(res);
+  auto H = reinterpret_cast<uint4*>(h_out);
+  auto Y = reinterpret_cast<uint4*>(y);
+  auto G = reinterpret_cast<const uint4*>(gamma);
+  auto B = reinterpret_cast<const uint4*>(beta);
+  const int nvec_per_thread = (cols / 8 + kLnThreads - 1) / kLnThreads;
+  if (nvec_per_thread <= 2)
+    ln_fwd_kernel<2><<<grid, kLnThreads, 0, stream>>>(mode, X, R, H, Y, G, B, stats, mean_rstd, rows, cols, total_cols, eps);
+  else if (nvec_per_thread <= 4)
+    ln_fwd_kernel<4><<<grid, kLnThreads, 0, stream>>>(mode, X, R, H, Y, G, B, stats, mean_rstd, rows, cols, total_cols, eps);
+  else
+    ln_fwd_kernel<8><<<grid, kLnThreads, 0, stream>>>(mode, X, R, H, Y, G, B, stats, mean_rstd, rows, cols, total_cols, eps);
+  return cudaGetLastError();
+}
+
+cudaError_t ln_bwd(int mode, const void* dy, const void* h, const void* gamma,
+                   const float* mean_rstd, const void* dres, void* dx, float* stats, float* dgamma,
+                   float* dbeta, int rows, int cols, int total_cols, cudaStream_t stream) {
+  if (cols % 8 != 0 || cols > 8 * kLnThreads * 8) return cudaErrorInvalidValue;
+  const int grid = rows < 148 * 4 ? rows : 148 * 4;
+  auto DY = reinterpret_cast<const uint4*>(dy);
+  auto H = reinterpret_cast<const uint4*>(h);
+  auto G = reinterpret_cast<const uint4*>(gamma);
+  auto DR = reinterpret_cast<const uint4*>(dres);
+  auto DX = reinterpret_cast<uint4*>(dx);
+  const int nvec_per_thread = (cols / 8 + kLnThreads - 1) / kLnThreads;
+  if (nvec_per_thread <= 2)
+    ln_bwd_kernel<2><<<grid, kLnThreads, 0, stream>>>(mode, DY, H, G, mean_rstd, DR, DX, stats, dgamma, dbeta, rows, cols, total_cols);
+  else if (nvec_per_thread <= 4)
+    ln_bwd_kernel<4><<<grid, kLnThreads, 0, stream>>>(mode, DY, H, G, mean_rstd, DR, DX, stats, dgamma, dbeta, rows, cols, total_cols);
+  else
+    ln_bwd_kernel<8><<<grid, kLnThreads, 0, stream>>>(mode, DY, H, G, mean_rstd, DR, DX, stats, dgamma, dbeta, rows, cols, total_cols);
+  return cudaGetLastError();
+}
+
+cudaError_t gelu_fwd(const void* x, void* y, int64_t n, cudaStream_t stream) {
+  if (n % 8) return cudaErrorInvalidValue;
+  gelu_fwd_kernel<<<grid_for(n / 8, 256), 256, 0, stream>>>(reinterpret_cast<const uint4*>(x), reinterpret_cast<uint4*>(y), n / 8);
+  return cudaGetLastError();
+}
+cudaError_t gelu_bwd(const void* dy, const void* x, void* dx, int64_t n, cudaStream_t stream) {
+  if (n % 8) return cudaErrorInvalidValue;
+  gelu_bwd_kernel<<<grid_for(n / 8, 256), 256, 0, stream>>>(reinterpret_cast<const uint4*>(dy), reinterpret_cast<const uint4*>(x), reinterpret_cast<uint4*>(dx), n / 8);
+  return cudaGetLastError();
+}
+cudaError_t add_bf16(const void* a, const void* b, void* out, int64_t n, cudaStream_t stream) {
+  if (n % 8) return cudaErrorInvalidValue;
+  add_kernel<<<grid_for(n / 8, 256), 256, 0, stream>>>(reinterpret_cast<const uint4*>(a), reinterpret_cast<const uint4*>(b), reinterpret_cast<uint4*>(out), n / 8);
+  return cudaGetLastError();
+}
+cudaError_t cast_f32_to_bf16(const float* in, void* out, int64_t n, int accumulate, cudaStream_t stream) {
+  if (n % 4) return cudaErrorInvalidValue;
+  cast_kernel<<<grid_for(n / 4, 256), 256, 0, stream>>>(reinterpret_cast<const float4*>(in), reinterpret_cast<uint2*>(out), n / 4, accumulate);
+  return cudaGetLastError();
+}
+
+cudaError_t adamw_step(void* param, float* master, float* m, float* v, const void* grad,
+                       int grad_fp32, int64_t n, float lr, float beta1, float beta2, float eps,
+                       float weight_decay, float bias_corr1, float bias_corr2,
+                       const float* grad_scale, cudaStream_t stream) {
+  if (n % 4) return cudaErrorInvalidValue;
+  adamw_kernel<<<grid_for(n / 4, 256), 256, 0, stream>>>(
+      reinterpret_cast<uint2*>(param), reinterpret_cast<float4*>(master), reinterpret_cast<float4*>(m),
+      reinterpret_cast<float4*>(v), grad, grad_fp32, n / 4, lr, beta1, beta2, eps, weight_decay,
+      bias_corr1, bias_corr2, grad_scale);
+  return cudaGetLastError();
+}
+
+cudaError_t sumsq(const void* x, int is_fp32, int64_t n, float* out, cudaStream_t stream) {
+  if (n % 4) return cudaErrorInvalidValue;
+  sumsq_kernel<<<grid_for(n / 4, 256, 148 * 8), 256, 0, stream>>>(x, is_fp32, n / 4, out);
+  return cudaGetLastError();
+}
+
+cudaError_t ce_partial(const void* logits, int64_t ld, const int64_t* targets, int rows, int cols,
+                       int col_offset, int vocab, float* row_max, float* row_sumexp,
+                       float* tgt_logit, cudaStream_t stream) {
+  if (ld % 8) return cudaErrorInvalidValue;
+  const int grid = rows < 148 * 8 ? rows : 148 * 8;
+  ce_partial_kernel<<<grid, 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(logits), ld, targets, rows, cols, col_offset, vocab, row_max, row_sumexp, tgt_logit);
+  return cudaGetLastError();
+}
+cudaError_t ce_grad(void* logits, int64_t ld, const int64_t* targets, int rows, int cols,
+                    int col_offset, int vocab, const float* gmax, const float* gsumexp, float scale,
+                    cudaStream_t stream) {
+  if (ld % 8 || cols % 8) return cudaErrorInvalidValue;
+  const int grid = rows < 148 * 8 ? rows : 148 * 8;
+  ce_grad_kernel<<<grid, 256, 0, stream>>>(reinterpret_cast<__nv_bfloat16*>(logits), ld, targets, rows, cols, col_offset, vocab, gmax, gsumexp, scale);
+  return cudaGetLastError();
+}
+
+cudaError_t embedding_fwd(const int64_t* tokens, const void* tok_table, const void* pos_table,
+                          void* out, int n_tokens, int seq, int cols, cudaStream_t stream) {
+  if (cols % 8) return cudaErrorInvalidValue;
+  const int grid = n_tokens < 148 * 16 ? n_tokens : 148 * 16;
+  embedding_fwd_kernel<<<grid, 128, 0, stream>>>(tokens, reinterpret_cast<const uint4*>(tok_table), reinterpret_cast<const uint4*>(pos_table), reinterpret_cast<uint4*>(out), n_tokens, seq, cols / 8);
+  return cudaGetLastError();
+}
+cudaError_t embedding_bwd(const int64_t* tokens, const void* dout, float* dtok, float* dpos,
+                          int n_tokens, int seq, int cols, cudaStream_t stream) {
+  if (cols % 8 || n_tokens % seq) return cudaErrorInvalidValue;
+  const int grid = n_tokens < 148 * 16 ? n_tokens : 148 * 16;
+  embedding_bwd_tok_kernel<<<grid, 128, 0, stream>>>(tokens, reinterpret_cast<const uint4*>(dout), dtok, n_tokens, cols / 8);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return e;
+  embedding_bwd_pos_kernel<<<grid_for((int64_t)seq * (cols / 8), 256), 256, 0, stream>>>(reinterpret_cast<const uint4*>(dout), dpos, n_tokens, seq, cols / 8);
+  return cudaGetLastError();
+}
+
+}  // namespace msb

@@ -1,0 +1,76 @@
+// C++ launchers of the non-GEMM kernels (LayerNorm over column-sharded features, GeLU,
+// AdamW, vocab-parallel cross-entropy, embedding, gradient norm).  All tensors are row-major;
+// bf16 activations/parameters, fp32 statistics and optimizer state.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace msb {
+
+// ---- LayerNorm over a feature dimension that may be split across the mesh columns --------
+// Replaces ShardedLayerNorm (ShardedLayers.py:123-138) plus the residual adds (:178,:184);
+// unlike the reference the affine parameters are applied.
+// mode 0: single GPU holds the whole feature dim: h = x (+ res); y = LN(h)*gamma + beta
+// mode 1: first pass of the sharded case: h = x (+ res); stats[row] = (sum h, sum h^2)
+// mode 2: second pass: y from h and the all-reduced stats
+// `h_out` may alias x; `res` and `h_out` may be null (no residual add: h == x).
+// mean_rstd receives (mean, rstd) per row (modes 0 and 2).
+cudaError_t ln_fwd(int mode, const void* x, const void* res, void* h_out, void* y,
+                   const void* gamma, const void* beta, float* stats, float* mean_rstd,
+                   int rows, int cols, int total_cols, float eps, cudaStream_t stream);
+
+// Backward.  g = dy * gamma, xhat = (h - mean) * rstd.
+// mode 0: everything local: dx = rstd * (g - mean_D(g) - xhat * mean_D(g * xhat)) (+ dres)
+// mode 1: stats[row] = (sum g, sum g * xhat) over the local columns; also accumulates
+//         dgamma / dbeta (fp32, atomically, must be zeroed by the caller)
+// mode 2: dx from the all-reduced stats
+// mode 0 accumulates dgamma / dbeta as mode 1 does.
+cudaError_t ln_bwd(int mode, const void* dy, const void* h, const void* gamma,
+                   const float* mean_rstd, const void* dres, void* dx, float* stats,
+                   float* dgamma, float* dbeta, int rows, int cols, int total_cols,
+                   cudaStream_t stream);
+
+// ---- GeLU (tanh approximation, the jax.nn.gelu default used at ShardedLayers.py:182) -----
+cudaError_t gelu_fwd(const void* x, void* y, int64_t n, cudaStream_t stream);
+cudaError_t gelu_bwd(const void* dy, const void* x, void* dx, int64_t n, cudaStream_t stream);
+
+// ---- elementwise add (bf16): out = a + b -------------------------------------------------
+cudaError_t add_bf16(const void* a, const void* b, void* out, int64_t n, cudaStream_t stream);
+
+// ---- AdamW over flat buffers -------------------------------------------------------------
+// param (bf16) and master/m/v (fp32) are updated in place from grad (bf16 or fp32).
+// grad_scale multiplies the gradient first (loss scaling / clipping).
+cudaError_t adamw_step(void* param, float* master, float* m, float* v, const void* grad,
+                       int grad_fp32, int64_t n, float lr, float beta1, float beta2, float eps,
+                       float weight_decay, float bias_corr1, float bias_corr2,
+                       const float* grad_scale, cudaStream_t stream);
+
+// out[0] += sum of squares of x (bf16 or fp32), fp32 atomics.
+cudaError_t sumsq(const void* x, int is_fp32, int64_t n, float* out, cudaStream_t stream);
+
+// ---- vocab-parallel softmax cross-entropy -------------------------------------------------
+// logits: bf16 [rows, cols] = this GPU's vocabulary slice [col_offset, col_offset + cols);
+// columns with global index >= vocab are padding and ignored.
+// pass 1: row_max[row], row_sumexp[row] (relative to row_max), tgt_logit[row] (0 if the
+//         target is not in this slice)
+cudaError_t ce_partial(const void* logits, int64_t ld, const int64_t* targets, int rows, int cols,
+                       int col_offset, int vocab, float* row_max, float* row_sumexp,
+                       float* tgt_logit, cudaStream_t stream);
+// pass 2: logits <- (softmax - onehot) * scale, in place, using the global max / sumexp.
+cudaError_t ce_grad(void* logits, int64_t ld, const int64_t* targets, int rows, int cols,
+                    int col_offset, int vocab, const float* gmax, const float* gsumexp,
+                    float scale, cudaStream_t stream);
+
+// ---- embedding ----------------------------------------------------------------------------
+// out[t, :] = tok_table[token[t], :] + pos_table[t % seq, :]   (tables bf16 [*, cols])
+cudaError_t embedding_fwd(const int64_t* tokens, const void* tok_table, const void* pos_table,
+                          void* out, int n_tokens, int seq, int cols, cudaStream_t stream);
+// dtok[token[t], :] += dout[t, :]; dpos[t % seq, :] += dout[t, :]   (fp32 accumulators)
+cudaError_t embedding_bwd(const int64_t* tokens, const void* dout, float* dtok, float* dpos,
+                          int n_tokens, int seq, int cols, cudaStream_t stream);
+
+// out(bf16)[i] = (accumulate ? out[i] : 0) + in(fp32)[i]
+cudaError_t cast_f32_to_bf16(const float* in, void* out, int64_t n, int accumulate,
+                             cudaStream_t stream);
+
+}  // namespace msb

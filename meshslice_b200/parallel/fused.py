@@ -1,0 +1,269 @@
+"""Launch descriptions of the three fused MeshSlice dataflows on the tcgen05 GEMM kernel.
+
+Global view used here (equivalent to the per-shard formulation of TensorParallel.py:153-214):
+
+  OS   Y[m, n]   = X_g[m, :] @ W_g[:, n]    X_g = all-gather of X over the mesh row (concat on k),
+                                            W_g = all-gather of W over the mesh column (concat on k)
+  LS   Yp[m, :]  = X[m, :] @ W_g[:, :]^T    W_g = all-gather of W over the mesh column (concat on n),
+                                            Y = reduce-scatter of Yp over the mesh row (split on n)
+  RS   Yp[:, n]  = X_g[:, :]^T @ W[:, n]    X_g = all-gather of X over the mesh row (concat on m),
+                                            Y = reduce-scatter of Yp over the mesh column (split on m)
+
+"Mesh row" = the C devices that share a row index; "mesh column" = the R devices that share a
+column index.  The slice count orders the work block-cyclically along the dimension whose data
+moves (m for OS, n for LS, m for RS): slice s is gathered / pushed while slice s-1 is in the
+tensor cores, and its flag is what the TMA producer of a tile waits for.  The result does not
+depend on the slice count.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import List
+
+import torch
+
+from .. import _native
+from . import runtime as rt
+
+BM, BN = 128, 256
+
+
+@dataclass
+class MeshCoord:
+    R: int
+    C: int
+    r: int
+    c: int
+
+    @property
+    def rank(self) -> int:
+        return self.r * self.C + self.c
+
+    def row_peers(self) -> List[int]:
+        """Ranks of the mesh row (same r), indexed by column."""
+        return [self.r * self.C + cc for cc in range(self.C)]
+
+    def col_peers(self) -> List[int]:
+        """Ranks of the mesh column (same c), indexed by row."""
+        return [rr * self.C + self.c for rr in range(self.R)]
+
+
+class FusedPlanError(ValueError):
+    """The shapes do not meet the divisibility rules of the fused kernel."""
+
+
+def pick_slices(n_blocks_per_part: int, want: int, cyc: int = 1) -> int:
+    """Largest slice count <= want such that slices * cyc divides the blocks of every part."""
+    s = max(1, min(want, n_blocks_per_part // cyc if cyc else 1))
+    while s > 1 and n_blocks_per_part % (s * cyc) != 0:
+        s -= 1
+    return max(s, 1)
+
+
+def _barrier_fields(world: rt.World, ranks: List[int], exit_barrier: bool, grid: int, timeout_ns: int):
+    ws = world.mine
+    n = world.size
+    if n <= 1:
+        return dict(n_ranks=0)
+    epoch = ws.next_epoch()
+    return dict(
+        n_ranks=n, my_rank=world.my_rank,
+        entry_flags=[world.flag_ptr(q, rt.ENTRY0) for q in range(n)],
+        exit_flags=[world.flag_ptr(q, rt.EXIT0) for q in range(n)],
+        epoch=epoch, go_flag=world.flag_ptr(world.my_rank, rt.GO),
+        done_counter=world.flag_ptr(world.my_rank, rt.DONE), done_target=grid,
+        exit_barrier=1 if exit_barrier else 0, timeout_ns=timeout_ns)
+
+
+class FusedGemm:
+    """Builds and launches fused dataflows for one rank.
+
+    ``world`` resolves peers' pointers (runtime.World).  ``x_ptrs`` / ``w_ptrs`` passed to the
+    methods are the device pointers of every peer's shard (own shard included), indexed by the
+    peer's position along the gathered mesh axis.
+    """
+
+    def __init__(self, mesh: MeshCoord, world: rt.World, grid: int, timeout_ns: int = 5_000_000_000,
+                 use_barriers: bool = True):
+        self.mesh = mesh
+        self.world = world
+        self.grid = grid
+        self.timeout_ns = timeout_ns
+        self.use_barriers = use_barriers
+        self.C = _native.load()
+        self._cache = {}
+
+    # ------------------------------------------------------------------ helpers
+    def _reset_flags(self, stream):
+        ws = self.world.mine
+        self.C.memset_zero(ws.local(ws.flags + 4 * rt.RESET0), rt.RESET_BYTES, stream)
+
+    def _common(self, out, accumulate, stream):
+        return dict(C=out.data_ptr(), ldc=out.stride(0), c_fp32=1 if out.dtype == torch.float32 else 0,
+                    accumulate=1 if accumulate else 0, status=_native.status().dev, grid=self.grid,
+                    stream=stream, timeout_ns=self.timeout_ns)
+
+    def _jobs(self, key, builder):
+        if key not in self._cache:
+            jobs, begin = builder()
+            dev = torch.device("cuda", torch.cuda.current_device())
+            self._cache[key] = rt.upload_jobs(jobs, begin, dev) + (len(begin) - 1,)
+        return self._cache[key]
+
+    def _launch(self, d, exit_barrier, phase="all", reset=True):
+        """phase 'gemm' leaves out the reduce phase and 'reduce' runs only it; together with
+        reset=False this lets a test run several emulated ranks one after another on one GPU."""
+        if reset:
+            self._reset_flags(d["stream"])
+        if phase == "gemm":
+            d["red_n"] = 0
+        elif phase == "reduce":
+            d.update(no_tiles=1, n_chunks=0, push_n=0, a_flag_mode=0, b_flag_mode=0)
+        if self.use_barriers:
+            d.update(_barrier_fields(self.world, [], exit_barrier, self.grid, self.timeout_ns))
+        self.C.gemm_run(d)
+
+    # ------------------------------------------------------------------ OS
+    def os(self, x_ptrs: List[int], w_ptrs: List[int], m: int, kl: int, kr: int, n: int, out,
+           n_slices: int = 4, accumulate: bool = False, bias=None, act=None, pre_act=None):
+        """Y[m, n] = concat_c(X_c)[m, C*kl] @ concat_r(W_r)[R*kr, n];  C*kl == R*kr."""
+        mc, ws = self.mesh, self.world.mine
+        Kd = mc.C * kl
+        if Kd != mc.R * kr:
+            raise FusedPlanError("OS: contraction sizes of X and W shards disagree")
+        if kl % 8 or n % 8 or m * Kd * 2 > ws.stage_a_bytes or Kd * n * 2 > ws.stage_b_bytes:
+            raise FusedPlanError("OS: shard does not fit the staging buffers / alignment")
+        tiles_m = (m + BM - 1) // BM
+        S = pick_slices(tiles_m, n_slices)
+        stream = _native.stream_ptr()
+        xg, wg = ws.local(ws.stage_a), ws.local(ws.stage_b)
+
+        def build():
+            jobs, begin = [], [0]
+            for r in range(mc.R):  # chunk 0: the whole gathered W
+                jobs.append((w_ptrs[r], wg + r * kr * n * 2, kr, n * 2, n * 2, n * 2))
+            begin.append(len(jobs))
+            for s in range(S):     # chunks 1..S: row blocks of X, block-cyclic
+                for blk in range(s, tiles_m, S):
+                    row0 = blk * BM
+                    rows = min(BM, m - row0)
+                    for c in range(mc.C):
+                        jobs.append((x_ptrs[c] + row0 * kl * 2, xg + row0 * Kd * 2 + c * kl * 2, rows,
+                                     kl * 2, kl * 2, Kd * 2))
+                begin.append(len(jobs))
+            return jobs, begin
+
+        jt, bt, n_chunks = self._jobs(("os", tuple(x_ptrs), tuple(w_ptrs), m, kl, kr, n, S), build)
+        d = self._common(out, accumulate, stream)
+        d.update(M=m, N=n, K=Kd, A=xg, B=wg, lda=Kd, ldb=n, a_mn_major=0, b_mn_major=1,
+                 slice_dim=0, n_slices=S, cyc=1, group=8,
+                 jobs=jt.data_ptr(), chunk_job_begin=bt.data_ptr(), n_chunks=n_chunks,
+                 chunk_flags=ws.local(ws.flags + 4 * rt.CHUNK0), chunk_target=self.grid,
+                 a_flag_mode=1, a_flag_base=1, b_flag_mode=2, b_flag_base=0, b_flag_count=1)
+        if bias is not None:
+            d["bias"] = bias.data_ptr()
+        if act == "gelu":
+            d["act"] = 1
+            if pre_act is not None:
+                d["C_pre"] = pre_act.data_ptr()
+        self._launch(d, exit_barrier=True)
+        return out
+
+    # ------------------------------------------------------------------ LS
+    def ls(self, x, w_ptrs: List[int], m: int, kl: int, nr: int, out, n_slices: int = 4,
+           accumulate: bool = False, phase: str = "all", reset: bool = True):
+        """Y[m, N/C] = reduce-scatter over the mesh row of  X[m, kl] @ concat_r(W_r)[R*nr, kl]^T."""
+        mc, ws = self.mesh, self.world.mine
+        N = mc.R * nr
+        if N % mc.C:
+            raise FusedPlanError("LS: output width not divisible by the mesh columns")
+        nc = N // mc.C
+        if nr % BN or nc % BN or m % BM or kl % 8:
+            raise FusedPlanError("LS: shard sizes must be multiples of the 128x256 tile")
+        if N * kl * 2 > ws.stage_b_bytes or mc.C * m * nc * 2 > ws.slot_bytes:
+            raise FusedPlanError("LS: staging / slot buffers too small")
+        blocks_src, blocks_own = nr // BN, nc // BN
+        import math
+        S = pick_slices(math.gcd(blocks_src, blocks_own), n_slices)
+        tiles_n, tiles_m = N // BN, m // BM
+        stream = _native.stream_ptr()
+        wg = ws.local(ws.stage_b)
+
+        def build():
+            jobs, begin = [], [0]
+            for s in range(S):
+                for blk in range(s, tiles_n, S):
+                    row0 = blk * BN
+                    r = row0 // nr
+                    jobs.append((w_ptrs[r] + (row0 - r * nr) * kl * 2, wg + row0 * kl * 2, BN, kl * 2,
+                                 kl * 2, kl * 2))
+                begin.append(len(jobs))
+            return jobs, begin
+
+        jt, bt, n_chunks = self._jobs(("ls", tuple(w_ptrs), m, kl, nr, S), build)
+        peers = mc.row_peers()  # owners of the output column blocks, indexed by column
+        d = self._common(out, accumulate, stream)
+        d.update(M=m, N=N, K=kl, A=x.data_ptr(), B=wg, lda=x.stride(0), ldb=kl, a_mn_major=0,
+                 b_mn_major=0, slice_dim=1, n_slices=S, cyc=1, group=4,
+                 jobs=jt.data_ptr(), chunk_job_begin=bt.data_ptr(), n_chunks=n_chunks,
+                 chunk_flags=ws.local(ws.flags + 4 * rt.CHUNK0), chunk_target=self.grid,
+                 b_flag_mode=1, b_flag_base=0,
+                 push_n=mc.C, push_dim=1, push_extent=nc, push_ld=nc,
+                 push_base=[self.world.ptr(q, ws.slots) + mc.c * m * nc * 2 for q in peers],
+                 push_counter=[self.world.flag_ptr(q, rt.COUNTER0) for q in peers],
+                 red_n=mc.C, red_slots=ws.local(ws.slots), red_rows=m, red_cols=nc, red_ld=nc,
+                 red_counter=ws.local(ws.flags + 4 * rt.COUNTER0),
+                 red_target=mc.C * (blocks_own // S) * tiles_m * 4, red_slice_dim=1)
+        self._launch(d, exit_barrier=True, phase=phase, reset=reset)
+        return out
+
+    # ------------------------------------------------------------------ RS
+    def rs(self, x_ptrs: List[int], w, kr: int, ml: int, n: int, out, n_slices: int = 4,
+           accumulate: bool = False, cyc: int = 4, phase: str = "all", reset: bool = True):
+        """Y[M/R, n] = reduce-scatter over the mesh column of  concat_c(X_c)[kr, C*ml]^T @ W[kr, n]."""
+        mc, ws = self.mesh, self.world.mine
+        M = mc.C * ml
+        if M % mc.R:
+            raise FusedPlanError("RS: output height not divisible by the mesh rows")
+        mr = M // mc.R
+        if ml % BM or mr % BM or n % BN or kr % 8:
+            raise FusedPlanError("RS: shard sizes must be multiples of the 128x256 tile")
+        if kr * M * 2 > ws.stage_a_bytes or mc.R * mr * n * 2 > ws.slot_bytes:
+            raise FusedPlanError("RS: staging / slot buffers too small")
+        import math
+        g = math.gcd(ml // BM, mr // BM)
+        while cyc > 1 and g % cyc:
+            cyc //= 2
+        S = pick_slices(g, n_slices, cyc)
+        tiles_m, tiles_n = M // BM, n // BN
+        stream = _native.stream_ptr()
+        xg = ws.local(ws.stage_a)
+
+        def build():
+            jobs, begin = [], [0]
+            ngroups = tiles_m // (S * cyc)
+            for s in range(S):
+                for cg in range(ngroups):
+                    col0 = (cg * S + s) * cyc * BM
+                    c = col0 // ml
+                    jobs.append((x_ptrs[c] + (col0 - c * ml) * 2, xg + col0 * 2, kr, cyc * BM * 2,
+                                 ml * 2, M * 2))
+                begin.append(len(jobs))
+            return jobs, begin
+
+        jt, bt, n_chunks = self._jobs(("rs", tuple(x_ptrs), kr, ml, n, S, cyc), build)
+        peers = mc.col_peers()  # owners of the output row blocks, indexed by row
+        d = self._common(out, accumulate, stream)
+        d.update(M=M, N=n, K=kr, A=xg, B=w.data_ptr(), lda=M, ldb=w.stride(0), a_mn_major=1,
+                 b_mn_major=1, slice_dim=0, n_slices=S, cyc=cyc, group=8,
+                 jobs=jt.data_ptr(), chunk_job_begin=bt.data_ptr(), n_chunks=n_chunks,
+                 chunk_flags=ws.local(ws.flags + 4 * rt.CHUNK0), chunk_target=self.grid,
+                 a_flag_mode=1, a_flag_base=0,
+                 push_n=mc.R, push_dim=0, push_extent=mr, push_ld=n,
+                 push_base=[self.world.ptr(q, ws.slots) + mc.r * mr * n * 2 for q in peers],
+                 push_counter=[self.world.flag_ptr(q, rt.COUNTER0) for q in peers],
+                 red_n=mc.R, red_slots=ws.local(ws.slots), red_rows=mr, red_cols=n, red_ld=n,
+                 red_counter=ws.local(ws.flags + 4 * rt.COUNTER0),
+                 red_target=mc.R * ((mr // BM) // S) * tiles_n * 4, red_slice_dim=0)
+        self._launch(d, exit_barrier=True, phase=phase, reset=reset)
+        return out

@@ -1,0 +1,118 @@
+"""Fused pull / push paths of the GEMM kernel on ONE GPU.
+
+Several mesh ranks are emulated one after another: every emulated rank has its own heap and
+workspace on the same device, "peer" pointers point into the other emulated ranks' buffers, and
+the cross-GPU barriers are switched off.  The push dataflows run their GEMM phase for every rank
+first and the reduce phase afterwards, so no launch ever waits for a kernel that is not running.
+"""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _setup(R, C, stage_a, stage_b, slots):
+    from meshslice_b200.parallel import runtime as rt
+    from meshslice_b200.parallel.fused import FusedGemm, MeshCoord
+    from meshslice_b200.ops.gemm import sm_count
+    wss = []
+    for _ in range(R * C):
+        heap = rt.SymmHeap(stage_a + stage_b + slots + (1 << 20))
+        wss.append(rt.Workspace(heap, stage_a, stage_b, slots))
+    ops = {}
+    for r in range(R):
+        for c in range(C):
+            mc = MeshCoord(R, C, r, c)
+            world = rt.World(wss, mc.rank, single_heap=False)
+            ops[(r, c)] = FusedGemm(mc, world, sm_count(), timeout_ns=300_000_000, use_barriers=False)
+    return ops, wss
+
+
+def _close(out, ref, K):
+    err = (out.float() - ref).abs().max().item()
+    assert err < 0.03 * K ** 0.5 + 0.05, err
+    assert ((out.float() - ref).norm() / ref.norm()).item() < 1.5e-2
+
+
+@pytest.mark.parametrize("mesh,slices", [((2, 2), 2), ((1, 4), 1), ((4, 2), 4)])
+def test_os_pull_both_operands(mesh, slices):
+    from meshslice_b200 import _native
+    R, C = mesh
+    M, Kd, N = 512 * R, 1024, 256 * C
+    X = torch.randn(M, Kd, device="cuda").bfloat16()
+    W = torch.randn(Kd, N, device="cuda").bfloat16()
+    m, kl, kr, n = M // R, Kd // C, Kd // R, N // C
+    xs = {(r, c): X[r * m:(r + 1) * m, c * kl:(c + 1) * kl].contiguous() for r in range(R) for c in range(C)}
+    wsd = {(r, c): W[r * kr:(r + 1) * kr, c * n:(c + 1) * n].contiguous() for r in range(R) for c in range(C)}
+    ops, _ = _setup(R, C, m * Kd * 2, Kd * n * 2, 16)
+    ref = X.float() @ W.float()
+    for (r, c), op in ops.items():
+        out = torch.empty(m, n, device="cuda", dtype=torch.bfloat16)
+        op.os([xs[(r, cc)].data_ptr() for cc in range(C)], [wsd[(rr, c)].data_ptr() for rr in range(R)],
+              m, kl, kr, n, out, n_slices=slices)
+        _native.check_status()
+        _close(out, ref[r * m:(r + 1) * m, c * n:(c + 1) * n], Kd)
+
+
+@pytest.mark.parametrize("mesh,slices", [((2, 2), 2), ((2, 4), 1)])
+def test_ls_pull_weights_push_over_row(mesh, slices):
+    from meshslice_b200 import _native
+    R, C = mesh
+    M, Kd, N = 256 * R, 128 * C, 512 * R * C
+    X = torch.randn(M, Kd, device="cuda").bfloat16()
+    W = torch.randn(N, Kd, device="cuda").bfloat16()
+    m, kl, nr, nc = M // R, Kd // C, N // R, N // C
+    xs = {(r, c): X[r * m:(r + 1) * m, c * kl:(c + 1) * kl].contiguous() for r in range(R) for c in range(C)}
+    wsd = {(r, c): W[r * nr:(r + 1) * nr, c * kl:(c + 1) * kl].contiguous() for r in range(R) for c in range(C)}
+    ops, _ = _setup(R, C, 16, N * kl * 2, C * m * nc * 2)
+    ref = X.float() @ W.float().t()
+    outs = {k: torch.empty(m, nc, device="cuda", dtype=torch.bfloat16) for k in ops}
+    for op in ops.values():
+        op._reset_flags(_native.stream_ptr())
+    for phase in ("gemm", "reduce"):
+        for (r, c), op in ops.items():
+            op.ls(xs[(r, c)], [wsd[(rr, c)].data_ptr() for rr in range(R)], m, kl, nr, outs[(r, c)],
+                  n_slices=slices, phase=phase, reset=False)
+            _native.check_status()
+    for (r, c), out in outs.items():
+        _close(out, ref[r * m:(r + 1) * m, c * nc:(c + 1) * nc], Kd)
+
+
+@pytest.mark.parametrize("mesh,slices,cyc", [((2, 2), 2, 1), ((2, 2), 1, 2), ((4, 2), 2, 2)])
+def test_rs_pull_inputs_push_over_column(mesh, slices, cyc):
+    from meshslice_b200 import _native
+    R, C = mesh
+    Kd, M, N = 192 * R, 512 * R * C, 256 * C
+    X = torch.randn(Kd, M, device="cuda").bfloat16()
+    W = torch.randn(Kd, N, device="cuda").bfloat16()
+    kr, ml, mr, n = Kd // R, M // C, M // R, N // C
+    xs = {(r, c): X[r * kr:(r + 1) * kr, c * ml:(c + 1) * ml].contiguous() for r in range(R) for c in range(C)}
+    wsd = {(r, c): W[r * kr:(r + 1) * kr, c * n:(c + 1) * n].contiguous() for r in range(R) for c in range(C)}
+    ops, _ = _setup(R, C, kr * M * 2, 16, R * mr * n * 2)
+    ref = X.float().t() @ W.float()
+    outs = {k: torch.empty(mr, n, device="cuda", dtype=torch.bfloat16) for k in ops}
+    for op in ops.values():
+        op._reset_flags(_native.stream_ptr())
+    for phase in ("gemm", "reduce"):
+        for (r, c), op in ops.items():
+            op.rs([xs[(r, cc)].data_ptr() for cc in range(C)], wsd[(r, c)], kr, ml, n, outs[(r, c)],
+                  n_slices=slices, cyc=cyc, phase=phase, reset=False)
+            _native.check_status()
+    for (r, c), out in outs.items():
+        _close(out, ref[r * mr:(r + 1) * mr, c * n:(c + 1) * n], Kd)
+
+
+def test_bounded_wait_reports_timeout_instead_of_hanging():
+    """A flag that nobody sets: the probe kernel gives up after its deadline and says so."""
+    from meshslice_b200 import _native
+    C = _native.load()
+    flag = torch.zeros(1, device="cuda", dtype=torch.int32)
+    st = torch.zeros(4, device="cuda", dtype=torch.int32)
+    C.bounded_wait_probe(flag.data_ptr(), 1, 50_000_000, st.data_ptr(), _native.stream_ptr())
+    torch.cuda.synchronize()
+    assert st[0].item() == 1
+    flag.fill_(5)
+    st.zero_()
+    C.bounded_wait_probe(flag.data_ptr(), 1, 50_000_000, st.data_ptr(), _native.stream_ptr())
+    torch.cuda.synchronize()
+    assert st[0].item() == 0
