@@ -1,0 +1,198 @@
+"""GPT-3-like decoder on a 2-D device mesh: learned token + position embeddings, pre-LayerNorm
+blocks (attention + GeLU MLP), final LayerNorm, vocabulary-parallel LM head with fused softmax
+cross-entropy.  The reference stops at one Transformer block (ShardedLayers.py:161-190) and has
+no embedding, head, loss or optimizer; they are added here on the same sharding rules:
+
+  activations      [tokens, d]          P(row, col)   tokens over mesh rows, features over columns
+  linear weights   [in, out]/[out, in]  P(row, col)   (dataflow 'ls' stores [out, in])
+  LayerNorm, embeddings                 P(None, col)  replicated over mesh rows
+
+All parameters of one rank live in two flat buffers ("sharded" and "row-replicated") so that
+the optimizer is one kernel launch per buffer; gradients mirror them.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import List, Optional, Tuple
+
+import torch
+
+from ..ops import functional as F
+from ..parallel.mesh import Mesh, ShardedTensor
+from .sharded_layers import GeLU, ShardedAttention, ShardedFFLayer, ShardedLayerNorm, _add
+
+
+@dataclass
+class GPTConfig:
+    n_layers: int = 32
+    d_model: int = 4096
+    n_heads: int = 32
+    ffn: int = 16384
+    vocab: int = 50257
+    seq: int = 2048
+    dataflows: Tuple[str, str, str, str] = ("os", "os", "os", "ls")   # in_proj, out_proj, ff1, ff2
+    ksplits: Tuple[int, int, int, int] = (4, 4, 4, 4)
+    head_ksplit: int = 4
+    algorithm: str = "meshslice"
+    causal: bool = True
+    eps: float = 1e-5
+    init_std: float = 0.02
+    vocab_pad: int = 2048          # the vocabulary is padded to a multiple of this
+    dtype: torch.dtype = torch.bfloat16
+
+    @property
+    def vocab_padded(self) -> int:
+        return (self.vocab + self.vocab_pad - 1) // self.vocab_pad * self.vocab_pad
+
+    def n_params(self) -> int:
+        d = self.d_model
+        per_layer = 3 * d * d + d * d + 2 * d * self.ffn + 4 * d
+        return self.n_layers * per_layer + (self.vocab_padded + self.seq) * d + d * self.vocab_padded + 2 * d
+
+    def flops_per_token(self) -> float:
+        """Model FLOPs of one training step per token (forward + backward = 3x forward GEMMs,
+        attention counted with its full S x S score matrix as the reference's block does)."""
+        d = self.d_model
+        gemm = 2 * (3 * d * d + d * d + 2 * d * self.ffn) * self.n_layers + 2 * d * self.vocab_padded
+        attn = 4 * self.seq * d * self.n_layers * (0.5 if self.causal else 1.0)
+        return 3.0 * (gemm + attn)
+
+
+class _Flat:
+    """Carves tensors out of one flat buffer per coordinate, in call order."""
+
+    def __init__(self):
+        self.requests = []     # (shape, dtype)
+
+    def size(self, dtype_size=2):
+        return sum((int(torch.Size(s).numel()) + 127) // 128 * 128 for s, _ in self.requests)
+
+
+class GPTBlock:
+    """Pre-LN decoder block: x + out_proj(attn(in_proj(LN1 x)));  h + ff2(gelu(ff1(LN2 h)))."""
+
+    def __init__(self, mesh: Mesh, cfg: GPTConfig, idx: int, device, alloc_sharded, alloc_rep, grad_sharded):
+        d, df, ks = cfg.d_model, cfg.dataflows, cfg.ksplits
+        kw = dict(dtype=cfg.dtype, device=device, std=cfg.init_std, alloc=alloc_sharded,
+                  grad_alloc=grad_sharded)
+        s = idx * 16
+        self.ln1 = ShardedLayerNorm(mesh, d, affine=True, eps=cfg.eps, dtype=cfg.dtype, device=device, alloc=alloc_rep)
+        self.in_proj = ShardedFFLayer(mesh, cfg.algorithm, df[0], ks[0], d, 3 * d, seed=s + 1, **kw)
+        self.attn = ShardedAttention(mesh, cfg.n_heads, cfg.seq, causal=cfg.causal)
+        self.out_proj = ShardedFFLayer(mesh, cfg.algorithm, df[1], ks[1], d, d, seed=s + 2, **kw)
+        self.ln2 = ShardedLayerNorm(mesh, d, affine=True, eps=cfg.eps, dtype=cfg.dtype, device=device, alloc=alloc_rep)
+        self.ff1 = ShardedFFLayer(mesh, cfg.algorithm, df[2], ks[2], d, cfg.ffn, seed=s + 3, **kw)
+        self.gelu = GeLU()
+        self.ff2 = ShardedFFLayer(mesh, cfg.algorithm, df[3], ks[3], cfg.ffn, d, seed=s + 4, **kw)
+
+    def forward(self, x: ShardedTensor, delta: Optional[ShardedTensor]):
+        """Input: residual stream x and a pending branch output ``delta`` (added inside LN1).
+        Returns (h, mlp_out): the caller's next LayerNorm adds them."""
+        y = self.ln1.forward(x, delta)            # residual stream becomes x + delta
+        x = self.ln1.h
+        a = self.out_proj.forward(self.attn.forward(self.in_proj.forward(y)))
+        y = self.ln2.forward(a, x)                # h = x + a
+        h = self.ln2.h
+        m = self.ff2.forward(self.gelu.forward(self.ff1.forward(y)))
+        return h, m
+
+    def backward(self, dh: ShardedTensor, dm: ShardedTensor):
+        """dh: gradient of the residual stream after this block, dm: gradient of the MLP output.
+        Returns (dx, ddelta) for the block below."""
+        d = self.ff1.backward(self.gelu.backward(self.ff2.backward(dm)))
+        dh2 = self.ln2.backward(d, dh)            # gradient of h = x + a
+        d = self.in_proj.backward(self.attn.backward(self.out_proj.backward(dh2)))
+        dx = self.ln1.backward(d, dh2)            # gradient of x + delta
+        return dx, dx
+
+    def layers(self):
+        return [self.ln1, self.in_proj, self.out_proj, self.ln2, self.ff1, self.ff2]
+
+
+class GPTModel:
+    def __init__(self, mesh: Mesh, cfg: GPTConfig, device=None, alloc_sharded=None, alloc_rep=None,
+                 grad_sharded=None):
+        self.mesh, self.cfg, self.device = mesh, cfg, device
+        if cfg.d_model % mesh.C or cfg.vocab_padded % mesh.C or cfg.n_heads % mesh.C:
+            raise ValueError("model width / heads / vocabulary must divide over the mesh columns")
+        d, C = cfg.d_model, mesh.C
+        a_rep = alloc_rep or (lambda shape, dtype, dev: torch.empty(shape, dtype=dtype, device=dev))
+        self.tok = ShardedTensor(mesh, {})
+        self.pos = ShardedTensor(mesh, {})
+        for (r, c) in mesh.coords():
+            g = torch.Generator().manual_seed(900001 + c)      # same along a mesh column
+            t = a_rep((cfg.vocab_padded, d // C), cfg.dtype, device)
+            t.copy_((torch.randn(cfg.vocab_padded, d // C, generator=g) * cfg.init_std).to(cfg.dtype))
+            p = a_rep((cfg.seq, d // C), cfg.dtype, device)
+            p.copy_((torch.randn(cfg.seq, d // C, generator=g) * cfg.init_std).to(cfg.dtype))
+            self.tok.shards[(r, c)], self.pos.shards[(r, c)] = t, p
+        z32 = lambda shape: ShardedTensor(mesh, {k: torch.zeros(shape, dtype=torch.float32, device=device)
+                                                 for k in mesh.coords()})
+        self.dtok, self.dpos = z32((cfg.vocab_padded, d // C)), z32((cfg.seq, d // C))
+        self.blocks = [GPTBlock(mesh, cfg, i, device, alloc_sharded, alloc_rep, grad_sharded)
+                       for i in range(cfg.n_layers)]
+        self.ln_f = ShardedLayerNorm(mesh, d, affine=True, eps=cfg.eps, dtype=cfg.dtype, device=device, alloc=alloc_rep)
+        self.head = ShardedFFLayer(mesh, cfg.algorithm, "os", cfg.head_ksplit, d, cfg.vocab_padded,
+                                   dtype=cfg.dtype, device=device, std=cfg.init_std, seed=777,
+                                   alloc=alloc_sharded, grad_alloc=grad_sharded)
+        self._saved = None
+
+    # ------------------------------------------------------------------ parameters
+    def parameters(self):
+        """[(name, param ShardedTensor, grad ShardedTensor, kind)] with kind 'sharded' (unique per
+        rank) or 'row_replicated' (same value along a mesh column; gradients are summed there)."""
+        out = [("tok", self.tok, self.dtok, "row_replicated"), ("pos", self.pos, self.dpos, "row_replicated")]
+        for i, b in enumerate(self.blocks):
+            for j, l in enumerate(b.layers()):
+                out += [(f"block{i}.{type(l).__name__}{j}.{n}", p, g, kind) for n, p, g, kind in l.parameters()]
+        out += [(f"ln_f.{n}", p, g, k) for n, p, g, k in self.ln_f.parameters()]
+        out += [(f"head.{n}", p, g, k) for n, p, g, k in self.head.parameters()]
+        return out
+
+    def zero_grad(self):
+        for _, _, g, _ in self.parameters():
+            for t in g.shards.values():
+                t.zero_()
+
+    # ------------------------------------------------------------------ training step pieces
+    def forward_backward(self, tokens: ShardedTensor, targets: ShardedTensor, n_tokens_global: int):
+        """One micro-batch: forward, loss, backward; gradients accumulate.  ``tokens`` / ``targets``
+        hold, per coordinate, the int64 ids of the sequences of that mesh row [local_tokens].
+        Returns the ShardedTensor of per-coordinate loss contributions (sum over local tokens of
+        the token loss divided by n_tokens_global; summing over the mesh rows gives the mean)."""
+        m, cfg = self.mesh, self.cfg
+        x = ShardedTensor(m, {k: F.embedding_fwd(tokens.shards[k], self.tok.shards[k], self.pos.shards[k], cfg.seq)
+                              for k in m.coords()})
+        delta = None
+        for b in self.blocks:
+            x, delta = b.forward(x, delta)
+        y = self.ln_f.forward(x, delta)
+        logits = self.head.forward(y)                                    # [T/R, Vp/C]
+        vc = cfg.vocab_padded // m.C
+        parts = {k: F.ce_partial(logits.shards[k], targets.shards[k], k[1] * vc, cfg.vocab) for k in m.coords()}
+        mx = ShardedTensor(m, {k: v[0] for k, v in parts.items()})
+        gmax = m.all_reduce(mx, "col", op="max")
+        se = ShardedTensor(m, {k: parts[k][1] * torch.exp(parts[k][0] - gmax.shards[k]) for k in m.coords()})
+        packed = m.all_reduce(ShardedTensor(m, {k: torch.stack([se.shards[k], parts[k][2]]) for k in m.coords()}), "col")
+        loss = ShardedTensor(m, {k: (torch.log(packed.shards[k][0]) + gmax.shards[k] - packed.shards[k][1]).sum()
+                                 / n_tokens_global for k in m.coords()})
+        # backward
+        for k in m.coords():
+            F.ce_grad_(logits.shards[k], targets.shards[k], k[1] * vc, cfg.vocab, gmax.shards[k],
+                       packed.shards[k][0].contiguous(), 1.0 / n_tokens_global)
+        d = self.head.backward(logits)
+        dx = self.ln_f.backward(d)                                       # gradient of x + delta
+        dh, dm = dx, dx
+        for b in reversed(self.blocks):
+            dh, dm = b.backward(dh, dm)
+        for k in m.coords():
+            F.embedding_bwd(tokens.shards[k], dh.shards[k], self.dtok.shards[k], self.dpos.shards[k], cfg.seq)
+        return loss
+
+    def sync_replicated_grads(self):
+        """Sum the gradients of row-replicated parameters over the mesh rows."""
+        for _, _, g, kind in self.parameters():
+            if kind == "row_replicated" and self.mesh.R > 1:
+                red = self.mesh.all_reduce(g, "row")
+                for k in g.shards:
+                    g.shards[k].copy_(red.shards[k])

@@ -1,0 +1,120 @@
+"""Fused engine of one rank: owns the symmetric heap and workspace and exposes the three
+MeshSlice dataflows on local shards, with in-kernel NVLink traffic (no NCCL on these paths).
+
+Operands that peers pull (gathered operands) must live in the symmetric heap.  Parameters are
+allocated there; an activation that is not is first copied into a send buffer of the heap on
+the caller's stream.  When a shape breaks the tile divisibility rules of the fused kernel the
+engine falls back to the generic collective formulation (NCCL + local tcgen05 GEMM) and says
+so once.
+"""
+from __future__ import annotations
+
+import warnings
+from typing import Optional
+
+import torch
+
+from .. import _native
+from ..ops.gemm import gemm, sm_count
+from . import runtime as rt
+from .fused import FusedGemm, FusedPlanError, MeshCoord
+from .mesh import DistMesh, ShardedTensor
+
+
+def _local(t):
+    return t.local() if isinstance(t, ShardedTensor) else t
+
+
+class FusedEngine:
+    def __init__(self, mesh: DistMesh, stage_a_bytes: int, stage_b_bytes: int, slot_bytes: int,
+                 send_bytes: int, extra_heap_bytes: int = 0, timeout_ns: int = 20_000_000_000):
+        self.mesh = mesh
+        total = stage_a_bytes + stage_b_bytes + slot_bytes + 2 * send_bytes + extra_heap_bytes + (8 << 20)
+        self.heap = rt.SymmHeap(total, group=mesh.group)
+        self.ws = rt.Workspace(self.heap, stage_a_bytes, stage_b_bytes, slot_bytes, send_bytes)
+        self.world = rt.World.real(self.ws)
+        self.coord = MeshCoord(mesh.R, mesh.C, mesh.r, mesh.c)
+        self.fg = FusedGemm(self.coord, self.world, sm_count(), timeout_ns=timeout_ns)
+        self._warned = set()
+        mesh.engine = self
+
+    # ------------------------------------------------------------------ helpers
+    def _pull_ptrs(self, t: torch.Tensor, ranks, send_off: int):
+        """Pointers of every peer's copy of ``t`` (own copy included)."""
+        t = t.contiguous()
+        off = self.heap.offset_of(t)
+        if off is None:
+            nbytes = t.numel() * t.element_size()
+            if nbytes > self.ws.send_bytes:
+                raise FusedPlanError("operand larger than the send buffer")
+            self.heap.bytes_view(send_off, nbytes).view(t.dtype).view(t.shape).copy_(t)
+            off = send_off
+        return [self.heap.ptr(q, off) for q in ranks]
+
+    def _fallback(self, which, err, X, W, n_slices):
+        if which not in self._warned:
+            warnings.warn(f"fused {which} not applicable ({err}); using NCCL collectives + local GEMM")
+            self._warned.add(which)
+        from . import tensor_parallel as tp
+        m = self.mesh
+        Xs = ShardedTensor(m, {(m.r, m.c): X})
+        Wsh = ShardedTensor(m, {(m.r, m.c): W})
+        fn = {"os": tp.collective_os, "ls": tp.collective_ls, "rs": tp.collective_rs}[which]
+        return fn(m, Xs, Wsh).local()
+
+    # ------------------------------------------------------------------ dataflows
+    def os(self, X, W, n_slices: int = 4, out: Optional[torch.Tensor] = None, accumulate=False,
+           bias=None, act=None, pre_act=None):
+        """Y[m, n] = AG_col(X)[m, Kd] @ AG_row(W)[Kd, n]."""
+        X, W = _local(X), _local(W)
+        m, kl = X.shape
+        kr, n = W.shape
+        if out is None:
+            out = torch.empty(m, n, dtype=torch.bfloat16, device=X.device)
+        try:
+            xp = self._pull_ptrs(X, self.coord.row_peers(), self.ws.send_a)
+            wp = self._pull_ptrs(W, self.coord.col_peers(), self.ws.send_b)
+            return self.fg.os(xp, wp, m, kl, kr, n, out, n_slices=n_slices, accumulate=accumulate,
+                              bias=bias, act=act, pre_act=pre_act)
+        except FusedPlanError as e:
+            y = self._fallback("os", e, X, W, n_slices)
+            if bias is not None or act is not None:
+                raise
+            out.copy_(y) if not accumulate else out.add_(y)
+            return out
+
+    def ls(self, X, W, n_slices: int = 4, out: Optional[torch.Tensor] = None, accumulate=False):
+        """Y[m, N/C] = RS_col( X[m, kl] @ AG_row(W)[N, kl]^T )."""
+        X, W = _local(X), _local(W)
+        m, kl = X.shape
+        nr = W.shape[0]
+        N = nr * self.mesh.R
+        if out is None:
+            out = torch.empty(m, N // self.mesh.C, dtype=torch.bfloat16, device=X.device)
+        try:
+            wp = self._pull_ptrs(W, self.coord.col_peers(), self.ws.send_b)
+            return self.fg.ls(X.contiguous(), wp, m, kl, nr, out, n_slices=n_slices, accumulate=accumulate)
+        except FusedPlanError as e:
+            y = self._fallback("ls", e, X, W, n_slices)
+            out.copy_(y) if not accumulate else out.add_(y)
+            return out
+
+    def rs(self, X, W, n_slices: int = 4, out: Optional[torch.Tensor] = None, accumulate=False):
+        """Y[M/R, n] = RS_row( AG_col(X)[kr, M]^T @ W[kr, n] )."""
+        X, W = _local(X), _local(W)
+        kr, ml = X.shape
+        n = W.shape[1]
+        M = ml * self.mesh.C
+        if out is None:
+            out = torch.empty(M // self.mesh.R, n, dtype=torch.bfloat16, device=X.device)
+        try:
+            xp = self._pull_ptrs(X, self.coord.row_peers(), self.ws.send_a)
+            return self.fg.rs(xp, W.contiguous(), kr, ml, n, out, n_slices=n_slices, accumulate=accumulate)
+        except FusedPlanError as e:
+            y = self._fallback("rs", e, X, W, n_slices)
+            out.copy_(y) if not accumulate else out.add_(y)
+            return out
+
+    def check(self):
+        """Raise if any kernel of this process reported a timeout (synchronises the device)."""
+        _native.check_status()

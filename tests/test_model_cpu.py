@@ -1,0 +1,131 @@
+"""GPT model and the reference-style Transformer block on emulated CPU meshes against a dense
+fp32 PyTorch model built from the same (unsharded) weights."""
+import math
+
+import pytest
+import torch
+
+from meshslice_b200.models.gpt import GPTConfig, GPTModel
+from meshslice_b200.models.sharded_layers import ShardedFFLayer, TransformerBlock
+from meshslice_b200.parallel.mesh import EmuMesh, ShardedTensor
+
+CFG = GPTConfig(n_layers=2, d_model=128, n_heads=4, ffn=512, vocab=1000, seq=32, ksplits=(2, 2, 2, 2),
+                head_ksplit=2, vocab_pad=256, dtype=torch.float32, causal=True)
+
+
+def _full(mesh, st):
+    return mesh.unshard(st)
+
+
+def _cols(mesh, st):
+    return torch.cat([st.shards[(0, c)] for c in range(mesh.C)], dim=-1)
+
+
+def _dense_loss(model, mesh, cfg, ids):
+    """Plain PyTorch forward of the same network with autograd."""
+    P = {}
+    def leaf(t):
+        t = t.clone().float().requires_grad_(True)
+        return t
+    P["tok"], P["pos"] = leaf(_cols(mesh, model.tok)), leaf(_cols(mesh, model.pos))
+    x = P["tok"][ids[:, :-1].reshape(-1)] + P["pos"][torch.arange(ids.shape[0] * cfg.seq) % cfg.seq]
+    H, D = cfg.n_heads, cfg.d_model // cfg.n_heads
+    Bsz = ids.shape[0]
+    def ln(v, layer, tag):
+        g, b = leaf(_cols(mesh, layer.gamma)), leaf(_cols(mesh, layer.bias))
+        P[tag + ".g"], P[tag + ".b"] = g, b
+        return torch.nn.functional.layer_norm(v, (cfg.d_model,), g, b, cfg.eps)
+    def lin(v, layer, tag):
+        w = leaf(_full(mesh, layer.weight))
+        P[tag] = w
+        return v @ (w.t() if layer.dataflow == "ls" else w)
+    for i, blk in enumerate(model.blocks):
+        y = ln(x, blk.ln1, f"{i}.ln1")
+        qkv = lin(y, blk.in_proj, f"{i}.in").view(Bsz, cfg.seq, H, 3, D)
+        q, k, v = (qkv[:, :, :, j].permute(0, 2, 1, 3) for j in range(3))
+        s = q @ k.transpose(-1, -2) / math.sqrt(D)
+        s = s.masked_fill(torch.ones(cfg.seq, cfg.seq, dtype=torch.bool).triu(1), float("-inf"))
+        a = (torch.softmax(s, -1) @ v).permute(0, 2, 1, 3).reshape(Bsz * cfg.seq, H * D)
+        x = x + lin(a, blk.out_proj, f"{i}.out")
+        y = ln(x, blk.ln2, f"{i}.ln2")
+        m = lin(torch.nn.functional.gelu(lin(y, blk.ff1, f"{i}.ff1"), approximate="tanh"), blk.ff2, f"{i}.ff2")
+        x = x + m
+    y = ln(x, model.ln_f, "lnf")
+    logits = lin(y, model.head, "head")[:, :cfg.vocab]
+    loss = torch.nn.functional.cross_entropy(logits, ids[:, 1:].reshape(-1))
+    loss.backward()
+    return loss, P
+
+
+@pytest.mark.parametrize("shape", [(1, 1), (2, 2), (2, 4), (4, 1)])
+def test_gpt_loss_and_grads_match_dense_model(shape):
+    R, C = shape
+    mesh = EmuMesh(R, C)
+    model = GPTModel(mesh, CFG)
+    B = 4
+    ids = torch.randint(0, CFG.vocab, (B, CFG.seq + 1), generator=torch.Generator().manual_seed(1))
+    per = B // R
+    tok = ShardedTensor(mesh, {(r, c): ids[r * per:(r + 1) * per, :-1].reshape(-1) for (r, c) in mesh.coords()})
+    tgt = ShardedTensor(mesh, {(r, c): ids[r * per:(r + 1) * per, 1:].reshape(-1) for (r, c) in mesh.coords()})
+    loss = model.forward_backward(tok, tgt, B * CFG.seq)
+    model.sync_replicated_grads()
+    total = sum(loss.shards[(r, 0)] for r in range(R))
+    ref, P = _dense_loss(model, mesh, CFG, ids)
+    assert abs(total.item() - ref.item()) < 1e-4
+    b0 = model.blocks[0]
+    for layer, tag in ((b0.in_proj, "0.in"), (b0.out_proj, "0.out"), (b0.ff1, "0.ff1"), (b0.ff2, "0.ff2"),
+                       (model.head, "head")):
+        got = _full(mesh, layer.grad)
+        assert torch.allclose(got, P[tag].grad, atol=2e-5, rtol=1e-3), tag
+    assert torch.allclose(_cols(mesh, b0.ln1.dgamma), P["0.ln1.g"].grad, atol=2e-5, rtol=1e-3)
+    assert torch.allclose(_cols(mesh, b0.ln2.dbias), P["0.ln2.b"].grad, atol=2e-5, rtol=1e-3)
+    assert torch.allclose(_cols(mesh, model.dtok), P["tok"].grad, atol=2e-5, rtol=1e-3)
+    assert torch.allclose(_cols(mesh, model.dpos), P["pos"].grad, atol=2e-5, rtol=1e-3)
+
+
+@pytest.mark.parametrize("dataflow", ["os", "ls", "rs"])
+def test_ff_layer_forward_backward_each_dataflow(dataflow):
+    """ShardedLayers.py:41-81: forward, dX and dW of every dataflow against dense autograd."""
+    mesh = EmuMesh(2, 4)
+    T, I, O = 64, 128, 256
+    layer = ShardedFFLayer(mesh, "meshslice", dataflow, 2, I, O, blocksize=8, dtype=torch.float32)
+    W = _full(mesh, layer.weight).clone().requires_grad_(True)
+    g = torch.Generator().manual_seed(3)
+    X = torch.randn(T, I, generator=g, requires_grad=True)
+    Yd = X @ (W.t() if dataflow == "ls" else W)
+    dY = torch.randn(T, O, generator=g)
+    Yd.backward(dY)
+    xin = mesh.shard(X.detach().t().contiguous() if dataflow == "rs" else X.detach())
+    y = layer.forward(xin)
+    assert torch.allclose(_full(mesh, y), Yd.detach(), atol=1e-4, rtol=1e-4)
+    dx = layer.backward(mesh.shard(dY))
+    dxf = _full(mesh, dx)
+    assert torch.allclose(dxf.t() if dataflow == "rs" else dxf, X.grad, atol=1e-4, rtol=1e-4)
+    assert torch.allclose(_full(mesh, layer.grad), W.grad, atol=1e-4, rtol=1e-4)
+
+
+def test_reference_transformer_block_forward_backward():
+    """The reference block (norm1..norm3, non-causal attention, no affine) vs dense autograd."""
+    mesh = EmuMesh(2, 2)
+    S, H, D, B = 16, 4, 16, 4
+    blk = TransformerBlock(mesh, S, H, D, ["os", "os", "os", "ls"], alg="meshflow", ksplits=(2, 2, 2, 2),
+                           dtype=torch.float32, std=0.05)
+    g = torch.Generator().manual_seed(0)
+    X = torch.randn(B * S, H * D, generator=g, requires_grad=True)
+    dY = torch.randn(B * S, H * D, generator=g)
+    Ws = {n: _full(mesh, getattr(blk, n).weight) for n in ("in_proj", "out_proj", "ff1", "ff2")}
+    def ln(v):
+        mu = v.mean(-1, keepdim=True)
+        return (v - mu) / torch.sqrt((v * v).mean(-1, keepdim=True) - mu * mu + 1e-6)
+    o = ln(X) @ Ws["in_proj"]
+    qkv = o.view(B, S, H, 3, D)
+    q, k, v = (qkv[:, :, :, j].permute(0, 2, 1, 3) for j in range(3))
+    a = (torch.softmax(q @ k.transpose(-1, -2) / math.sqrt(D), -1) @ v).permute(0, 2, 1, 3).reshape(B * S, H * D)
+    res = ln(a @ Ws["out_proj"] + X)
+    o = torch.nn.functional.gelu(res @ Ws["ff1"], approximate="tanh") @ Ws["ff2"].t()
+    Yd = ln(o + res)
+    Yd.backward(dY)
+    y = blk.forward(mesh.shard(X.detach()))
+    assert torch.allclose(_full(mesh, y), Yd.detach(), atol=2e-4, rtol=1e-3)
+    dx = blk.backward(mesh.shard(dY))
+    assert torch.allclose(_full(mesh, dx), X.grad, atol=2e-4, rtol=1e-3)
