@@ -24,7 +24,12 @@ void check(cudaError_t e, const char* what) {
 }
 template <class T>
 T* P(uint64_t p) { return reinterpret_cast<T*>(static_cast<uintptr_t>(p)); }
-cudaStream_t S(uint64_t s) { return reinterpret_cast<cudaStream_t>(static_cast<uintptr_t>(s)); }
+// every launcher converts its stream handle exactly once, so this also counts launches
+static uint64_t g_launches = 0;
+cudaStream_t S(uint64_t s) {
+  ++g_launches;
+  return reinterpret_cast<cudaStream_t>(static_cast<uintptr_t>(s));
+}
 
 int64_t geti(const py::dict& d, const char* k, int64_t def = 0) {
   return d.contains(k) ? d[k].cast<int64_t>() : def;
@@ -205,7 +210,9 @@ py::tuple status_read(uint64_t host_ptr) {
 void status_clear(uint64_t host_ptr) { std::memset(P<void>(host_ptr), 0, 64); }
 
 void memset_zero(uint64_t ptr, size_t bytes, uint64_t stream) {
-  check(cudaMemsetAsync(P<void>(ptr), 0, bytes, S(stream)), "cudaMemsetAsync");
+  check(cudaMemsetAsync(P<void>(ptr), 0, bytes,
+                        reinterpret_cast<cudaStream_t>(static_cast<uintptr_t>(stream))),
+        "cudaMemsetAsync");
 }
 
 }  // namespace
@@ -227,6 +234,7 @@ PYBIND11_MODULE(_C, m) {
   m.def("status_read", &status_read);
   m.def("status_clear", &status_clear);
   m.def("memset_zero", &memset_zero);
+  m.def("launch_count", []() { return g_launches; }, "kernel launches issued by this module so far");
 
   m.def("p2p_copy", [](uint64_t jobs, int n_jobs, const py::dict& bar, int grid, uint64_t stream) {
     check(p2p_copy(P<const CopyJob>(jobs), n_jobs, parse_barrier(bar), grid, S(stream)), "p2p_copy");

@@ -58,29 +58,22 @@ class GPTConfig:
         return 3.0 * (gemm + attn)
 
 
-class _Flat:
-    """Carves tensors out of one flat buffer per coordinate, in call order."""
-
-    def __init__(self):
-        self.requests = []     # (shape, dtype)
-
-    def size(self, dtype_size=2):
-        return sum((int(torch.Size(s).numel()) + 127) // 128 * 128 for s, _ in self.requests)
-
-
 class GPTBlock:
     """Pre-LN decoder block: x + out_proj(attn(in_proj(LN1 x)));  h + ff2(gelu(ff1(LN2 h)))."""
 
-    def __init__(self, mesh: Mesh, cfg: GPTConfig, idx: int, device, alloc_sharded, alloc_rep, grad_sharded):
+    def __init__(self, mesh: Mesh, cfg: GPTConfig, idx: int, device, alloc_sharded, alloc_rep, grad_sharded,
+                 grad_rep=None):
         d, df, ks = cfg.d_model, cfg.dataflows, cfg.ksplits
         kw = dict(dtype=cfg.dtype, device=device, std=cfg.init_std, alloc=alloc_sharded,
                   grad_alloc=grad_sharded)
         s = idx * 16
-        self.ln1 = ShardedLayerNorm(mesh, d, affine=True, eps=cfg.eps, dtype=cfg.dtype, device=device, alloc=alloc_rep)
+        self.ln1 = ShardedLayerNorm(mesh, d, affine=True, eps=cfg.eps, dtype=cfg.dtype, device=device, alloc=alloc_rep,
+                                    grad_alloc=grad_rep)
         self.in_proj = ShardedFFLayer(mesh, cfg.algorithm, df[0], ks[0], d, 3 * d, seed=s + 1, **kw)
         self.attn = ShardedAttention(mesh, cfg.n_heads, cfg.seq, causal=cfg.causal)
         self.out_proj = ShardedFFLayer(mesh, cfg.algorithm, df[1], ks[1], d, d, seed=s + 2, **kw)
-        self.ln2 = ShardedLayerNorm(mesh, d, affine=True, eps=cfg.eps, dtype=cfg.dtype, device=device, alloc=alloc_rep)
+        self.ln2 = ShardedLayerNorm(mesh, d, affine=True, eps=cfg.eps, dtype=cfg.dtype, device=device, alloc=alloc_rep,
+                                    grad_alloc=grad_rep)
         self.ff1 = ShardedFFLayer(mesh, cfg.algorithm, df[2], ks[2], d, cfg.ffn, seed=s + 3, **kw)
         self.gelu = GeLU()
         self.ff2 = ShardedFFLayer(mesh, cfg.algorithm, df[3], ks[3], cfg.ffn, d, seed=s + 4, **kw)
@@ -111,7 +104,7 @@ class GPTBlock:
 
 class GPTModel:
     def __init__(self, mesh: Mesh, cfg: GPTConfig, device=None, alloc_sharded=None, alloc_rep=None,
-                 grad_sharded=None):
+                 grad_sharded=None, grad_rep=None):
         self.mesh, self.cfg, self.device = mesh, cfg, device
         if cfg.d_model % mesh.C or cfg.vocab_padded % mesh.C or cfg.n_heads % mesh.C:
             raise ValueError("model width / heads / vocabulary must divide over the mesh columns")
@@ -126,12 +119,14 @@ class GPTModel:
             p = a_rep((cfg.seq, d // C), cfg.dtype, device)
             p.copy_((torch.randn(cfg.seq, d // C, generator=g) * cfg.init_std).to(cfg.dtype))
             self.tok.shards[(r, c)], self.pos.shards[(r, c)] = t, p
-        z32 = lambda shape: ShardedTensor(mesh, {k: torch.zeros(shape, dtype=torch.float32, device=device)
+        g_rep = grad_rep or (lambda shape, dtype, dev: torch.empty(shape, dtype=dtype, device=dev))
+        z32 = lambda shape: ShardedTensor(mesh, {k: g_rep(shape, torch.float32, device).zero_()
                                                  for k in mesh.coords()})
         self.dtok, self.dpos = z32((cfg.vocab_padded, d // C)), z32((cfg.seq, d // C))
-        self.blocks = [GPTBlock(mesh, cfg, i, device, alloc_sharded, alloc_rep, grad_sharded)
+        self.blocks = [GPTBlock(mesh, cfg, i, device, alloc_sharded, alloc_rep, grad_sharded, grad_rep)
                        for i in range(cfg.n_layers)]
-        self.ln_f = ShardedLayerNorm(mesh, d, affine=True, eps=cfg.eps, dtype=cfg.dtype, device=device, alloc=alloc_rep)
+        self.ln_f = ShardedLayerNorm(mesh, d, affine=True, eps=cfg.eps, dtype=cfg.dtype, device=device, alloc=alloc_rep,
+                                    grad_alloc=grad_rep)
         self.head = ShardedFFLayer(mesh, cfg.algorithm, "os", cfg.head_ksplit, d, cfg.vocab_padded,
                                    dtype=cfg.dtype, device=device, std=cfg.init_std, seed=777,
                                    alloc=alloc_sharded, grad_alloc=grad_sharded)

@@ -100,14 +100,15 @@ class ShardedLayerNorm:
     no affine transform (ShardedLayers.py:123-138); ``affine=True`` applies gamma / beta."""
 
     def __init__(self, mesh: Mesh, in_dim: int, affine: bool = False, eps: float = 1e-6,
-                 dtype=torch.bfloat16, device=None, alloc: Optional[Callable] = None):
+                 dtype=torch.bfloat16, device=None, alloc: Optional[Callable] = None,
+                 grad_alloc: Optional[Callable] = None):
         self.mesh, self.in_dim, self.affine, self.eps = mesh, in_dim, affine, eps
         local = in_dim // mesh.C
         a = alloc or _default_alloc
         mk = lambda fill: ShardedTensor(mesh, {k: a((local,), dtype, device).fill_(fill) for k in mesh.coords()})
         self.gamma, self.bias = mk(1.0), mk(0.0)
-        z = lambda: ShardedTensor(mesh, {k: torch.zeros(local, dtype=torch.float32, device=device)
-                                         for k in mesh.coords()})
+        ga = grad_alloc or _default_alloc
+        z = lambda: ShardedTensor(mesh, {k: ga((local,), torch.float32, device).zero_() for k in mesh.coords()})
         self.dgamma, self.dbias = z(), z()
         self._saved = None
 

@@ -118,3 +118,29 @@ class FusedEngine:
     def check(self):
         """Raise if any kernel of this process reported a timeout (synchronises the device)."""
         _native.check_status()
+
+
+class LocalGemmEngine:
+    """Engine of a 1 x 1 mesh: the three dataflows degenerate to local tcgen05 GEMMs in the
+    'nn' / 'nt' / 'tn' layouts (no operand is transposed in memory)."""
+
+    def __init__(self, mesh):
+        self.mesh = mesh
+        mesh.engine = self
+
+    @staticmethod
+    def _run(X, W, layout, out, accumulate, **kw):
+        X, W = _local(X), _local(W)
+        return gemm(X, W, layout, out=out, accumulate=accumulate, **kw)
+
+    def os(self, X, W, n_slices=1, out=None, accumulate=False, bias=None, act=None, pre_act=None):
+        return self._run(X, W, "nn", out, accumulate, bias=bias, act=act, pre_act=pre_act)
+
+    def ls(self, X, W, n_slices=1, out=None, accumulate=False):
+        return self._run(X, W, "nt", out, accumulate)
+
+    def rs(self, X, W, n_slices=1, out=None, accumulate=False):
+        return self._run(X, W, "tn", out, accumulate)
+
+    def check(self):
+        _native.check_status()

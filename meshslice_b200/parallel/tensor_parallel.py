@@ -369,7 +369,11 @@ class SPMD:
     def _build(self, which: str, K: int) -> Callable:
         eng = self._fused()
         if eng is not None:
-            return partial(getattr(eng, which), n_slices=K)
+            fn, mesh = getattr(eng, which), self.mesh
+            def run(X, W, **kw):
+                y = fn(X, W, n_slices=K, **kw)
+                return ShardedTensor(mesh, {mesh.coords()[0]: y}) if isinstance(X, ShardedTensor) else y
+            return run
         return partial(self.funcs[which], self.mesh, K=K, B=self.blocksize)
 
     def OS(self, K: int = 8):
@@ -391,7 +395,11 @@ def createMultihostMatrix(mesh: Mesh, global_shape, dtype=torch.bfloat16, seed: 
         raise ValueError(f"shape {tuple(global_shape)} not divisible by mesh {mesh.shape}")
     shards = {}
     for (r, c) in mesh.coords():
-        g = torch.Generator(device="cpu").manual_seed(seed * 1000003 + r * mesh.C + c)
-        t = torch.randn(d0 // mesh.R, d1 // mesh.C, generator=g) * std
+        on_gpu = device is not None and torch.device(device).type == "cuda"
+        g = torch.Generator(device=device if on_gpu else "cpu").manual_seed(seed * 1000003 + r * mesh.C + c)
+        t = torch.randn(d0 // mesh.R, d1 // mesh.C, generator=g, device=device if on_gpu else None,
+                        dtype=torch.float32 if not on_gpu else dtype)
+        if std != 1.0:
+            t = t * std
         shards[(r, c)] = t.to(dtype).to(device) if device is not None else t.to(dtype)
     return ShardedTensor(mesh, shards)
