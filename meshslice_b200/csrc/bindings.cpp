@@ -11,6 +11,7 @@
 
 #include "comm/p2p.h"
 #include "gemm/sm100_gemm.h"
+#include "ops/attention.h"
 #include "ops/ops.h"
 
 namespace py = pybind11;
@@ -321,5 +322,17 @@ PYBIND11_MODULE(_C, m) {
                             int n_tokens, int seq, int cols, uint64_t stream) {
     check(embedding_bwd(P<int64_t>(tokens), P<void>(dout), P<float>(dtok), P<float>(dpos), n_tokens,
                         seq, cols, S(stream)), "embedding_bwd");
+  });
+  m.def("attention_fwd", [](uint64_t qkv, uint64_t out, uint64_t lse, int batch, int seq, int heads,
+                            int causal, float scale, uint64_t status, uint64_t stream) {
+    check(attention_fwd(P<void>(qkv), P<void>(out), P<float>(lse), batch, seq, heads, causal, scale,
+                        P<uint32_t>(status), S(stream)), "attention_fwd");
+  });
+  m.def("attention_bwd", [](uint64_t qkv, uint64_t out, uint64_t dout, uint64_t lse, uint64_t dqkv,
+                            uint64_t dq_acc, uint64_t delta, int batch, int seq, int heads, int causal,
+                            float scale, uint64_t status, uint64_t stream) {
+    check(attention_bwd(P<void>(qkv), P<void>(out), P<void>(dout), P<float>(lse), P<void>(dqkv),
+                        P<float>(dq_acc), P<float>(delta), batch, seq, heads, causal, scale,
+                        P<uint32_t>(status), S(stream)), "attention_bwd");
   });
 }
