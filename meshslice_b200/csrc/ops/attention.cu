@@ -578,18 +578,29 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constan
 
 constexpr size_t kAttnSmem = 6 * kTile + 256 + 1024;
 
+// The shared-memory attribute is per device: set it once on every device that launches.
+cudaError_t configure_device() {
+  static bool configured[64] = {false};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (dev >= 0 && dev < 64 && configured[dev]) return cudaSuccess;
+  e = cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kAttnSmem);
+  if (e != cudaSuccess) return e;
+  e = cudaFuncSetAttribute(attn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kAttnSmem);
+  if (e != cudaSuccess) return e;
+  if (dev >= 0 && dev < 64) configured[dev] = true;
+  return cudaSuccess;
+}
+
 }  // namespace
 
 cudaError_t attention_fwd(const void* qkv, void* out, float* lse, int batch, int seq, int heads,
                           int causal, float scale, uint32_t* status, cudaStream_t stream) {
   if (seq % kBlk != 0 || batch <= 0 || heads <= 0) return cudaErrorInvalidValue;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kAttnSmem);
+  {
+    cudaError_t e = configure_device();
     if (e != cudaSuccess) return e;
-    e = cudaFuncSetAttribute(attn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kAttnSmem);
-    if (e != cudaSuccess) return e;
-    configured = true;
   }
   CUtensorMap tm;
   const uint64_t width = (uint64_t)heads * 3 * kD;
@@ -611,11 +622,9 @@ cudaError_t attention_bwd(const void* qkv, const void* out, const void* dout, co
                           void* dqkv, float* dq_acc, float* delta, int batch, int seq, int heads,
                           int causal, float scale, uint32_t* status, cudaStream_t stream) {
   if (seq % kBlk != 0 || batch <= 0 || heads <= 0) return cudaErrorInvalidValue;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kAttnSmem);
-    if (e != cudaSuccess) return e;
-    configured = true;
+  {
+    cudaError_t e0 = configure_device();
+    if (e0 != cudaSuccess) return e0;
   }
   const int64_t tokens = (int64_t)batch * seq;
   cudaError_t e = cudaMemsetAsync(dq_acc, 0, tokens * heads * kD * sizeof(float), stream);

@@ -63,14 +63,14 @@ def test_gemm_bias_gelu_epilogue():
     from meshslice_b200.ops.gemm import gemm
     a, b = _operands(256, 512, 256, "nn")
     a = a * 0.1
-    bias = torch.randn(512, device="cuda").bfloat16()
+    bias = torch.randn(512, device="cuda", generator=torch.Generator(device="cuda").manual_seed(5)).bfloat16()
     pre = torch.empty(256, 512, device="cuda", dtype=torch.bfloat16)
     out = gemm(a, b, "nn", bias=bias, act="gelu", pre_act=pre)
     _native.check_status()
     h = _ref(a, b, "nn") + bias.float()
     _check(pre, h, 256)
-    ref = torch.nn.functional.gelu(pre.float(), approximate="tanh")
-    assert (out.float() - ref).abs().max().item() < 3e-2
+    ref = torch.nn.functional.gelu(h, approximate="tanh")   # the kernel applies GeLU to the fp32 sum
+    assert ((out.float() - ref).abs() <= 0.03 + 0.01 * ref.abs()).all()
 
 
 def test_gemm_many_tiles_persistent_schedule():
