@@ -23,7 +23,7 @@ CU_SOURCES = [
     "gemm/sm100_gemm.cu",
     "ops/ops.cu",
     "ops/attention.cu",
-    "ops/noalloc_reduce.cu",
+    "ops/attention_noalloc.cu",
     "comm/p2p.cu",
 ]
 CPP_SOURCES = ["bindings.cpp"]
