@@ -20,7 +20,10 @@ namespace msb {
 constexpr int kBM = 128;
 constexpr int kBN = 256;
 constexpr int kBK = 64;
-constexpr int kStages = 4;
+#ifndef MSB_STAGES
+#define MSB_STAGES 4
+#endif
+constexpr int kStages = MSB_STAGES;
 constexpr int kMaxPeers = 8;
 constexpr int kGemmThreads = 224;  // 7 warps: TMA, MMA, 4x epilogue, communication
 constexpr int kCommBufBytes = 8192;

@@ -1,0 +1,104 @@
+"""Stand-alone peer-to-peer collectives on the symmetric heap (the kernels of csrc/comm/p2p.cu)
+with NCCL twins for comparison.  They are the B200 counterparts of the collectives that
+BenchCollectives2D.py:16-26 times, along either mesh axis and on either tensor dimension.
+
+All three pull: a rank reads its peers' input buffers directly over NVLink, so the input must
+live in the symmetric heap (``P2PCollectives.input``); outputs are ordinary local tensors.
+"""
+from __future__ import annotations
+
+from typing import List
+
+import numpy as np
+import torch
+
+from .. import _native
+from . import runtime as rt
+from .mesh import DistMesh
+
+
+class P2PCollectives:
+    def __init__(self, mesh: DistMesh, heap: rt.SymmHeap, max_bytes: int, grid: int = 148, timeout_ns: int = 10_000_000_000):
+        self.mesh, self.heap, self.grid, self.timeout_ns = mesh, heap, grid, timeout_ns
+        self.C = _native.load()
+        self.flags = heap.alloc(rt.FLAG_WORDS * 4)
+        heap.bytes_view(self.flags, rt.FLAG_WORDS * 4).zero_()
+        self.inp_off = heap.alloc(max_bytes)
+        self.max_bytes = max_bytes
+        self.epoch = 0
+        self.done_total = 0
+        torch.cuda.synchronize()
+        mesh.dist.barrier()
+
+    def input(self, shape, dtype=torch.bfloat16) -> torch.Tensor:
+        """View of the symmetric input buffer; fill it before calling a collective."""
+        return self.heap.tensor(self.inp_off, shape, dtype)
+
+    def _bar(self, grid):
+        self.epoch += 1
+        self.done_total += grid
+        n = self.heap.world
+        f = lambda q, w: self.heap.ptr(q, self.flags + 4 * w)
+        return dict(n_ranks=n, my_rank=self.heap.rank, entry_flags=[f(q, rt.ENTRY0) for q in range(n)],
+                    exit_flags=[f(q, rt.EXIT0) for q in range(n)], epoch=self.epoch,
+                    go_flag=f(self.heap.rank, rt.GO), done_counter=f(self.heap.rank, rt.DONE),
+                    done_target=self.done_total, status=_native.status().dev, timeout_ns=self.timeout_ns)
+
+    def _peers(self, axis) -> List[int]:
+        m = self.mesh
+        return [m.r * m.C + c for c in range(m.C)] if axis == "col" else [r * m.C + m.c for r in range(m.R)]
+
+    def _copy(self, jobs):
+        jt, _ = rt.upload_jobs(jobs, [0, len(jobs)], torch.device("cuda", torch.cuda.current_device()))
+        self.C.p2p_copy(jt.data_ptr(), len(jobs), self._bar(self.grid), self.grid, _native.stream_ptr())
+        return jt
+
+    def all_gather(self, rows: int, cols: int, axis: str, dim: int, out: torch.Tensor = None):
+        """Gathers every peer's [rows, cols] bf16 input along ``axis`` and concatenates on ``dim``."""
+        peers = self._peers(axis)
+        n = len(peers)
+        shape = (rows * n, cols) if dim == 0 else (rows, cols * n)
+        if out is None:
+            out = torch.empty(shape, dtype=torch.bfloat16, device="cuda")
+        rb = cols * 2
+        jobs = []
+        for i, q in enumerate(peers):
+            src = self.heap.ptr(q, self.inp_off)
+            if dim == 0:
+                jobs.append((src, out.data_ptr() + i * rows * rb, rows, rb, rb, rb))
+            else:
+                jobs.append((src, out.data_ptr() + i * rb, rows, rb, rb, n * rb))
+        self._keep = self._copy(jobs)
+        return out
+
+    def send_recv(self, rows: int, cols: int, axis: str, out: torch.Tensor = None):
+        """Ring shift by +1: every rank receives the input of its predecessor along ``axis``."""
+        peers = self._peers(axis)
+        i = peers.index(self.heap.rank)
+        src = self.heap.ptr(peers[(i - 1) % len(peers)], self.inp_off)
+        if out is None:
+            out = torch.empty(rows, cols, dtype=torch.bfloat16, device="cuda")
+        rb = cols * 2
+        self._keep = self._copy([(src, out.data_ptr(), rows, rb, rb, rb)])
+        return out
+
+    def reduce_scatter(self, rows: int, cols: int, axis: str, dim: int, out: torch.Tensor = None):
+        """Sum of the peers' [rows, cols] inputs, this rank keeping its chunk along ``dim``."""
+        peers = self._peers(axis)
+        n = len(peers)
+        i = peers.index(self.heap.rank)
+        if dim == 0:
+            r_, c_ = rows // n, cols
+            off = i * r_ * cols * 2
+        else:
+            r_, c_ = rows, cols // n
+            off = i * c_ * 2
+        if out is None:
+            out = torch.empty(r_, c_, dtype=torch.bfloat16, device="cuda")
+        srcs = [self.heap.ptr(q, self.inp_off) + off for q in peers]
+        self.C.p2p_reduce(srcs, cols, out.data_ptr(), c_, r_, c_, self._bar(self.grid), self.grid,
+                          _native.stream_ptr())
+        return out
+
+    def barrier(self):
+        self.C.p2p_barrier(self._bar(1), _native.stream_ptr())
