@@ -62,7 +62,11 @@ class P2PCollectives:
             out = torch.empty(shape, dtype=torch.bfloat16, device="cuda")
         rb = cols * 2
         jobs = []
-        for i, q in enumerate(peers):
+        me = peers.index(self.heap.rank)
+        # every rank starts with a different peer so that no port serves all readers at once
+        for k in range(n):
+            i = (me + 1 + k) % n
+            q = peers[i]
             src = self.heap.ptr(q, self.inp_off)
             if dim == 0:
                 jobs.append((src, out.data_ptr() + i * rows * rb, rows, rb, rb, rb))
