@@ -205,7 +205,10 @@ class DistMesh(Mesh):
         if n == 1:
             return ShardedTensor(self, {(self.r, self.c): x})
         out = torch.empty((n,) + tuple(x.shape), dtype=x.dtype, device=x.device)
-        self.dist.all_gather_into_tensor(out, x, group=self._group(axis))
+        if x.is_cuda:
+            self.dist.all_gather_into_tensor(out, x, group=self._group(axis))
+        else:   # Gloo has no flat all-gather
+            self.dist.all_gather([out[i] for i in range(n)], x, group=self._group(axis))
         parts = [out[i] for i in range(n)]
         return ShardedTensor(self, {(self.r, self.c): torch.cat(parts, dim=dim) if dim != 0 else out.reshape(-1, *x.shape[1:])})
 
@@ -219,8 +222,12 @@ class DistMesh(Mesh):
         else:
             x = x.reshape(n, x.shape[0] // n, *x.shape[1:])
         x = x.contiguous()
-        out = torch.empty(x.shape[1:], dtype=x.dtype, device=x.device)
-        self.dist.reduce_scatter_tensor(out, x, group=self._group(axis))
+        if x.is_cuda:
+            out = torch.empty(x.shape[1:], dtype=x.dtype, device=x.device)
+            self.dist.reduce_scatter_tensor(out, x, group=self._group(axis))
+        else:   # Gloo has no reduce-scatter: all-reduce and keep the own chunk
+            self.dist.all_reduce(x, group=self._group(axis))
+            out = x[self._index(axis)].clone()
         return ShardedTensor(self, {(self.r, self.c): out})
 
     def all_reduce(self, st, axis, op="sum"):

@@ -1,0 +1,64 @@
+"""Host-side failure detection for a group of ranks.
+
+The reference has none (a failing ``jax.distributed.initialize`` simply raises).  Here every rank
+publishes a heartbeat (its step counter, or a departure notice) in the job's key-value store
+between steps, and checks its peers' entries before launching the next step: a rank that left or
+raised is reported as ``PeerLostError`` on every surviving rank *before* they enter a collective
+or a fused kernel that would wait for it.  Device-side waits are bounded separately (the kernels
+report a status code instead of spinning), so a lost peer can never hang a GPU.
+"""
+from __future__ import annotations
+
+import time
+from typing import Optional
+
+
+class PeerLostError(RuntimeError):
+    pass
+
+
+class Heartbeat:
+    def __init__(self, store, rank: int, world: int, prefix: str = "hb"):
+        self.store, self.rank, self.world, self.prefix = store, rank, world, prefix
+
+    def _key(self, r):
+        return f"{self.prefix}/{r}"
+
+    def beat(self, step: int):
+        self.store.set(self._key(self.rank), f"step:{step}")
+
+    def leave(self, reason: str = "left"):
+        """Publish a departure notice (call between steps, with nothing in flight)."""
+        self.store.set(self._key(self.rank), f"gone:{reason}")
+
+    def check(self, step: int, timeout_s: float = 5.0):
+        """Raises PeerLostError if a peer announced its departure or has not reached ``step``
+        within ``timeout_s``."""
+        deadline = time.time() + timeout_s
+        for r in range(self.world):
+            if r == self.rank:
+                continue
+            while True:
+                try:
+                    v = self.store.get(self._key(r)).decode()
+                except Exception:
+                    v = ""
+                if v.startswith("gone:"):
+                    raise PeerLostError(f"rank {r} left the job ({v[5:]}) before step {step}")
+                if v.startswith("step:") and int(v[5:]) >= step:
+                    break
+                if time.time() > deadline:
+                    raise PeerLostError(f"rank {r} did not reach step {step} within {timeout_s}s (last: {v or 'nothing'})")
+                time.sleep(0.02)
+
+
+def guarded_step(hb: Heartbeat, step: int, fn, timeout_s: float = 5.0):
+    """Heartbeat, check the peers, run ``fn``; on any exception publish a departure notice so
+    that the other ranks stop cleanly instead of waiting."""
+    hb.beat(step)
+    hb.check(step, timeout_s)
+    try:
+        return fn()
+    except Exception as e:
+        hb.leave(f"{type(e).__name__}: {e}")
+        raise
