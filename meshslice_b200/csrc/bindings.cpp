@@ -99,11 +99,13 @@ void gemm_run(const py::dict& d) {
   if (a.group < 1) a.group = 1;
   if (geti(d, "no_tiles")) a.tiles_m = 0;  // reduce phase only
   // pull side
-  a.jobs = P<const CopyJob>(getp(d, "jobs"));
-  a.chunk_job_begin = P<const int>(getp(d, "chunk_job_begin"));
+  a.jobs = P<const PushJob>(getp(d, "jobs"));
+  a.chunks = P<const ChunkDesc>(getp(d, "chunks"));
+  a.skip_comm = (int)geti(d, "skip_comm");
+  a.gather_src[0] = P<const char>(getp(d, "gather_src0"));
+  a.gather_src[1] = P<const char>(getp(d, "gather_src1"));
   a.n_chunks = (int)geti(d, "n_chunks");
   a.chunk_flags = P<uint32_t>(getp(d, "chunk_flags"));
-  a.chunk_target = (uint32_t)geti(d, "chunk_target");
   a.a_flag_mode = (int)geti(d, "a_flag_mode");
   a.a_flag_base = (int)geti(d, "a_flag_base");
   a.a_flag_count = (int)geti(d, "a_flag_count");
@@ -225,6 +227,8 @@ PYBIND11_MODULE(_C, m) {
   m.attr("BK") = kBK;
   m.attr("MAX_PEERS") = kMaxPeers;
   m.attr("COPY_JOB_BYTES") = (int)sizeof(CopyJob);
+  m.attr("PUSH_JOB_BYTES") = (int)sizeof(PushJob);
+  m.attr("CHUNK_DESC_BYTES") = (int)sizeof(ChunkDesc);
 
   m.def("gemm_run", &gemm_run, "persistent tcgen05 GEMM with optional fused pull / push");
   m.def("symm_alloc", &symm_alloc);

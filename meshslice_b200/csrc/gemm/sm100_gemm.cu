@@ -88,13 +88,16 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 __device__ __forceinline__ float bf16_lo(uint32_t v) { return __uint_as_float(v << 16); }
 __device__ __forceinline__ float bf16_hi(uint32_t v) { return __uint_as_float(v & 0xffff0000u); }
 
-// Waits for the chunk flags of one operand.  Returns false on timeout.
+// Waits for the chunk flags of one operand (bumped by this GPU's and by peers' CTAs).
+__device__ __forceinline__ bool wait_chunk(const GemmArgs& a, int idx, uint64_t tmo) {
+  return wait_flag_geq_sys(a.chunk_flags + idx, a.chunks[idx].target, tmo);
+}
 __device__ __forceinline__ bool wait_operand(const GemmArgs& a, int mode, int base, int count,
                                              int slice, uint64_t tmo) {
   if (mode == 0) return true;
-  if (mode == 1) return wait_flag_geq_gpu(a.chunk_flags + base + slice, a.chunk_target, tmo);
+  if (mode == 1) return wait_chunk(a, base + slice, tmo);
   for (int i = 0; i < count; ++i)
-    if (!wait_flag_geq_gpu(a.chunk_flags + base + i, a.chunk_target, tmo)) return false;
+    if (!wait_chunk(a, base + i, tmo)) return false;
   return true;
 }
 
@@ -103,14 +106,16 @@ __device__ __forceinline__ bool wait_operand(const GemmArgs& a, int mode, int ba
 // ------------------------------------------------------------------------------------------
 struct Piece {
   const char* src;
-  char* dst;
   uint32_t rows;
   uint32_t row_bytes;
   uint64_t sp, dp;
+  uint64_t dst_off;       // byte offset of this piece inside every destination block
+  const PushJob* job;
 };
 
 struct PieceCursor {
-  const CopyJob* jobs;
+  const PushJob* jobs;
+  const char* srcs[2];
   int job, job_end;
   uint32_t next_in_job;   // next piece index of this CTA inside the current job
   uint32_t pieces_in_job;
@@ -118,7 +123,7 @@ struct PieceCursor {
   uint32_t running;       // pieces of earlier jobs of the chunk (for the round-robin)
   __device__ void open_job() {
     while (job < job_end) {
-      const CopyJob& j = jobs[job];
+      const PushJob& j = jobs[job];
       if (j.row_bytes >= (uint32_t)kCommBufBytes) {
         segs_per_row = (j.row_bytes + kCommBufBytes - 1) / kCommBufBytes;
         rows_per_piece = 1;
@@ -135,8 +140,10 @@ struct PieceCursor {
       ++job;
     }
   }
-  __device__ void init(const CopyJob* js, int jb, int je) {
+  __device__ void init(const PushJob* js, const char* const* bases, int jb, int je) {
     jobs = js;
+    srcs[0] = bases[0];
+    srcs[1] = bases[1];
     job = jb;
     job_end = je;
     running = 0;
@@ -144,24 +151,26 @@ struct PieceCursor {
   }
   __device__ bool next(Piece& p) {
     if (job >= job_end) return false;
-    const CopyJob& j = jobs[job];
+    const PushJob& j = jobs[job];
+    const char* base = srcs[j.src_sel & 1];
     const uint32_t idx = next_in_job;
     if (segs_per_row > 1) {
       const uint32_t row = idx / segs_per_row, seg = idx - row * segs_per_row;
       const uint32_t off = seg * kCommBufBytes;
-      p.src = j.src + (uint64_t)row * j.src_pitch + off;
-      p.dst = j.dst + (uint64_t)row * j.dst_pitch + off;
+      p.src = base + j.src_off + (uint64_t)row * j.src_pitch + off;
+      p.dst_off = (uint64_t)row * j.dst_pitch + off;
       p.rows = 1;
       p.row_bytes = min((uint32_t)kCommBufBytes, j.row_bytes - off);
     } else {
       const uint32_t row0 = idx * rows_per_piece;
-      p.src = j.src + (uint64_t)row0 * j.src_pitch;
-      p.dst = j.dst + (uint64_t)row0 * j.dst_pitch;
+      p.src = base + j.src_off + (uint64_t)row0 * j.src_pitch;
+      p.dst_off = (uint64_t)row0 * j.dst_pitch;
       p.rows = min(rows_per_piece, j.rows - row0);
       p.row_bytes = j.row_bytes;
     }
     p.sp = j.src_pitch;
     p.dp = j.dst_pitch;
+    p.job = &j;
     next_in_job += gridDim.x;
     if (next_in_job >= pieces_in_job) {
       running += pieces_in_job;
@@ -201,20 +210,21 @@ __device__ void comm_warp_main(const GemmArgs& a, uint8_t* comm_smem, uint64_t* 
     }
   }
 
-  // ---- pull side
-  if (lane == 0 && ok && a.n_chunks > 0) {
+  // ---- gather side: read a piece of the local shard once, write it to every GPU of the group
+  if (lane == 0 && ok && a.n_chunks > 0 && !a.skip_comm) {
     uint32_t issued = 0, stored = 0;
     Piece q[kCommBufs];
     for (int c = 0; c < a.n_chunks && ok; ++c) {
+      const ChunkDesc& cd = a.chunks[c];
       PieceCursor cur;
-      cur.init(a.jobs, a.chunk_job_begin[c], a.chunk_job_begin[c + 1]);
+      cur.init(a.jobs, a.gather_src, cd.job_begin, cd.job_end);
       bool more = true;
       while (ok) {
         while (more && issued - stored < 2) {
           Piece p;
           more = cur.next(p);
           if (!more) break;
-          bulk_wait_read<2>();  // the store that last read this buffer has finished
+          bulk_wait_read<2>();  // the stores that last read this buffer have finished reading
           const uint32_t b = issued % kCommBufs;
           uint8_t* buf = comm_smem + b * kCommBufBytes;
           const uint32_t total = p.rows * p.row_bytes;
@@ -237,24 +247,30 @@ __device__ void comm_warp_main(const GemmArgs& a, uint8_t* comm_smem, uint64_t* 
         }
         const Piece& p = q[b];
         const uint8_t* buf = comm_smem + b * kCommBufBytes;
-        if (p.rows == 1 || p.dp == p.row_bytes) {
-          bulk_s2g(p.dst, buf, p.rows * p.row_bytes);
-        } else {
-          for (uint32_t r = 0; r < p.rows; ++r)
-            bulk_s2g(p.dst + r * p.dp, buf + r * p.row_bytes, p.row_bytes);
+        const PushJob& jb = *p.job;
+        for (uint32_t d = 0; d < jb.n_dst; ++d) {
+          char* dst = jb.dst[d] + p.dst_off;
+          if (p.rows == 1 || p.dp == p.row_bytes) {
+            bulk_s2g(dst, buf, p.rows * p.row_bytes);
+          } else {
+            for (uint32_t r = 0; r < p.rows; ++r)
+              bulk_s2g(dst + r * p.dp, buf + r * p.row_bytes, p.row_bytes);
+          }
         }
-        bulk_commit();
+        bulk_commit();   // one group per piece, whatever the number of destinations
         ++stored;
       }
+      // this CTA's share of the chunk has been written everywhere: tell every destination
       bulk_wait_all<0>();
       fence_proxy_async();
-      __threadfence();
-      if (ok) red_add_release_gpu(a.chunk_flags + c, 1u);
+      __threadfence_system();
+      if (ok)
+        for (uint32_t d = 0; d < cd.n_sig; ++d) red_add_release_sys(cd.sig[d], 1u);
     }
     bulk_wait_all<0>();
   }
 
-  // ---- exit barrier: peers may overwrite their shards only after everybody stopped pulling
+  // ---- optional exit barrier: nobody leaves before every rank has finished its transfers
   if (a.n_ranks > 0 && a.exit_barrier) {
     if (lane == 0) red_add_release_gpu(a.done_counter, 1u);
     if (blockIdx.x == 0) {

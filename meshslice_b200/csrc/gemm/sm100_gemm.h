@@ -2,14 +2,15 @@
 //
 // One kernel computes  C[M,N] = op(A) * op(B)  (bf16 inputs, fp32 accumulation in TMEM) and,
 // when asked to, also moves the data of the surrounding 2-D tensor-parallel collectives:
-//   * "pull" side (all-gather -> GEMM): a communication warp in every CTA copies chunks of
-//     peer shards into this GPU's staging buffer with untiled bulk copies and publishes one
-//     flag per chunk; the TMA producer warp waits for the flag of the chunk a tile needs.
+//   * gather side (all-gather -> GEMM): a communication warp in every CTA reads chunks of this
+//     GPU's shard and writes them into the staging buffers of all GPUs of the group with posted
+//     bulk stores over NVLink, then bumps one flag per chunk on each of them; the TMA producer
+//     warp waits for the flag of the chunk a tile needs.
 //   * "push" side (GEMM -> reduce-scatter): the epilogue stores each partial tile straight
 //     into the slot buffer of the GPU that owns it (peer stores over NVLink), bumps a
 //     per-slice counter there, and a trailing phase on the owner sums the slots.
 // This covers the three MeshSlice dataflows of the reference (TensorParallel.py:153-214):
-// OS = pull A and B, LS = pull B and push over columns, RS = pull A and push over rows.
+// OS = gather A and B, LS = gather B and push over columns, RS = gather A and push over rows.
 #pragma once
 #include <cuda.h>
 #include <cuda_runtime.h>
@@ -44,10 +45,34 @@ enum GemmStatus : uint32_t {
   kTimeoutGo = 10,        // CTA waited too long for the local "peers are ready" flag
 };
 
-// One 2-D copy of the pull side.  All addresses 16-byte aligned, row_bytes % 16 == 0.
+// One 2-D copy of the gather side: a block of THIS GPU's shard is read once and written into
+// the staging buffer of every GPU of the gathering group (own GPU included) with posted bulk
+// stores over NVLink.  All addresses 16-byte aligned, row_bytes % 16 == 0.
+struct PushJob {
+  uint64_t src_off;       // byte offset inside the local source tensor gather_src[src_sel]
+  uint32_t rows;
+  uint32_t row_bytes;
+  uint64_t src_pitch;
+  uint64_t dst_pitch;
+  uint32_t n_dst;
+  uint32_t src_sel;       // which of GemmArgs::gather_src holds the block
+  char* dst[kMaxPeers];   // same block inside each destination GPU's staging buffer
+};
+
+// One chunk of the gather: its jobs, the flag word to bump on every destination GPU once this
+// CTA's share of the chunk has landed there, and the flag value that means "complete" on the
+// consumer (CTAs per GPU x GPUs contributing to the chunk).
+struct ChunkDesc {
+  int job_begin, job_end;
+  uint32_t n_sig;
+  uint32_t target;
+  uint32_t* sig[kMaxPeers];
+};
+
+// One 2-D copy by pulling (stand-alone P2P collectives): src may be peer memory.
 struct CopyJob {
-  const char* src;  // peer (or local) memory
-  char* dst;        // local staging
+  const char* src;
+  char* dst;
   uint32_t rows;
   uint32_t row_bytes;
   uint64_t src_pitch;
@@ -73,12 +98,13 @@ struct GemmArgs {
   int n_slices;        // block-cyclic slices of the sliced dimension (divides its tile count)
   int group;           // raster group size along the sliced dimension
   int cyc;             // tiles per cyclic block: slice s holds blocks (g*n_slices + s)*cyc + w
-  // ---- pull side ----
-  const CopyJob* jobs;
-  const int* chunk_job_begin;  // [n_chunks + 1]
+  // ---- gather side (all-gather -> GEMM) ----
+  const PushJob* jobs;
+  const char* gather_src[2];   // local shards the jobs read from (so plans do not depend on them)
+  const ChunkDesc* chunks;     // [n_chunks]
   int n_chunks;
-  uint32_t* chunk_flags;       // [n_chunks] monotonic; each launch adds gridDim.x to each
-  uint32_t chunk_target;       // value that marks "complete" for this launch
+  int skip_comm;               // 1: this launch moves no data (the chunks were filled earlier)
+  uint32_t* chunk_flags;       // [n_chunks] local flags, bumped by every contributing CTA
   int a_flag_mode;             // 0: none, 1: flag a_flag_base + slice(tile), 2: all of [base, base+count)
   int a_flag_base, a_flag_count;
   int b_flag_mode;

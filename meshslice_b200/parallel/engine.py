@@ -1,9 +1,8 @@
 """Fused engine of one rank: owns the symmetric heap and workspace and exposes the three
 MeshSlice dataflows on local shards, with in-kernel NVLink traffic (no NCCL on these paths).
 
-Operands that peers pull (gathered operands) must live in the symmetric heap.  Parameters are
-allocated there; an activation that is not is first copied into a send buffer of the heap on
-the caller's stream.  When a shape breaks the tile divisibility rules of the fused kernel the
+Gathered operands are pushed: every rank reads its own shard (any device tensor) and writes it
+into the peers' staging buffers, so only the workspace lives in the symmetric heap.  When a shape breaks the tile divisibility rules of the fused kernel the
 engine falls back to the generic collective formulation (NCCL + local tcgen05 GEMM) and says
 so once.
 """
@@ -39,17 +38,15 @@ class FusedEngine:
         mesh.engine = self
 
     # ------------------------------------------------------------------ helpers
-    def _pull_ptrs(self, t: torch.Tensor, ranks, send_off: int):
-        """Pointers of every peer's copy of ``t`` (own copy included)."""
-        t = t.contiguous()
-        off = self.heap.offset_of(t)
-        if off is None:
-            nbytes = t.numel() * t.element_size()
-            if nbytes > self.ws.send_bytes:
-                raise FusedPlanError("operand larger than the send buffer")
-            self.heap.bytes_view(send_off, nbytes).view(t.dtype).view(t.shape).copy_(t)
-            off = send_off
-        return [self.heap.ptr(q, off) for q in ranks]
+    @staticmethod
+    def _own(t: torch.Tensor, n: int, idx: int):
+        """Pointer list indexed by the position along the gathering axis; only this rank's own
+        shard is read by its kernel (it is pushed to the peers), so only that entry is set."""
+        if t.data_ptr() % 16:
+            raise FusedPlanError("gathered operand must be 16-byte aligned")
+        lst = [0] * n
+        lst[idx] = t.data_ptr()
+        return lst
 
     def _fallback(self, which, err, X, W, n_slices):
         if which not in self._warned:
@@ -72,8 +69,9 @@ class FusedEngine:
         if out is None:
             out = torch.empty(m, n, dtype=torch.bfloat16, device=X.device)
         try:
-            xp = self._pull_ptrs(X, self.coord.row_peers(), self.ws.send_a)
-            wp = self._pull_ptrs(W, self.coord.col_peers(), self.ws.send_b)
+            X, W = X.contiguous(), W.contiguous()
+            xp = self._own(X, self.mesh.C, self.mesh.c)
+            wp = self._own(W, self.mesh.R, self.mesh.r)
             return self.fg.os(xp, wp, m, kl, kr, n, out, n_slices=n_slices, accumulate=accumulate,
                               bias=bias, act=act, pre_act=pre_act)
         except FusedPlanError as e:
@@ -92,7 +90,8 @@ class FusedEngine:
         if out is None:
             out = torch.empty(m, N // self.mesh.C, dtype=torch.bfloat16, device=X.device)
         try:
-            wp = self._pull_ptrs(W, self.coord.col_peers(), self.ws.send_b)
+            W = W.contiguous()
+            wp = self._own(W, self.mesh.R, self.mesh.r)
             return self.fg.ls(X.contiguous(), wp, m, kl, nr, out, n_slices=n_slices, accumulate=accumulate)
         except FusedPlanError as e:
             y = self._fallback("ls", e, X, W, n_slices)
@@ -108,7 +107,8 @@ class FusedEngine:
         if out is None:
             out = torch.empty(M // self.mesh.R, n, dtype=torch.bfloat16, device=X.device)
         try:
-            xp = self._pull_ptrs(X, self.coord.row_peers(), self.ws.send_a)
+            X = X.contiguous()
+            xp = self._own(X, self.mesh.C, self.mesh.c)
             return self.fg.rs(xp, W.contiguous(), kr, ml, n, out, n_slices=n_slices, accumulate=accumulate)
         except FusedPlanError as e:
             y = self._fallback("rs", e, X, W, n_slices)

@@ -105,18 +105,24 @@ class FusedGemm:
 
     def _jobs(self, key, builder):
         if key not in self._cache:
-            jobs, begin = builder()
+            jobs, chunks = builder()
             dev = torch.device("cuda", torch.cuda.current_device())
-            self._cache[key] = rt.upload_jobs(jobs, begin, dev) + (len(begin) - 1,)
+            self._cache[key] = rt.upload_push_plan(jobs, chunks, dev) + (len(chunks),)
         return self._cache[key]
 
+    def _chunk_flag(self, rank: int, idx: int) -> int:
+        return self.world.flag_ptr(rank, rt.CHUNK0 + idx)
+
     def _launch(self, d, exit_barrier, phase="all", reset=True):
-        """phase 'gemm' leaves out the reduce phase and 'reduce' runs only it; together with
-        reset=False this lets a test run several emulated ranks one after another on one GPU."""
+        """phases 'comm' (gather only), 'gemm' (tiles only) and 'reduce' (slot sums only) split one
+        launch in three; together with reset=False this lets a test run several emulated ranks
+        one after another on one GPU without any launch waiting for a kernel that is not running."""
         if reset:
             self._reset_flags(d["stream"])
-        if phase == "gemm":
-            d["red_n"] = 0
+        if phase == "comm":          # only move the gathered operands
+            d.update(no_tiles=1, red_n=0, push_n=0)
+        elif phase == "gemm":        # tiles only: the chunks were filled by an earlier 'comm' launch
+            d.update(red_n=0, skip_comm=1)
         elif phase == "reduce":
             d.update(no_tiles=1, n_chunks=0, push_n=0, a_flag_mode=0, b_flag_mode=0)
         if self.use_barriers:
@@ -125,7 +131,8 @@ class FusedGemm:
 
     # ------------------------------------------------------------------ OS
     def os(self, x_ptrs: List[int], w_ptrs: List[int], m: int, kl: int, kr: int, n: int, out,
-           n_slices: int = 4, accumulate: bool = False, bias=None, act=None, pre_act=None):
+           n_slices: int = 4, accumulate: bool = False, bias=None, act=None, pre_act=None,
+           phase: str = "all", reset: bool = True):
         """Y[m, n] = concat_c(X_c)[m, C*kl] @ concat_r(W_r)[R*kr, n];  C*kl == R*kr."""
         mc, ws = self.mesh, self.world.mine
         Kd = mc.C * kl
@@ -138,35 +145,40 @@ class FusedGemm:
         stream = _native.stream_ptr()
         xg, wg = ws.local(ws.stage_a), ws.local(ws.stage_b)
 
+        rowp, colp = mc.row_peers(), mc.col_peers()
+        x_mine, w_mine = x_ptrs[mc.c], w_ptrs[mc.r]
+
         def build():
-            jobs, begin = [], [0]
-            for r in range(mc.R):  # chunk 0: the whole gathered W
-                jobs.append((w_ptrs[r], wg + r * kr * n * 2, kr, n * 2, n * 2, n * 2))
-            begin.append(len(jobs))
-            for s in range(S):     # chunks 1..S: row blocks of X, block-cyclic
+            jobs, chunks = [], []
+            # chunk 0: this rank's W shard goes to every GPU of its mesh column
+            jobs.append((1, 0, kr, n * 2, n * 2, n * 2,
+                         [self.world.ptr(q, ws.stage_b) + mc.r * kr * n * 2 for q in colp]))
+            chunks.append((0, 1, [self._chunk_flag(q, 0) for q in colp], self.grid * mc.R))
+            for s in range(S):     # chunks 1..S: row blocks of this rank's X shard, block-cyclic
+                jb = len(jobs)
                 for blk in range(s, tiles_m, S):
                     row0 = blk * BM
                     rows = min(BM, m - row0)
-                    for c in range(mc.C):
-                        jobs.append((x_ptrs[c] + row0 * kl * 2, xg + row0 * Kd * 2 + c * kl * 2, rows,
-                                     kl * 2, kl * 2, Kd * 2))
-                begin.append(len(jobs))
-            return jobs, begin
+                    jobs.append((0, row0 * kl * 2, rows, kl * 2, kl * 2, Kd * 2,
+                                 [self.world.ptr(q, ws.stage_a) + row0 * Kd * 2 + mc.c * kl * 2 for q in rowp]))
+                chunks.append((jb, len(jobs), [self._chunk_flag(q, 1 + s) for q in rowp], self.grid * mc.C))
+            return jobs, chunks
 
-        jt, bt, n_chunks = self._jobs(("os", tuple(x_ptrs), tuple(w_ptrs), m, kl, kr, n, S), build)
+        jt, ct, n_chunks = self._jobs(("os", m, kl, kr, n, S), build)
         d = self._common(out, accumulate, stream)
         d.update(M=m, N=n, K=Kd, A=xg, B=wg, lda=Kd, ldb=n, a_mn_major=0, b_mn_major=1,
                  slice_dim=0, n_slices=S, cyc=1, group=8,
-                 jobs=jt.data_ptr(), chunk_job_begin=bt.data_ptr(), n_chunks=n_chunks,
-                 chunk_flags=ws.local(ws.flags + 4 * rt.CHUNK0), chunk_target=self.grid,
-                 a_flag_mode=1, a_flag_base=1, b_flag_mode=2, b_flag_base=0, b_flag_count=1)
+                 jobs=jt.data_ptr(), chunks=ct.data_ptr(), n_chunks=n_chunks,
+                 chunk_flags=ws.local(ws.flags + 4 * rt.CHUNK0),
+                 a_flag_mode=1, a_flag_base=1, b_flag_mode=2, b_flag_base=0, b_flag_count=1,
+                 gather_src0=x_mine, gather_src1=w_mine)
         if bias is not None:
             d["bias"] = bias.data_ptr()
         if act == "gelu":
             d["act"] = 1
             if pre_act is not None:
                 d["C_pre"] = pre_act.data_ptr()
-        self._launch(d, exit_barrier=True)
+        self._launch(d, exit_barrier=False, phase=phase, reset=reset)
         return out
 
     # ------------------------------------------------------------------ LS
@@ -189,32 +201,37 @@ class FusedGemm:
         stream = _native.stream_ptr()
         wg = ws.local(ws.stage_b)
 
+        colp = mc.col_peers()
+        w_mine = w_ptrs[mc.r]
+
         def build():
-            jobs, begin = [], [0]
-            for s in range(S):
+            jobs, chunks = [], []
+            for s in range(S):     # n-blocks of this rank's W shard that belong to slice s
+                jb = len(jobs)
                 for blk in range(s, tiles_n, S):
                     row0 = blk * BN
-                    r = row0 // nr
-                    jobs.append((w_ptrs[r] + (row0 - r * nr) * kl * 2, wg + row0 * kl * 2, BN, kl * 2,
-                                 kl * 2, kl * 2))
-                begin.append(len(jobs))
-            return jobs, begin
+                    if row0 // nr != mc.r:
+                        continue
+                    jobs.append((1, (row0 - mc.r * nr) * kl * 2, BN, kl * 2, kl * 2, kl * 2,
+                                 [self.world.ptr(q, ws.stage_b) + row0 * kl * 2 for q in colp]))
+                chunks.append((jb, len(jobs), [self._chunk_flag(q, s) for q in colp], self.grid * mc.R))
+            return jobs, chunks
 
-        jt, bt, n_chunks = self._jobs(("ls", tuple(w_ptrs), m, kl, nr, S), build)
+        jt, ct, n_chunks = self._jobs(("ls", m, kl, nr, S), build)
         peers = mc.row_peers()  # owners of the output column blocks, indexed by column
         d = self._common(out, accumulate, stream)
         d.update(M=m, N=N, K=kl, A=x.data_ptr(), B=wg, lda=x.stride(0), ldb=kl, a_mn_major=0,
                  b_mn_major=0, slice_dim=1, n_slices=S, cyc=1, group=4,
-                 jobs=jt.data_ptr(), chunk_job_begin=bt.data_ptr(), n_chunks=n_chunks,
-                 chunk_flags=ws.local(ws.flags + 4 * rt.CHUNK0), chunk_target=self.grid,
-                 b_flag_mode=1, b_flag_base=0,
+                 jobs=jt.data_ptr(), chunks=ct.data_ptr(), n_chunks=n_chunks,
+                 chunk_flags=ws.local(ws.flags + 4 * rt.CHUNK0),
+                 b_flag_mode=1, b_flag_base=0, gather_src1=w_mine,
                  push_n=mc.C, push_dim=1, push_extent=nc, push_ld=nc,
                  push_base=[self.world.ptr(q, ws.slots) + mc.c * m * nc * 2 for q in peers],
                  push_counter=[self.world.flag_ptr(q, rt.COUNTER0) for q in peers],
                  red_n=mc.C, red_slots=ws.local(ws.slots), red_rows=m, red_cols=nc, red_ld=nc,
                  red_counter=ws.local(ws.flags + 4 * rt.COUNTER0),
                  red_target=mc.C * (blocks_own // S) * tiles_m * 4, red_slice_dim=1)
-        self._launch(d, exit_barrier=True, phase=phase, reset=reset)
+        self._launch(d, exit_barrier=False, phase=phase, reset=reset)
         return out
 
     # ------------------------------------------------------------------ RS
@@ -239,31 +256,36 @@ class FusedGemm:
         stream = _native.stream_ptr()
         xg = ws.local(ws.stage_a)
 
+        rowp = mc.row_peers()
+        x_mine = x_ptrs[mc.c]
+
         def build():
-            jobs, begin = [], [0]
+            jobs, chunks = [], []
             ngroups = tiles_m // (S * cyc)
-            for s in range(S):
+            for s in range(S):     # column groups of this rank's X shard that belong to slice s
+                jb = len(jobs)
                 for cg in range(ngroups):
                     col0 = (cg * S + s) * cyc * BM
-                    c = col0 // ml
-                    jobs.append((x_ptrs[c] + (col0 - c * ml) * 2, xg + col0 * 2, kr, cyc * BM * 2,
-                                 ml * 2, M * 2))
-                begin.append(len(jobs))
-            return jobs, begin
+                    if col0 // ml != mc.c:
+                        continue
+                    jobs.append((0, (col0 - mc.c * ml) * 2, kr, cyc * BM * 2, ml * 2, M * 2,
+                                 [self.world.ptr(q, ws.stage_a) + col0 * 2 for q in rowp]))
+                chunks.append((jb, len(jobs), [self._chunk_flag(q, s) for q in rowp], self.grid * mc.C))
+            return jobs, chunks
 
-        jt, bt, n_chunks = self._jobs(("rs", tuple(x_ptrs), kr, ml, n, S, cyc), build)
+        jt, ct, n_chunks = self._jobs(("rs", kr, ml, n, S, cyc), build)
         peers = mc.col_peers()  # owners of the output row blocks, indexed by row
         d = self._common(out, accumulate, stream)
         d.update(M=M, N=n, K=kr, A=xg, B=w.data_ptr(), lda=M, ldb=w.stride(0), a_mn_major=1,
                  b_mn_major=1, slice_dim=0, n_slices=S, cyc=cyc, group=8,
-                 jobs=jt.data_ptr(), chunk_job_begin=bt.data_ptr(), n_chunks=n_chunks,
-                 chunk_flags=ws.local(ws.flags + 4 * rt.CHUNK0), chunk_target=self.grid,
-                 a_flag_mode=1, a_flag_base=0,
+                 jobs=jt.data_ptr(), chunks=ct.data_ptr(), n_chunks=n_chunks,
+                 chunk_flags=ws.local(ws.flags + 4 * rt.CHUNK0),
+                 a_flag_mode=1, a_flag_base=0, gather_src0=x_mine,
                  push_n=mc.R, push_dim=0, push_extent=mr, push_ld=n,
                  push_base=[self.world.ptr(q, ws.slots) + mc.r * mr * n * 2 for q in peers],
                  push_counter=[self.world.flag_ptr(q, rt.COUNTER0) for q in peers],
                  red_n=mc.R, red_slots=ws.local(ws.slots), red_rows=mr, red_cols=n, red_ld=n,
                  red_counter=ws.local(ws.flags + 4 * rt.COUNTER0),
                  red_target=mc.R * ((mr // BM) // S) * tiles_n * 4, red_slice_dim=0)
-        self._launch(d, exit_barrier=True, phase=phase, reset=reset)
+        self._launch(d, exit_barrier=False, phase=phase, reset=reset)
         return out

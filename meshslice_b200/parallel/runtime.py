@@ -164,12 +164,37 @@ class World:
 
 JOB_DTYPE = np.dtype([("src", "<u8"), ("dst", "<u8"), ("rows", "<u4"), ("row_bytes", "<u4"),
                       ("sp", "<u8"), ("dp", "<u8")])
+PUSH_DTYPE = np.dtype([("src", "<u8"), ("rows", "<u4"), ("row_bytes", "<u4"), ("sp", "<u8"), ("dp", "<u8"),
+                       ("n_dst", "<u4"), ("src_sel", "<u4"), ("dst", "<u8", (8,))])
+CHUNK_DTYPE = np.dtype([("job_begin", "<i4"), ("job_end", "<i4"), ("n_sig", "<u4"), ("target", "<u4"),
+                        ("sig", "<u8", (8,))])
 
 
 def upload_jobs(jobs: List[tuple], chunk_begin: List[int], device) -> tuple:
-    """Copies a job list and its chunk index to the device.  Returns (jobs_t, begin_t)."""
+    """Pull jobs of the stand-alone P2P collectives: (src, dst, rows, row_bytes, sp, dp)."""
     arr = np.array(jobs, dtype=JOB_DTYPE)
     assert arr.dtype.itemsize == _native.load().COPY_JOB_BYTES
     jt = torch.from_numpy(arr.view(np.uint8).copy()).to(device)
     bt = torch.tensor(chunk_begin, dtype=torch.int32, device=device)
     return jt, bt
+
+
+def upload_push_plan(jobs: List[tuple], chunks: List[tuple], device) -> tuple:
+    """Gather plan of the fused kernel.
+    jobs:   (src_sel, src_offset, rows, row_bytes, src_pitch, dst_pitch, [dst pointers])
+    chunks: (job_begin, job_end, [flag pointers], target)"""
+    C = _native.load()
+    ja = np.zeros(len(jobs), dtype=PUSH_DTYPE)
+    for i, (sel, src, rows, rb, sp, dp, dsts) in enumerate(jobs):
+        ja[i]["src"], ja[i]["rows"], ja[i]["row_bytes"], ja[i]["sp"], ja[i]["dp"] = src, rows, rb, sp, dp
+        ja[i]["src_sel"] = sel
+        ja[i]["n_dst"] = len(dsts)
+        ja[i]["dst"][:len(dsts)] = dsts
+    ca = np.zeros(len(chunks), dtype=CHUNK_DTYPE)
+    for i, (jb, je, sigs, target) in enumerate(chunks):
+        ca[i]["job_begin"], ca[i]["job_end"], ca[i]["n_sig"], ca[i]["target"] = jb, je, len(sigs), target
+        ca[i]["sig"][:len(sigs)] = sigs
+    assert ja.dtype.itemsize == C.PUSH_JOB_BYTES and ca.dtype.itemsize == C.CHUNK_DESC_BYTES
+    jt = torch.from_numpy(ja.view(np.uint8).copy()).to(device)
+    ct = torch.from_numpy(ca.view(np.uint8).copy()).to(device)
+    return jt, ct

@@ -2,8 +2,8 @@
 
 Several mesh ranks are emulated one after another: every emulated rank has its own heap and
 workspace on the same device, "peer" pointers point into the other emulated ranks' buffers, and
-the cross-GPU barriers are switched off.  The push dataflows run their GEMM phase for every rank
-first and the reduce phase afterwards, so no launch ever waits for a kernel that is not running.
+the cross-GPU barriers are switched off.  Every dataflow runs in phases over all emulated ranks
+(gather, then tiles, then slot sums), so no launch ever waits for a kernel that is not running.
 """
 import pytest
 import torch
@@ -46,11 +46,15 @@ def test_os_pull_both_operands(mesh, slices):
     wsd = {(r, c): W[r * kr:(r + 1) * kr, c * n:(c + 1) * n].contiguous() for r in range(R) for c in range(C)}
     ops, _ = _setup(R, C, m * Kd * 2, Kd * n * 2, 16)
     ref = X.float() @ W.float()
-    for (r, c), op in ops.items():
-        out = torch.empty(m, n, device="cuda", dtype=torch.bfloat16)
-        op.os([xs[(r, cc)].data_ptr() for cc in range(C)], [wsd[(rr, c)].data_ptr() for rr in range(R)],
-              m, kl, kr, n, out, n_slices=slices)
-        _native.check_status()
+    outs = {k: torch.empty(m, n, device="cuda", dtype=torch.bfloat16) for k in ops}
+    for op in ops.values():
+        op._reset_flags(_native.stream_ptr())
+    for phase in ("comm", "gemm"):
+        for (r, c), op in ops.items():
+            op.os([xs[(r, cc)].data_ptr() for cc in range(C)], [wsd[(rr, c)].data_ptr() for rr in range(R)],
+                  m, kl, kr, n, outs[(r, c)], n_slices=slices, phase=phase, reset=False)
+            _native.check_status()
+    for (r, c), out in outs.items():
         _close(out, ref[r * m:(r + 1) * m, c * n:(c + 1) * n], Kd)
 
 
@@ -69,7 +73,7 @@ def test_ls_pull_weights_push_over_row(mesh, slices):
     outs = {k: torch.empty(m, nc, device="cuda", dtype=torch.bfloat16) for k in ops}
     for op in ops.values():
         op._reset_flags(_native.stream_ptr())
-    for phase in ("gemm", "reduce"):
+    for phase in ("comm", "gemm", "reduce"):
         for (r, c), op in ops.items():
             op.ls(xs[(r, c)], [wsd[(rr, c)].data_ptr() for rr in range(R)], m, kl, nr, outs[(r, c)],
                   n_slices=slices, phase=phase, reset=False)
@@ -93,7 +97,7 @@ def test_rs_pull_inputs_push_over_column(mesh, slices, cyc):
     outs = {k: torch.empty(mr, n, device="cuda", dtype=torch.bfloat16) for k in ops}
     for op in ops.values():
         op._reset_flags(_native.stream_ptr())
-    for phase in ("gemm", "reduce"):
+    for phase in ("comm", "gemm", "reduce"):
         for (r, c), op in ops.items():
             op.rs([xs[(r, cc)].data_ptr() for cc in range(C)], wsd[(r, c)], kr, ml, n, outs[(r, c)],
                   n_slices=slices, cyc=cyc, phase=phase, reset=False)
