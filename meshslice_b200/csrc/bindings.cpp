@@ -126,7 +126,7 @@ void gemm_run(const py::dict& d) {
       a.push_counter[i] = P<uint32_t>(pc[i]);
     }
     const int tile = a.push_dim == 0 ? kBM : kBN;
-    if (a.push_extent % tile != 0 || a.push_ld % 8 != 0)
+    if (a.push_extent % tile != 0 || a.push_ld % 8 != 0 || a.M % kBM != 0 || a.N % kBN != 0)
       throw std::runtime_error("gemm: owner extent must be a multiple of the tile size");
   }
   a.red_n = (int)geti(d, "red_n");

@@ -30,7 +30,8 @@ constexpr uint32_t kBStageBytes = kBN * kBK * 2;  // 32 KiB
 constexpr uint32_t kSmemA = 0;
 constexpr uint32_t kSmemB = kSmemA + kStages * kAStageBytes;
 constexpr uint32_t kSmemComm = kSmemB + kStages * kBStageBytes;
-constexpr uint32_t kSmemBar = kSmemComm + kCommBufs * kCommBufBytes;
+constexpr uint32_t kSmemEpi = kSmemComm + kCommBufs * kCommBufBytes;
+constexpr uint32_t kSmemBar = kSmemEpi + 4 * kEpiStageBytes;
 constexpr uint32_t kSmemTotal = kSmemBar + 256;
 constexpr uint32_t kSmemAlloc = kSmemTotal + 1024;  // slack for manual 1024-byte alignment
 constexpr uint32_t kTmemCols = 512;
@@ -224,7 +225,7 @@ __device__ void comm_warp_main(const GemmArgs& a, uint8_t* comm_smem, uint64_t* 
           Piece p;
           more = cur.next(p);
           if (!more) break;
-          bulk_wait_read<2>();  // the stores that last read this buffer have finished reading
+          bulk_wait_read<0>();  // the stores that last read this buffer have finished reading
           const uint32_t b = issued % kCommBufs;
           uint8_t* buf = comm_smem + b * kCommBufBytes;
           const uint32_t total = p.rows * p.row_bytes;
@@ -357,6 +358,7 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
   uint8_t* sA = smem + kSmemA;
   uint8_t* sB = smem + kSmemB;
   uint8_t* sComm = smem + kSmemComm;
+  uint8_t* sEpi = smem + kSmemEpi;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kSmemBar);
   uint64_t* full_bar = bars;                   // [kStages]
   uint64_t* empty_bar = bars + kStages;        // [kStages]
@@ -527,24 +529,66 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
         else ocol_shift = owner * a.push_extent;
       }
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * kBN;
+      if (a.push_n > 0) {
+        // Push path: 64 columns at a time go through this warp's 4 KiB staging buffer and leave
+        // as one 128-byte bulk store per row (posted writes over NVLink), not as 16-byte stores.
+        // Rows sit 144 bytes apart in the staging buffer so that the lanes hit different banks.
+        uint8_t* stage = sEpi + (warp - 2) * kEpiStageBytes;
+        __nv_bfloat16* orow_ptr = reinterpret_cast<__nv_bfloat16*>(out) + orow * ld;
 #pragma unroll 1
-      for (int c = 0; c < kBN / 32; ++c) {
-        uint32_t r[32];
-        __syncwarp();
-        tmem_ld_32x32(taddr + c * 32, r);
-        tmem_ld_wait();
-        if (c == kBN / 32 - 1) {
-          // accumulator fully read: hand it back to the MMA warp
-          tc_fence_before_sync();
-          mbar_arrive(tempty_bar + acc);
-        }
-        const int col0 = tc.n_blk * kBN + c * 32;
-        const int nvalid = min(32, a.N - col0);
-        if (row_ok && nvalid > 0) {
-          float v[32];
+        for (int c2 = 0; c2 < kBN / 64; ++c2) {
+          uint32_t r0[32], r1[32];
+          __syncwarp();
+          tmem_ld_32x32(taddr + c2 * 64, r0);
+          tmem_ld_32x32(taddr + c2 * 64 + 32, r1);
+          tmem_ld_wait();
+          if (c2 == kBN / 64 - 1) {
+            tc_fence_before_sync();
+            mbar_arrive(tempty_bar + acc);
+          }
+          bulk_wait_read<0>();   // this lane's previous row store has left the staging buffer
+          __syncwarp();
+          uint4* srow = reinterpret_cast<uint4*>(stage + lane * kEpiRowPitch);
 #pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
-          if (a.push_n == 0) {
+          for (int k = 0; k < 8; ++k) {
+            const uint32_t* r = k < 4 ? r0 : r1;
+            const int b = (k & 3) * 8;
+            uint4 u;
+            u.x = pack_bf16(__uint_as_float(r[b + 0]), __uint_as_float(r[b + 1]));
+            u.y = pack_bf16(__uint_as_float(r[b + 2]), __uint_as_float(r[b + 3]));
+            u.z = pack_bf16(__uint_as_float(r[b + 4]), __uint_as_float(r[b + 5]));
+            u.w = pack_bf16(__uint_as_float(r[b + 6]), __uint_as_float(r[b + 7]));
+            srow[k] = u;
+          }
+          fence_proxy_async_smem();
+          const int col0 = tc.n_blk * kBN + c2 * 64 - ocol_shift;
+          if (row_ok) bulk_s2g(orow_ptr + col0, stage + lane * kEpiRowPitch, 128);
+          bulk_commit();
+        }
+        // every row store of this warp has completed; then count the warp's part of the tile
+        bulk_wait_all<0>();
+        fence_proxy_async();
+        __threadfence_system();
+        __syncwarp();
+        if (lane == 0) red_add_release_sys(a.push_counter[owner] + tc.slice, 1u);
+      } else {
+#pragma unroll 1
+        for (int c = 0; c < kBN / 32; ++c) {
+          uint32_t r[32];
+          __syncwarp();
+          tmem_ld_32x32(taddr + c * 32, r);
+          tmem_ld_wait();
+          if (c == kBN / 32 - 1) {
+            // accumulator fully read: hand it back to the MMA warp
+            tc_fence_before_sync();
+            mbar_arrive(tempty_bar + acc);
+          }
+          const int col0 = tc.n_blk * kBN + c * 32;
+          const int nvalid = min(32, a.N - col0);
+          if (row_ok && nvalid > 0) {
+            float v[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
             if (bias != nullptr) {
               for (int i = 0; i < 32; ++i)
                 if (i < nvalid) v[i] += __bfloat162float(bias[col0 + i]);
@@ -555,16 +599,9 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
 #pragma unroll
               for (int i = 0; i < 32; ++i) v[i] = gelu_tanh(v[i]);
             }
+            store_row32(a, out, ld, out_fp32, accum, orow, col0, nvalid, v);
           }
-          store_row32(a, out, ld, out_fp32, accum, orow, col0 - ocol_shift, nvalid, v);
         }
-      }
-      if (a.push_n > 0) {
-        // make this warp's part of the tile visible to the owner, then count it there
-        // (four counts per tile: one per epilogue warp, so no CTA-wide barrier is needed)
-        __threadfence_system();
-        __syncwarp();
-        if (lane == 0) red_add_release_sys(a.push_counter[owner] + tc.slice, 1u);
       }
     }
   } else {

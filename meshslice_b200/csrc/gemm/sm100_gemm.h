@@ -27,8 +27,10 @@ constexpr int kBK = 64;
 constexpr int kStages = MSB_STAGES;
 constexpr int kMaxPeers = 8;
 constexpr int kGemmThreads = 224;  // 7 warps: TMA, MMA, 4x epilogue, communication
-constexpr int kCommBufBytes = 8192;
-constexpr int kCommBufs = 4;
+constexpr int kCommBufBytes = 7168;
+constexpr int kCommBufs = 2;
+constexpr int kEpiRowPitch = 144;      // 128 data bytes + 16 pad: spreads the rows over the banks
+constexpr int kEpiStageBytes = 32 * kEpiRowPitch;  // per epilogue warp: 32 rows x 64 bf16 columns
 
 // Error codes written to the status word (first error wins).
 enum GemmStatus : uint32_t {
