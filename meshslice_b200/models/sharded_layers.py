@@ -58,10 +58,17 @@ class ShardedFFLayer:
         self.grad = ShardedTensor(mesh, {k: galloc(v.shape, dtype, v.device).zero_() for k, v in init.shards.items()})
         b = SPMD(mesh, algorithm, blocksize, backend=backend)
         self._OS, self._LS, self._RS = b.OS(ksplit), b.LS(ksplit), b.RS(ksplit)
+        self._fused = b._fused() is not None
         self._x = None
 
-    # dW accumulates across micro-batches
-    def _acc(self, dw: ShardedTensor):
+    # dW accumulates across micro-batches: the fused kernels add into the gradient buffer in
+    # their epilogue / reduce phase, the generic formulation adds afterwards
+    def _dw(self, fn, a: ShardedTensor, b: ShardedTensor):
+        if self._fused:
+            (key, g), = self.grad.shards.items()
+            fn(a, b, out=g, accumulate=True)
+            return
+        dw = fn(a, b)
         for k, g in self.grad.shards.items():
             g += dw.shards[k]
 
@@ -78,12 +85,12 @@ class ShardedFFLayer:
         x, w = self._x, self.weight
         self._x = None
         if self.dataflow == "os":
-            self._acc(self._RS(x, dy))
+            self._dw(self._RS, x, dy)
             return self._LS(dy, w) if need_dx else None
         if self.dataflow == "ls":
-            self._acc(self._RS(dy, x))
+            self._dw(self._RS, dy, x)
             return self._OS(dy, w) if need_dx else None
-        self._acc(self._OS(x, dy))
+        self._dw(self._OS, x, dy)
         return self._LS(w, dy) if need_dx else None
 
     def zero_grad(self):
