@@ -21,6 +21,7 @@ OBJ = PKG / "csrc" / "build"
 
 CU_SOURCES = [
     "gemm/sm100_gemm.cu",
+    "gemm/sm100_gemm2.cu",
     "ops/ops.cu",
     "ops/attention.cu",
     "ops/attention_noalloc.cu",

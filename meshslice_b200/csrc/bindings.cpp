@@ -164,7 +164,9 @@ void gemm_run(const py::dict& d) {
   if (!a.a_mn_major) r = make_tensor_map_2d(&ta, P<void>(A), a.K, a.M, lda * 2, kBK, kBM);
   else r = make_tensor_map_2d(&ta, P<void>(A), a.M, a.K, lda * 2, 64, kBK);
   if (r != 0) throw std::runtime_error("gemm: tensor map for A failed, code " + std::to_string(r));
-  if (!a.b_mn_major) r = make_tensor_map_2d(&tb, P<void>(B), a.K, a.N, ldb * 2, kBK, kBN);
+  const bool plain = a.n_chunks == 0 && a.n_ranks == 0 && a.red_n == 0 && a.push_n == 0 && a.tiles_m > 0;
+  const bool pair = plain && geti(d, "two_cta", 1) != 0;
+  if (!a.b_mn_major) r = make_tensor_map_2d(&tb, P<void>(B), a.K, a.N, ldb * 2, kBK, pair ? kBN / 2 : kBN);
   else r = make_tensor_map_2d(&tb, P<void>(B), a.N, a.K, ldb * 2, 64, kBK);
   if (r != 0) throw std::runtime_error("gemm: tensor map for B failed, code " + std::to_string(r));
 
@@ -172,6 +174,13 @@ void gemm_run(const py::dict& d) {
   const int ntiles = a.tiles_m * a.tiles_n;
   const bool needs_all = a.n_chunks > 0 || a.n_ranks > 0 || a.red_n > 0;
   if (!needs_all && grid > ntiles) grid = ntiles;
+  if (pair) {
+    const int clusters = ((a.M + 2 * kBM - 1) / (2 * kBM)) * a.tiles_n;
+    int g2 = (int)geti(d, "grid", 148) & ~1;
+    if (g2 > 2 * clusters) g2 = 2 * clusters;
+    check(launch_sm100_gemm2(ta, tb, a, g2, S(getp(d, "stream"))), "sm100_gemm2 launch");
+    return;
+  }
   check(launch_sm100_gemm(ta, tb, a, grid, S(getp(d, "stream"))), "sm100_gemm launch");
 }
 

@@ -494,6 +494,8 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
     const __nv_bfloat16* bias = reinterpret_cast<const __nv_bfloat16*>(a.bias);
     bool ok = true;
     int it = 0;
+    bool pend_valid = false;   // push path: a tile whose arrival has not been counted yet
+    int pend_owner = 0, pend_slice = 0;
     for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++it) {
       const TileCoord tc = tile_coord(t, a);
       const uint32_t acc = it & 1, acc_phase = (it >> 1) & 1;
@@ -565,12 +567,18 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
           if (row_ok) bulk_s2g(orow_ptr + col0, stage + lane * kEpiRowPitch, 128);
           bulk_commit();
         }
-        // every row store of this warp has completed; then count the warp's part of the tile
-        bulk_wait_all<0>();
-        fence_proxy_async();
-        __threadfence_system();
-        __syncwarp();
-        if (lane == 0) red_add_release_sys(a.push_counter[owner] + tc.slice, 1u);
+        // Count the PREVIOUS tile at its owner now: its row stores are the groups older than the
+        // four just committed, so waiting for them costs no NVLink round trip on this tile.
+        if (pend_valid) {
+          bulk_wait_all<kBN / 64>();
+          fence_proxy_async();
+          __threadfence_system();
+          __syncwarp();
+          if (lane == 0) red_add_release_sys(a.push_counter[pend_owner] + pend_slice, 1u);
+        }
+        pend_valid = true;
+        pend_owner = owner;
+        pend_slice = tc.slice;
       } else {
 #pragma unroll 1
         for (int c = 0; c < kBN / 32; ++c) {
@@ -603,6 +611,14 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
           }
         }
       }
+    }
+    if (pend_valid) {
+      // last tile of this CTA: all of this warp's row stores must have completed
+      bulk_wait_all<0>();
+      fence_proxy_async();
+      __threadfence_system();
+      __syncwarp();
+      if (lane == 0) red_add_release_sys(a.push_counter[pend_owner] + pend_slice, 1u);
     }
   } else {
     // ===================== communication warp =====================

@@ -148,6 +148,11 @@ struct GemmArgs {
 cudaError_t launch_sm100_gemm(const CUtensorMap& tma_a, const CUtensorMap& tma_b,
                               const GemmArgs& args, int grid, cudaStream_t stream);
 
+// Two-CTA (cta_group::2) variant for plain local GEMMs (no gather / push / reduce / barriers).
+// The tensor map of a K-major B must use a {64, kBN / 2} box.
+cudaError_t launch_sm100_gemm2(const CUtensorMap& tma_a, const CUtensorMap& tma_b,
+                               const GemmArgs& args, int grid, cudaStream_t stream);
+
 // Builds a 2-D bf16 tensor map with 128-byte swizzle.  `inner` is the contiguous extent,
 // `outer` the number of rows, `pitch_bytes` the row pitch.  Returns 0 on success.
 int make_tensor_map_2d(CUtensorMap* map, const void* base, uint64_t inner, uint64_t outer,

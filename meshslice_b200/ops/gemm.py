@@ -7,6 +7,8 @@ descriptors select the major-ness.
 """
 from __future__ import annotations
 
+import os
+
 import torch
 
 from .. import _native
@@ -38,7 +40,7 @@ def _dims(a, b, layout):
     return M, N, K
 
 
-def gemm_args(a, b, layout, out, *, accumulate=False, bias=None, act=None, pre_act=None):
+def gemm_args(a, b, layout, out, *, accumulate=False, bias=None, act=None, pre_act=None, two_cta=None):
     """Argument dict of the native launcher for a plain local GEMM."""
     M, N, K = _dims(a, b, layout)
     for t in (a, b):
@@ -51,6 +53,9 @@ def gemm_args(a, b, layout, out, *, accumulate=False, bias=None, act=None, pre_a
              C=out.data_ptr(), ldc=out.stride(0), c_fp32=1 if out.dtype == torch.float32 else 0,
              accumulate=1 if accumulate else 0, status=_native.status().dev, grid=sm_count(a.device),
              stream=_native.stream_ptr(), timeout_ns=1_000_000_000)
+    if two_cta is None:
+        two_cta = os.environ.get("MSB_TWO_CTA", "1") != "0"
+    d["two_cta"] = 1 if two_cta else 0
     if bias is not None:
         d["bias"] = bias.data_ptr()
     if act is not None:
@@ -63,13 +68,14 @@ def gemm_args(a, b, layout, out, *, accumulate=False, bias=None, act=None, pre_a
 
 
 def gemm(a, b, layout="nn", *, out=None, out_dtype=torch.bfloat16, accumulate=False, bias=None,
-         act=None, pre_act=None):
-    """C = op(A) @ op(B) on the tensor cores of the current GPU."""
+         act=None, pre_act=None, two_cta=None):
+    """C = op(A) @ op(B) on the tensor cores of the current GPU.  ``two_cta`` selects the
+    cta_group::2 kernel (default: on, MSB_TWO_CTA=0 turns it off)."""
     M, N, K = _dims(a, b, layout)
     if out is None:
         if accumulate:
             raise ValueError("accumulate=True needs an output tensor")
         out = torch.empty((M, N), dtype=out_dtype, device=a.device)
     _native.load().gemm_run(gemm_args(a, b, layout, out, accumulate=accumulate, bias=bias, act=act,
-                                      pre_act=pre_act))
+                                      pre_act=pre_act, two_cta=two_cta))
     return out
