@@ -86,7 +86,7 @@ void gemm_run(const py::dict& d) {
   a.act = (int)geti(d, "act");
   a.C_pre = P<void>(getp(d, "C_pre"));
   if (a.ldc % 8) throw std::runtime_error("gemm: ldc must be a multiple of 8");
-  a.tiles_m = (a.M + kBM - 1) / kBM;
+  a.tiles_m = (a.M + 2 * kBM - 1) / (2 * kBM);   // 256-row cluster tiles
   a.tiles_n = (a.N + kBN - 1) / kBN;
   a.slice_dim = (int)geti(d, "slice_dim");
   a.n_slices = (int)geti(d, "n_slices", 1);
@@ -125,8 +125,8 @@ void gemm_run(const py::dict& d) {
       a.push_base[i] = P<void>(pb[i]);
       a.push_counter[i] = P<uint32_t>(pc[i]);
     }
-    const int tile = a.push_dim == 0 ? kBM : kBN;
-    if (a.push_extent % tile != 0 || a.push_ld % 8 != 0 || a.M % kBM != 0 || a.N % kBN != 0)
+    const int tile = a.push_dim == 0 ? 2 * kBM : kBN;
+    if (a.push_extent % tile != 0 || a.push_ld % 8 != 0 || a.M % (2 * kBM) != 0 || a.N % kBN != 0)
       throw std::runtime_error("gemm: owner extent must be a multiple of the tile size");
   }
   a.red_n = (int)geti(d, "red_n");
@@ -138,7 +138,7 @@ void gemm_run(const py::dict& d) {
   a.red_target = (uint32_t)geti(d, "red_target");
   a.red_slice_dim = (int)geti(d, "red_slice_dim");
   if (a.red_n > 0) {
-    const int rt = a.red_slice_dim == 0 ? (a.red_rows + kBM - 1) / kBM : (a.red_cols + kBN - 1) / kBN;
+    const int rt = a.red_slice_dim == 0 ? (a.red_rows + 2 * kBM - 1) / (2 * kBM) : (a.red_cols + kBN - 1) / kBN;
     if (rt % (a.n_slices * a.cyc) != 0 || a.red_cols % 8 != 0 || a.red_ld % 8 != 0)
       throw std::runtime_error("gemm: reduce phase shape not divisible by the slice count");
   }
@@ -166,14 +166,16 @@ void gemm_run(const py::dict& d) {
   if (r != 0) throw std::runtime_error("gemm: tensor map for A failed, code " + std::to_string(r));
   const bool plain = a.n_chunks == 0 && a.n_ranks == 0 && a.red_n == 0 && a.push_n == 0 && a.tiles_m > 0;
   const bool pair = plain && geti(d, "two_cta", 1) != 0;
-  if (!a.b_mn_major) r = make_tensor_map_2d(&tb, P<void>(B), a.K, a.N, ldb * 2, kBK, pair ? kBN / 2 : kBN);
+  if (!a.b_mn_major) r = make_tensor_map_2d(&tb, P<void>(B), a.K, a.N, ldb * 2, kBK, kBN / 2);
   else r = make_tensor_map_2d(&tb, P<void>(B), a.N, a.K, ldb * 2, 64, kBK);
   if (r != 0) throw std::runtime_error("gemm: tensor map for B failed, code " + std::to_string(r));
 
   int grid = (int)geti(d, "grid", 148);
   const int ntiles = a.tiles_m * a.tiles_n;
   const bool needs_all = a.n_chunks > 0 || a.n_ranks > 0 || a.red_n > 0;
-  if (!needs_all && grid > ntiles) grid = ntiles;
+  if (!needs_all && grid > 2 * ntiles) grid = 2 * ntiles;
+  grid &= ~1;
+  if (grid < 2) grid = 2;
   if (pair) {
     const int clusters = ((a.M + 2 * kBM - 1) / (2 * kBM)) * a.tiles_n;
     int g2 = (int)geti(d, "grid", 148) & ~1;

@@ -25,8 +25,8 @@ namespace msb {
 
 namespace {
 
-constexpr uint32_t kAStageBytes = kBM * kBK * 2;  // 16 KiB
-constexpr uint32_t kBStageBytes = kBN * kBK * 2;  // 32 KiB
+constexpr uint32_t kAStageBytes = kBM * kBK * 2;        // 16 KiB: this CTA's 128 rows of A
+constexpr uint32_t kBStageBytes = (kBN / 2) * kBK * 2;  // 16 KiB: this CTA's 128 columns of B
 constexpr uint32_t kSmemA = 0;
 constexpr uint32_t kSmemB = kSmemA + kStages * kAStageBytes;
 constexpr uint32_t kSmemComm = kSmemB + kStages * kBStageBytes;
@@ -37,6 +37,47 @@ constexpr uint32_t kSmemAlloc = kSmemTotal + 1024;  // slack for manual 1024-byt
 constexpr uint32_t kTmemCols = 512;
 constexpr int kEpiThreads = 128;
 
+// ---- CTA pair (cluster of two) helpers ----
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t mapa_u32(uint32_t addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* map, uint32_t leader_bar,
+                                                 int32_t x, int32_t y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(map), "r"(leader_bar), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void umma_f16_pair(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc,
+                                              uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar_addr) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_addr)
+               : "memory");
+}
+
+// m_blk counts 256-row cluster tiles; a CTA of rank r works on rows (2 * m_blk + r) * 128.
 struct TileCoord {
   int m_blk, n_blk, slice;
 };
@@ -349,7 +390,7 @@ __device__ __forceinline__ void store_row32(const GemmArgs& a, void* base, int64
 // ------------------------------------------------------------------------------------------
 // kernel
 // ------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(kGemmThreads, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
 sm100_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                   const __grid_constant__ GemmArgs a) {
   extern __shared__ uint8_t smem_raw[];
@@ -369,30 +410,34 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();   // 0: leader of the CTA pair (issues the MMAs)
+  const int cluster_id = blockIdx.x >> 1, n_clusters = gridDim.x >> 1;
   const uint64_t tmo = a.timeout_ns;
-  const int num_tiles = a.tiles_m * a.tiles_n;
+  const int num_tiles = a.tiles_m * a.tiles_n;   // 256 x 256 cluster tiles
   const int kblocks = (a.K + kBK - 1) / kBK;
 
   if (warp == 0 && lane == 0) {
     tma_prefetch_desc(&tma_a);
     tma_prefetch_desc(&tma_b);
     for (int i = 0; i < kStages; ++i) {
-      mbar_init(full_bar + i, 1);
-      mbar_init(empty_bar + i, 1);
+      mbar_init(full_bar + i, 1);    // used in the leader: both CTAs' loads complete on it
+      mbar_init(empty_bar + i, 1);   // one per CTA
     }
     for (int i = 0; i < 2; ++i) {
-      mbar_init(tfull_bar + i, 1);
-      mbar_init(tempty_bar + i, kEpiThreads);
+      mbar_init(tfull_bar + i, 1);                  // one per CTA
+      mbar_init(tempty_bar + i, 2 * kEpiThreads);   // used in the leader: both CTAs' epilogues
     }
     for (int i = 0; i < kCommBufs; ++i) mbar_init(comm_bar + i, 1);
     mbar_fence_init();
   }
   if (warp == 1) {
-    tmem_alloc(tmem_slot, kTmemCols);
-    tmem_relinquish();
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                 "r"(kTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
   }
   tc_fence_before_sync();
-  __syncthreads();
+  cluster_sync_all();   // both CTAs' barriers exist before any remote arrival or commit
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
 
@@ -407,7 +452,7 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
         }
       }
       uint32_t stage = 0, phase = 0;
-      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+      for (int t = cluster_id; t < num_tiles && ok; t += n_clusters) {
         const TileCoord tc = tile_coord(t, a);
         if (a.a_flag_mode | a.b_flag_mode) {
           if (!wait_operand(a, a.a_flag_mode, a.a_flag_base, a.a_flag_count, tc.slice, 3 * tmo) ||
@@ -418,30 +463,31 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
           }
           fence_proxy_async();
         }
+        const int row_a = (2 * tc.m_blk + (int)rank) * kBM;        // this CTA's 128 rows of A
+        const int col_b = tc.n_blk * kBN + (int)rank * (kBN / 2);  // this CTA's 128 columns of B
         for (int kb = 0; kb < kblocks; ++kb) {
           if (!mbar_wait(empty_bar + stage, phase ^ 1, 5 * tmo)) {
             report(a, kTimeoutEmpty, t, kb);
             ok = false;
             break;
           }
-          mbar_expect_tx(full_bar + stage, kAStageBytes + kBStageBytes);
+          const uint32_t fb = mapa_u32(smem_u32(full_bar + stage), 0);   // the leader's barrier
+          if (rank == 0) mbar_expect_tx(full_bar + stage, 2 * (kAStageBytes + kBStageBytes));
           uint8_t* da = sA + stage * kAStageBytes;
           uint8_t* db = sB + stage * kBStageBytes;
           if (!a.a_mn_major) {
-            tma_load_2d(da, &tma_a, full_bar + stage, kb * kBK, tc.m_blk * kBM);
+            tma_load_2d_pair(da, &tma_a, fb, kb * kBK, row_a);
           } else {
 #pragma unroll
             for (int j = 0; j < kBM / 64; ++j)
-              tma_load_2d(da + j * (kBK * 128), &tma_a, full_bar + stage, tc.m_blk * kBM + j * 64,
-                          kb * kBK);
+              tma_load_2d_pair(da + j * (kBK * 128), &tma_a, fb, row_a + j * 64, kb * kBK);
           }
           if (!a.b_mn_major) {
-            tma_load_2d(db, &tma_b, full_bar + stage, kb * kBK, tc.n_blk * kBN);
+            tma_load_2d_pair(db, &tma_b, fb, kb * kBK, col_b);
           } else {
 #pragma unroll
-            for (int j = 0; j < kBN / 64; ++j)
-              tma_load_2d(db + j * (kBK * 128), &tma_b, full_bar + stage, tc.n_blk * kBN + j * 64,
-                          kb * kBK);
+            for (int j = 0; j < kBN / 128; ++j)
+              tma_load_2d_pair(db + j * (kBK * 128), &tma_b, fb, col_b + j * 64, kb * kBK);
           }
           if (++stage == kStages) { stage = 0; phase ^= 1; }
         }
@@ -449,8 +495,8 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
     }
   } else if (warp == 1) {
     // ===================== MMA issuer =====================
-    if (lane == 0) {
-      const uint32_t idesc = make_idesc_bf16(kBM, kBN, a.a_mn_major, a.b_mn_major);
+    if (lane == 0 && rank == 0) {
+      const uint32_t idesc = make_idesc_bf16(2 * kBM, kBN, a.a_mn_major, a.b_mn_major);
       const uint32_t a_lbo = a.a_mn_major ? kBK * 128 : 16;
       const uint32_t b_lbo = a.b_mn_major ? kBK * 128 : 16;
       const uint32_t a_kstep = a.a_mn_major ? 16 * 128 : 32;  // bytes per K=16 step
@@ -458,7 +504,7 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
       uint32_t stage = 0, phase = 0;
       bool ok = true;
       int it = 0;
-      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++it) {
+      for (int t = cluster_id; t < num_tiles && ok; t += n_clusters, ++it) {
         const uint32_t acc = it & 1, acc_phase = (it >> 1) & 1;
         if (!mbar_wait(tempty_bar + acc, acc_phase ^ 1, 6 * tmo)) {
           report(a, kTimeoutTmemEmpty, t, acc);
@@ -480,12 +526,18 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
           for (int k = 0; k < kBK / 16; ++k) {
             const uint64_t da = make_smem_desc(sa + k * a_kstep, a_lbo, 1024);
             const uint64_t db = make_smem_desc(sb + k * b_kstep, b_lbo, 1024);
-            umma_f16(tmem_d, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+            umma_f16_pair(tmem_d, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
           }
-          umma_commit(empty_bar + stage);
+          const uint32_t eb = smem_u32(empty_bar + stage);
+          umma_commit_pair(eb);                // this CTA's stage is free again
+          umma_commit_pair(mapa_u32(eb, 1));   // and so is the peer's
           if (++stage == kStages) { stage = 0; phase ^= 1; }
         }
-        if (ok) umma_commit(tfull_bar + acc);
+        if (ok) {
+          const uint32_t tb = smem_u32(tfull_bar + acc);
+          umma_commit_pair(tb);
+          umma_commit_pair(mapa_u32(tb, 1));
+        }
       }
     }
   } else if (warp < 6) {
@@ -496,9 +548,11 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
     int it = 0;
     bool pend_valid = false;   // push path: a tile whose arrival has not been counted yet
     int pend_owner = 0, pend_slice = 0;
-    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++it) {
+    for (int t = cluster_id; t < num_tiles && ok; t += n_clusters, ++it) {
       const TileCoord tc = tile_coord(t, a);
       const uint32_t acc = it & 1, acc_phase = (it >> 1) & 1;
+      const int m_blk = 2 * tc.m_blk + (int)rank;   // this CTA's 128-row block
+      const uint32_t te_leader = mapa_u32(smem_u32(tempty_bar + acc), 0);
       // lane 0 does the bounded wait and the warp follows its verdict, so the warp-wide
       // tcgen05.ld below is never reached by only some of the lanes
       int okw = 1;
@@ -511,7 +565,7 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
       }
       mbar_wait(tfull_bar + acc, acc_phase, tmo);  // already complete: orders this lane's reads
       tc_fence_after_sync();
-      const int64_t row = (int64_t)tc.m_blk * kBM + q * 32 + lane;
+      const int64_t row = (int64_t)m_blk * kBM + q * 32 + lane;
       const bool row_ok = row < a.M;
       // destination of this tile
       void* out = a.C;
@@ -521,7 +575,7 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
       int ocol_shift = 0;
       int owner = 0;
       if (a.push_n > 0) {
-        const int c0 = a.push_dim == 0 ? tc.m_blk * kBM : tc.n_blk * kBN;
+        const int c0 = a.push_dim == 0 ? m_blk * kBM : tc.n_blk * kBN;
         owner = c0 / a.push_extent;
         out = a.push_base[owner];
         ld = a.push_ld;
@@ -546,7 +600,7 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
           tmem_ld_wait();
           if (c2 == kBN / 64 - 1) {
             tc_fence_before_sync();
-            mbar_arrive(tempty_bar + acc);
+            mbar_arrive_cluster(te_leader);
           }
           bulk_wait_read<0>();   // this lane's previous row store has left the staging buffer
           __syncwarp();
@@ -587,9 +641,9 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
           tmem_ld_32x32(taddr + c * 32, r);
           tmem_ld_wait();
           if (c == kBN / 32 - 1) {
-            // accumulator fully read: hand it back to the MMA warp
+            // accumulator fully read: hand it back to the leader's MMA warp
             tc_fence_before_sync();
-            mbar_arrive(tempty_bar + acc);
+            mbar_arrive_cluster(te_leader);
           }
           const int col0 = tc.n_blk * kBN + c * 32;
           const int nvalid = min(32, a.N - col0);
@@ -625,15 +679,19 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
     comm_warp_main(a, sComm, comm_bar);
   }
 
-  // ---- all roles of this CTA are done with TMEM and the pipeline
+  // ---- all roles of both CTAs of the pair are done with TMEM, barriers and the pipeline
   tc_fence_before_sync();
-  __syncthreads();
+  cluster_sync_all();
   tc_fence_after_sync();
-  if (warp == 1) tmem_dealloc(tmem_base, kTmemCols);
+  if (warp == 1)
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols)
+                 : "memory");
 
   // ===================== reduce phase =====================
   if (a.red_n > 0) {
-    const int tiles_r = (a.red_rows + kBM - 1) / kBM;
+    // row slices follow the 256-row cluster tiles of the senders, column slices the 256 columns
+    const int RB = a.red_slice_dim == 0 ? 2 * kBM : kBM;
+    const int tiles_r = (a.red_rows + RB - 1) / RB;
     const int tiles_c = (a.red_cols + kBN - 1) / kBN;
     const int tiles_s = a.red_slice_dim == 0 ? tiles_r : tiles_c;
     const int tiles_o = a.red_slice_dim == 0 ? tiles_c : tiles_r;
@@ -661,10 +719,10 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
       }
       ok = __syncthreads_and(ok);
       if (!ok) break;
-      // 128 x 256 block, 8 bf16 per vector
-      for (int vi = threadIdx.x; vi < kBM * (kBN / 8); vi += kGemmThreads) {
+      // RB x 256 block, 8 bf16 per vector
+      for (int vi = threadIdx.x; vi < RB * (kBN / 8); vi += kGemmThreads) {
         const int rr = vi / (kBN / 8), cv = vi - rr * (kBN / 8);
-        const int64_t row = (int64_t)rb * kBM + rr;
+        const int64_t row = (int64_t)rb * RB + rr;
         const int col = cb * kBN + cv * 8;
         if (row >= a.red_rows || col >= a.red_cols) continue;
         float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};

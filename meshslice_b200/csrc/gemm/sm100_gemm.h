@@ -22,7 +22,7 @@ constexpr int kBM = 128;
 constexpr int kBN = 256;
 constexpr int kBK = 64;
 #ifndef MSB_STAGES
-#define MSB_STAGES 4
+#define MSB_STAGES 6
 #endif
 constexpr int kStages = MSB_STAGES;
 constexpr int kMaxPeers = 8;
@@ -95,7 +95,7 @@ struct GemmArgs {
   int act;             // 0: none, 1: tanh-GeLU
   void* C_pre;         // bf16, same layout as C: pre-activation copy (act != 0), may be null
   // ---- tile order ----
-  int tiles_m, tiles_n;
+  int tiles_m, tiles_n;  // tiles_m counts 256-row cluster tiles (two CTAs x 128 rows)
   int slice_dim;       // 0: slices over M blocks, 1: slices over N blocks
   int n_slices;        // block-cyclic slices of the sliced dimension (divides its tile count)
   int group;           // raster group size along the sliced dimension
@@ -143,8 +143,8 @@ struct GemmArgs {
   uint64_t timeout_ns;
 };
 
-// Launch on `stream`.  Tensor maps must describe A and B with 128-byte swizzle and boxes
-// {64, kBM} / {64, kBN} (K-major) or {64, kBK} (MN-major).
+// Launch on `stream` (grid even: CTA pairs).  Tensor maps must describe A and B with 128-byte
+// swizzle and boxes {64, kBM} / {64, kBN / 2} (K-major) or {64, kBK} (MN-major).
 cudaError_t launch_sm100_gemm(const CUtensorMap& tma_a, const CUtensorMap& tma_b,
                               const GemmArgs& args, int grid, cudaStream_t stream);
 

@@ -25,7 +25,8 @@ import torch
 from .. import _native
 from . import runtime as rt
 
-BM, BN = 128, 256
+BM, BN = 256, 256      # rows / columns of one cluster tile (two CTAs x 128 rows)
+CTA_M = 128            # rows one CTA pushes per tile
 
 
 @dataclass
@@ -191,7 +192,7 @@ class FusedGemm:
             raise FusedPlanError("LS: output width not divisible by the mesh columns")
         nc = N // mc.C
         if nr % BN or nc % BN or m % BM or kl % 8:
-            raise FusedPlanError("LS: shard sizes must be multiples of the 128x256 tile")
+            raise FusedPlanError("LS: shard sizes must be multiples of the 256x256 cluster tile")
         if N * kl * 2 > ws.stage_b_bytes or mc.C * m * nc * 2 > ws.slot_bytes:
             raise FusedPlanError("LS: staging / slot buffers too small")
         blocks_src, blocks_own = nr // BN, nc // BN
@@ -230,13 +231,13 @@ class FusedGemm:
                  push_counter=[self.world.flag_ptr(q, rt.COUNTER0) for q in peers],
                  red_n=mc.C, red_slots=ws.local(ws.slots), red_rows=m, red_cols=nc, red_ld=nc,
                  red_counter=ws.local(ws.flags + 4 * rt.COUNTER0),
-                 red_target=mc.C * (blocks_own // S) * tiles_m * 4, red_slice_dim=1)
+                 red_target=mc.C * (blocks_own // S) * (m // CTA_M) * 4, red_slice_dim=1)
         self._launch(d, exit_barrier=False, phase=phase, reset=reset)
         return out
 
     # ------------------------------------------------------------------ RS
     def rs(self, x_ptrs: List[int], w, kr: int, ml: int, n: int, out, n_slices: int = 4,
-           accumulate: bool = False, cyc: int = 4, phase: str = "all", reset: bool = True):
+           accumulate: bool = False, cyc: int = 2, phase: str = "all", reset: bool = True):
         """Y[M/R, n] = reduce-scatter over the mesh column of  concat_c(X_c)[kr, C*ml]^T @ W[kr, n]."""
         mc, ws = self.mesh, self.world.mine
         M = mc.C * ml
@@ -244,7 +245,7 @@ class FusedGemm:
             raise FusedPlanError("RS: output height not divisible by the mesh rows")
         mr = M // mc.R
         if ml % BM or mr % BM or n % BN or kr % 8:
-            raise FusedPlanError("RS: shard sizes must be multiples of the 128x256 tile")
+            raise FusedPlanError("RS: shard sizes must be multiples of the 256x256 cluster tile")
         if kr * M * 2 > ws.stage_a_bytes or mc.R * mr * n * 2 > ws.slot_bytes:
             raise FusedPlanError("RS: staging / slot buffers too small")
         import math
@@ -286,6 +287,6 @@ class FusedGemm:
                  push_counter=[self.world.flag_ptr(q, rt.COUNTER0) for q in peers],
                  red_n=mc.R, red_slots=ws.local(ws.slots), red_rows=mr, red_cols=n, red_ld=n,
                  red_counter=ws.local(ws.flags + 4 * rt.COUNTER0),
-                 red_target=mc.R * ((mr // BM) // S) * tiles_n * 4, red_slice_dim=0)
+                 red_target=mc.R * ((mr // BM) // S) * 2 * tiles_n * 4, red_slice_dim=0)
         self._launch(d, exit_barrier=False, phase=phase, reset=reset)
         return out
