@@ -183,7 +183,16 @@ void gemm_run(const py::dict& d) {
     check(launch_sm100_gemm2(ta, tb, a, g2, S(getp(d, "stream"))), "sm100_gemm2 launch");
     return;
   }
-  check(launch_sm100_gemm(ta, tb, a, grid, S(getp(d, "stream"))), "sm100_gemm launch");
+  static PushMaps pm;   // only the first push_n entries are read by the kernel
+  if (a.push_n > 0) {
+    const uint64_t rows = (uint64_t)geti(d, "push_rows");
+    if (rows == 0) throw std::runtime_error("gemm: push_rows (rows of an owner's slot) required");
+    for (int i = 0; i < a.push_n; ++i) {
+      r = make_tensor_map_2d(&pm.m[i], a.push_base[i], (uint64_t)a.push_ld, rows, (uint64_t)a.push_ld * 2, 64, 32);
+      if (r != 0) throw std::runtime_error("gemm: tensor map for an owner's slot failed, code " + std::to_string(r));
+    }
+  }
+  check(launch_sm100_gemm(ta, tb, pm, a, grid, S(getp(d, "stream"))), "sm100_gemm launch");
 }
 
 // ---------------------------------------------------------------------------------------

@@ -392,7 +392,7 @@ __device__ __forceinline__ void store_row32(const GemmArgs& a, void* base, int64
 // ------------------------------------------------------------------------------------------
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
 sm100_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
-                  const __grid_constant__ GemmArgs a) {
+                  const __grid_constant__ PushMaps pmaps, const __grid_constant__ GemmArgs a) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
@@ -586,11 +586,12 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
       }
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * kBN;
       if (a.push_n > 0) {
-        // Push path: 64 columns at a time go through this warp's 4 KiB staging buffer and leave
-        // as one 128-byte bulk store per row (posted writes over NVLink), not as 16-byte stores.
-        // Rows sit 144 bytes apart in the staging buffer so that the lanes hit different banks.
+        // Push path: 64 columns at a time go through this warp's 4 KiB staging buffer (128-byte
+        // swizzled, so the lanes' row writes spread over the banks) and leave as ONE 2-D TMA
+        // tensor store of 32 rows x 128 bytes into the owner's slot (posted writes over NVLink).
         uint8_t* stage = sEpi + (warp - 2) * kEpiStageBytes;
-        __nv_bfloat16* orow_ptr = reinterpret_cast<__nv_bfloat16*>(out) + orow * ld;
+        const CUtensorMap* omap = &pmaps.m[owner];
+        const int32_t y0 = (int32_t)(orow - lane);   // first row of this warp's 32-row band
 #pragma unroll 1
         for (int c2 = 0; c2 < kBN / 64; ++c2) {
           uint32_t r0[32], r1[32];
@@ -602,9 +603,9 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
             tc_fence_before_sync();
             mbar_arrive_cluster(te_leader);
           }
-          bulk_wait_read<0>();   // this lane's previous row store has left the staging buffer
+          if (lane == 0) bulk_wait_read<0>();   // the previous store has left the staging buffer
           __syncwarp();
-          uint4* srow = reinterpret_cast<uint4*>(stage + lane * kEpiRowPitch);
+          uint8_t* srow = stage + lane * 128;
 #pragma unroll
           for (int k = 0; k < 8; ++k) {
             const uint32_t* r = k < 4 ? r0 : r1;
@@ -614,21 +615,25 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
             u.y = pack_bf16(__uint_as_float(r[b + 2]), __uint_as_float(r[b + 3]));
             u.z = pack_bf16(__uint_as_float(r[b + 4]), __uint_as_float(r[b + 5]));
             u.w = pack_bf16(__uint_as_float(r[b + 6]), __uint_as_float(r[b + 7]));
-            srow[k] = u;
+            *reinterpret_cast<uint4*>(srow + ((k ^ (lane & 7)) << 4)) = u;
           }
           fence_proxy_async_smem();
-          const int col0 = tc.n_blk * kBN + c2 * 64 - ocol_shift;
-          if (row_ok) bulk_s2g(orow_ptr + col0, stage + lane * kEpiRowPitch, 128);
-          bulk_commit();
+          __syncwarp();
+          if (lane == 0) {
+            const int32_t x0 = tc.n_blk * kBN + c2 * 64 - ocol_shift;
+            asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+                         ::"l"(omap), "r"(smem_u32(stage)), "r"(x0), "r"(y0)
+                         : "memory");
+            bulk_commit();
+          }
         }
         // Count the PREVIOUS tile at its owner now: its row stores are the groups older than the
         // four just committed, so waiting for them costs no NVLink round trip on this tile.
-        if (pend_valid) {
+        if (pend_valid && lane == 0) {
           bulk_wait_all<kBN / 64>();
           fence_proxy_async();
           __threadfence_system();
-          __syncwarp();
-          if (lane == 0) red_add_release_sys(a.push_counter[pend_owner] + pend_slice, 1u);
+          red_add_release_sys(a.push_counter[pend_owner] + pend_slice, 1u);
         }
         pend_valid = true;
         pend_owner = owner;
@@ -666,13 +671,12 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
         }
       }
     }
-    if (pend_valid) {
-      // last tile of this CTA: all of this warp's row stores must have completed
+    if (pend_valid && lane == 0) {
+      // last tile of this CTA: all of this warp's tensor stores must have completed
       bulk_wait_all<0>();
       fence_proxy_async();
       __threadfence_system();
-      __syncwarp();
-      if (lane == 0) red_add_release_sys(a.push_counter[pend_owner] + pend_slice, 1u);
+      red_add_release_sys(a.push_counter[pend_owner] + pend_slice, 1u);
     }
   } else {
     // ===================== communication warp =====================
@@ -776,7 +780,8 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
 size_t sm100_gemm_smem_bytes() { return kSmemAlloc; }
 
 cudaError_t launch_sm100_gemm(const CUtensorMap& tma_a, const CUtensorMap& tma_b,
-                              const GemmArgs& args, int grid, cudaStream_t stream) {
+                              const PushMaps& push_maps, const GemmArgs& args, int grid,
+                              cudaStream_t stream) {
   static bool configured[64] = {false};
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
@@ -787,7 +792,7 @@ cudaError_t launch_sm100_gemm(const CUtensorMap& tma_a, const CUtensorMap& tma_b
     if (e != cudaSuccess) return e;
     configured[dev] = true;
   }
-  sm100_gemm_kernel<<<grid, kGemmThreads, kSmemAlloc, stream>>>(tma_a, tma_b, args);
+  sm100_gemm_kernel<<<grid, kGemmThreads, kSmemAlloc, stream>>>(tma_a, tma_b, push_maps, args);
   return cudaGetLastError();
 }
 

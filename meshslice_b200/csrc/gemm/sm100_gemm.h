@@ -29,8 +29,7 @@ constexpr int kMaxPeers = 8;
 constexpr int kGemmThreads = 224;  // 7 warps: TMA, MMA, 4x epilogue, communication
 constexpr int kCommBufBytes = 7168;
 constexpr int kCommBufs = 2;
-constexpr int kEpiRowPitch = 144;      // 128 data bytes + 16 pad: spreads the rows over the banks
-constexpr int kEpiStageBytes = 32 * kEpiRowPitch;  // per epilogue warp: 32 rows x 64 bf16 columns
+constexpr int kEpiStageBytes = 32 * 128;  // per epilogue warp: 32 rows x 64 bf16 columns, 128-byte swizzled
 
 // Error codes written to the status word (first error wins).
 enum GemmStatus : uint32_t {
@@ -79,6 +78,11 @@ struct CopyJob {
   uint32_t row_bytes;
   uint64_t src_pitch;
   uint64_t dst_pitch;
+};
+
+// Tensor maps of the owners' slot buffers for the push side ({64, 32} boxes, 128-byte swizzle).
+struct PushMaps {
+  CUtensorMap m[kMaxPeers];
 };
 
 struct GemmArgs {
@@ -146,7 +150,8 @@ struct GemmArgs {
 // Launch on `stream` (grid even: CTA pairs).  Tensor maps must describe A and B with 128-byte
 // swizzle and boxes {64, kBM} / {64, kBN / 2} (K-major) or {64, kBK} (MN-major).
 cudaError_t launch_sm100_gemm(const CUtensorMap& tma_a, const CUtensorMap& tma_b,
-                              const GemmArgs& args, int grid, cudaStream_t stream);
+                              const PushMaps& push_maps, const GemmArgs& args, int grid,
+                              cudaStream_t stream);
 
 // Two-CTA (cta_group::2) variant for plain local GEMMs (no gather / push / reduce / barriers).
 // The tensor map of a K-major B must use a {64, kBN / 2} box.

@@ -226,7 +226,7 @@ class FusedGemm:
                  jobs=jt.data_ptr(), chunks=ct.data_ptr(), n_chunks=n_chunks,
                  chunk_flags=ws.local(ws.flags + 4 * rt.CHUNK0),
                  b_flag_mode=1, b_flag_base=0, gather_src1=w_mine,
-                 push_n=mc.C, push_dim=1, push_extent=nc, push_ld=nc,
+                 push_n=mc.C, push_dim=1, push_extent=nc, push_ld=nc, push_rows=m,
                  push_base=[self.world.ptr(q, ws.slots) + mc.c * m * nc * 2 for q in peers],
                  push_counter=[self.world.flag_ptr(q, rt.COUNTER0) for q in peers],
                  red_n=mc.C, red_slots=ws.local(ws.slots), red_rows=m, red_cols=nc, red_ld=nc,
@@ -282,7 +282,7 @@ class FusedGemm:
                  jobs=jt.data_ptr(), chunks=ct.data_ptr(), n_chunks=n_chunks,
                  chunk_flags=ws.local(ws.flags + 4 * rt.CHUNK0),
                  a_flag_mode=1, a_flag_base=0, gather_src0=x_mine,
-                 push_n=mc.R, push_dim=0, push_extent=mr, push_ld=n,
+                 push_n=mc.R, push_dim=0, push_extent=mr, push_ld=n, push_rows=mr,
                  push_base=[self.world.ptr(q, ws.slots) + mc.r * mr * n * 2 for q in peers],
                  push_counter=[self.world.flag_ptr(q, rt.COUNTER0) for q in peers],
                  red_n=mc.R, red_slots=ws.local(ws.slots), red_rows=mr, red_cols=n, red_ld=n,
