@@ -134,12 +134,19 @@ __device__ __forceinline__ float bf16_hi(uint32_t v) { return __uint_as_float(v 
 __device__ __forceinline__ bool wait_chunk(const GemmArgs& a, int idx, uint64_t tmo) {
   return wait_flag_geq_sys(a.chunk_flags + idx, a.chunks[idx].target, tmo);
 }
+// `seen` remembers chunks already observed complete, so that only the first tile that needs a
+// chunk pays for the system-scope flag reads.
 __device__ __forceinline__ bool wait_operand(const GemmArgs& a, int mode, int base, int count,
-                                             int slice, uint64_t tmo) {
+                                             int slice, uint64_t tmo, uint64_t& seen) {
   if (mode == 0) return true;
-  if (mode == 1) return wait_chunk(a, base + slice, tmo);
-  for (int i = 0; i < count; ++i)
-    if (!wait_chunk(a, base + i, tmo)) return false;
+  const int lo = mode == 1 ? base + slice : base;
+  const int hi = mode == 1 ? lo + 1 : base + count;
+  for (int i = lo; i < hi; ++i) {
+    const uint64_t bit = 1ull << (i & 63);
+    if (i < 64 && (seen & bit)) continue;
+    if (!wait_chunk(a, i, tmo)) return false;
+    if (i < 64) seen |= bit;
+  }
   return true;
 }
 
@@ -452,16 +459,18 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
         }
       }
       uint32_t stage = 0, phase = 0;
+      uint64_t seen = 0;
       for (int t = cluster_id; t < num_tiles && ok; t += n_clusters) {
         const TileCoord tc = tile_coord(t, a);
         if (a.a_flag_mode | a.b_flag_mode) {
-          if (!wait_operand(a, a.a_flag_mode, a.a_flag_base, a.a_flag_count, tc.slice, 3 * tmo) ||
-              !wait_operand(a, a.b_flag_mode, a.b_flag_base, a.b_flag_count, tc.slice, 3 * tmo)) {
+          const uint64_t before = seen;
+          if (!wait_operand(a, a.a_flag_mode, a.a_flag_base, a.a_flag_count, tc.slice, 3 * tmo, seen) ||
+              !wait_operand(a, a.b_flag_mode, a.b_flag_base, a.b_flag_count, tc.slice, 3 * tmo, seen)) {
             report(a, kTimeoutChunk, t, tc.slice);
             ok = false;
             break;
           }
-          fence_proxy_async();
+          if (seen != before || a.n_chunks > 64) fence_proxy_async();
         }
         const int row_a = (2 * tc.m_blk + (int)rank) * kBM;        // this CTA's 128 rows of A
         const int col_b = tc.n_blk * kBN + (int)rank * (kBN / 2);  // this CTA's 128 columns of B

@@ -149,30 +149,37 @@ class FusedGemm:
         rowp, colp = mc.row_peers(), mc.col_peers()
         x_mine, w_mine = x_ptrs[mc.c], w_ptrs[mc.r]
 
+        gather_w, gather_x = mc.R > 1, mc.C > 1     # a group of one needs no copy at all
+        xbase = 1 if gather_w else 0                # index of the first X chunk
+
         def build():
             jobs, chunks = [], []
-            # chunk 0: this rank's W shard goes to every GPU of its mesh column
-            jobs.append((1, 0, kr, n * 2, n * 2, n * 2,
-                         [self.world.ptr(q, ws.stage_b) + mc.r * kr * n * 2 for q in colp]))
-            chunks.append((0, 1, [self._chunk_flag(q, 0) for q in colp], self.grid * mc.R))
-            for s in range(S):     # chunks 1..S: row blocks of this rank's X shard, block-cyclic
+            if gather_w:   # chunk 0: this rank's W shard goes to every GPU of its mesh column
+                jobs.append((1, 0, kr, n * 2, n * 2, n * 2,
+                             [self.world.ptr(q, ws.stage_b) + mc.r * kr * n * 2 for q in colp]))
+                chunks.append((0, 1, [self._chunk_flag(q, 0) for q in colp], self.grid * mc.R))
+            for s in range(S if gather_x else 0):   # row blocks of this rank's X shard, block-cyclic
                 jb = len(jobs)
                 for blk in range(s, tiles_m, S):
                     row0 = blk * BM
                     rows = min(BM, m - row0)
                     jobs.append((0, row0 * kl * 2, rows, kl * 2, kl * 2, Kd * 2,
                                  [self.world.ptr(q, ws.stage_a) + row0 * Kd * 2 + mc.c * kl * 2 for q in rowp]))
-                chunks.append((jb, len(jobs), [self._chunk_flag(q, 1 + s) for q in rowp], self.grid * mc.C))
+                chunks.append((jb, len(jobs), [self._chunk_flag(q, xbase + s) for q in rowp], self.grid * mc.C))
             return jobs, chunks
 
-        jt, ct, n_chunks = self._jobs(("os", m, kl, kr, n, S), build)
         d = self._common(out, accumulate, stream)
-        d.update(M=m, N=n, K=Kd, A=xg, B=wg, lda=Kd, ldb=n, a_mn_major=0, b_mn_major=1,
-                 slice_dim=0, n_slices=S, cyc=1, group=8,
-                 jobs=jt.data_ptr(), chunks=ct.data_ptr(), n_chunks=n_chunks,
-                 chunk_flags=ws.local(ws.flags + 4 * rt.CHUNK0),
-                 a_flag_mode=1, a_flag_base=1, b_flag_mode=2, b_flag_base=0, b_flag_count=1,
+        d.update(M=m, N=n, K=Kd, A=xg if gather_x else x_mine, B=wg if gather_w else w_mine, lda=Kd, ldb=n,
+                 a_mn_major=0, b_mn_major=1, slice_dim=0, n_slices=S, cyc=1, group=8,
                  gather_src0=x_mine, gather_src1=w_mine)
+        if gather_w or gather_x:
+            jt, ct, n_chunks = self._jobs(("os", m, kl, kr, n, S), build)
+            d.update(jobs=jt.data_ptr(), chunks=ct.data_ptr(), n_chunks=n_chunks,
+                     chunk_flags=ws.local(ws.flags + 4 * rt.CHUNK0))
+            if gather_x:
+                d.update(a_flag_mode=1, a_flag_base=xbase)
+            if gather_w:
+                d.update(b_flag_mode=2, b_flag_base=0, b_flag_count=1)
         if bias is not None:
             d["bias"] = bias.data_ptr()
         if act == "gelu":
@@ -218,14 +225,17 @@ class FusedGemm:
                 chunks.append((jb, len(jobs), [self._chunk_flag(q, s) for q in colp], self.grid * mc.R))
             return jobs, chunks
 
-        jt, ct, n_chunks = self._jobs(("ls", m, kl, nr, S), build)
         peers = mc.row_peers()  # owners of the output column blocks, indexed by column
         d = self._common(out, accumulate, stream)
-        d.update(M=m, N=N, K=kl, A=x.data_ptr(), B=wg, lda=x.stride(0), ldb=kl, a_mn_major=0,
-                 b_mn_major=0, slice_dim=1, n_slices=S, cyc=1, group=4,
-                 jobs=jt.data_ptr(), chunks=ct.data_ptr(), n_chunks=n_chunks,
-                 chunk_flags=ws.local(ws.flags + 4 * rt.CHUNK0),
-                 b_flag_mode=1, b_flag_base=0, gather_src1=w_mine,
+        gather_w = mc.R > 1     # a mesh column of one GPU already holds the whole W
+        d.update(M=m, N=N, K=kl, A=x.data_ptr(), B=wg if gather_w else w_mine, lda=x.stride(0), ldb=kl,
+                 a_mn_major=0, b_mn_major=0, slice_dim=1, n_slices=S, cyc=1, group=4, gather_src1=w_mine)
+        if gather_w:
+            jt, ct, n_chunks = self._jobs(("ls", m, kl, nr, S), build)
+            d.update(jobs=jt.data_ptr(), chunks=ct.data_ptr(), n_chunks=n_chunks,
+                     chunk_flags=ws.local(ws.flags + 4 * rt.CHUNK0), b_flag_mode=1, b_flag_base=0)
+        if mc.C > 1:   # a mesh row of one GPU keeps its product: plain epilogue into `out`
+            d.update(
                  push_n=mc.C, push_dim=1, push_extent=nc, push_ld=nc, push_rows=m,
                  push_base=[self.world.ptr(q, ws.slots) + mc.c * m * nc * 2 for q in peers],
                  push_counter=[self.world.flag_ptr(q, rt.COUNTER0) for q in peers],
@@ -274,14 +284,17 @@ class FusedGemm:
                 chunks.append((jb, len(jobs), [self._chunk_flag(q, s) for q in rowp], self.grid * mc.C))
             return jobs, chunks
 
-        jt, ct, n_chunks = self._jobs(("rs", kr, ml, n, S, cyc), build)
         peers = mc.col_peers()  # owners of the output row blocks, indexed by row
         d = self._common(out, accumulate, stream)
-        d.update(M=M, N=n, K=kr, A=xg, B=w.data_ptr(), lda=M, ldb=w.stride(0), a_mn_major=1,
-                 b_mn_major=1, slice_dim=0, n_slices=S, cyc=cyc, group=8,
-                 jobs=jt.data_ptr(), chunks=ct.data_ptr(), n_chunks=n_chunks,
-                 chunk_flags=ws.local(ws.flags + 4 * rt.CHUNK0),
-                 a_flag_mode=1, a_flag_base=0, gather_src0=x_mine,
+        gather_x = mc.C > 1     # a mesh row of one GPU already holds the whole X
+        d.update(M=M, N=n, K=kr, A=xg if gather_x else x_mine, B=w.data_ptr(), lda=M, ldb=w.stride(0),
+                 a_mn_major=1, b_mn_major=1, slice_dim=0, n_slices=S, cyc=cyc, group=8, gather_src0=x_mine)
+        if gather_x:
+            jt, ct, n_chunks = self._jobs(("rs", kr, ml, n, S, cyc), build)
+            d.update(jobs=jt.data_ptr(), chunks=ct.data_ptr(), n_chunks=n_chunks,
+                     chunk_flags=ws.local(ws.flags + 4 * rt.CHUNK0), a_flag_mode=1, a_flag_base=0)
+        if mc.R > 1:   # a mesh column of one GPU keeps its product: plain epilogue into `out`
+            d.update(
                  push_n=mc.R, push_dim=0, push_extent=mr, push_ld=n, push_rows=mr,
                  push_base=[self.world.ptr(q, ws.slots) + mc.r * mr * n * 2 for q in peers],
                  push_counter=[self.world.flag_ptr(q, rt.COUNTER0) for q in peers],
