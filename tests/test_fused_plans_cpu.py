@@ -1,0 +1,156 @@
+"""Host-side logic of the fused dataflows, checked without a GPU: the gather plans of all ranks
+of a mesh must fill every destination's staging buffer exactly once, chunk by chunk, and the
+flag targets / reduce targets must equal the number of arrivals the kernels produce."""
+import numpy as np
+import pytest
+
+from meshslice_b200.parallel import fused as fz
+from meshslice_b200.parallel import runtime as rt
+
+
+class FakeWS:
+    """Workspace with fake, non-overlapping 'addresses' per rank."""
+    def __init__(self, rank):
+        base = (rank + 1) << 40
+        self.flags, self.stage_a, self.stage_b, self.slots = 0, 1 << 20, 1 << 34, 1 << 36
+        self.stage_a_bytes = self.stage_b_bytes = self.slot_bytes = 1 << 33
+        self.base, self.epoch = base, 0
+
+    def local(self, off):
+        return self.base + off
+
+    def next_epoch(self):
+        self.epoch += 1
+        return self.epoch
+
+
+class FakeWorld:
+    def __init__(self, n, me):
+        self.wss = [FakeWS(r) for r in range(n)]
+        self.my_rank, self.size = me, n
+
+    @property
+    def mine(self):
+        return self.wss[self.my_rank]
+
+    def ptr(self, rank, off):
+        return self.wss[rank].base + off
+
+    def flag_ptr(self, rank, word):
+        return self.ptr(rank, 4 * word)
+
+
+def _capture(R, C, call):
+    """Runs `call(fg, mesh_coord)` for every rank and returns {rank: (plan, launch dict)}."""
+    out = {}
+    for r in range(R):
+        for c in range(C):
+            mc = fz.MeshCoord(R, C, r, c)
+            fg = fz.FusedGemm.__new__(fz.FusedGemm)
+            fg.mesh, fg.world, fg.grid, fg.timeout_ns, fg.use_barriers = mc, FakeWorld(R * C, mc.rank), 148, 1, False
+            fg._cache = {}
+            cap = {}
+            fg._jobs = lambda key, builder, cap=cap: (cap.setdefault("plan", builder()),
+                                                      type("T", (), {"data_ptr": lambda s: 1})(),
+                                                      type("T", (), {"data_ptr": lambda s: 2})(),
+                                                      len(cap["plan"][1]))[1:]
+            fg._launch = lambda d, exit_barrier, phase="all", reset=True, cap=cap: cap.setdefault("d", d)
+            fg._common = lambda out_, acc, stream: {}
+            call(fg, mc)
+            out[mc.rank] = cap
+    return out
+
+
+class FakeT:
+    def __init__(self, ptr, stride0):
+        self._p, self._s = ptr, stride0
+
+    def data_ptr(self):
+        return self._p
+
+    def stride(self, i):
+        return self._s
+
+
+@pytest.fixture(autouse=True)
+def _no_gpu(monkeypatch):
+    monkeypatch.setattr(fz._native, "stream_ptr", lambda: 0)
+
+
+def _coverage(caps, dst_rank, stage_off, total_bytes, fake_base):
+    """Bytes written into one destination's staging buffer by all ranks, as a counter array."""
+    cnt = np.zeros(total_bytes // 16, dtype=np.int32)
+    lo = fake_base + stage_off
+    for cap in caps.values():
+        if "plan" not in cap:
+            continue
+        jobs, _ = cap["plan"]
+        for sel, src, rows, rb, sp, dp, dsts in jobs:
+            for dptr in dsts:
+                if not (lo <= dptr < lo + total_bytes):
+                    continue
+                for r in range(rows):
+                    a = (dptr - lo + r * dp) // 16
+                    cnt[a:a + rb // 16] += 1
+    return cnt
+
+
+@pytest.mark.parametrize("mesh", [(2, 4), (4, 2), (1, 8), (8, 1), (2, 2)])
+def test_os_plans_fill_both_staging_buffers_once(mesh):
+    R, C = mesh
+    m, Kd, n = 1024, 2048, 512
+    kl, kr = Kd // C, Kd // R
+    caps = _capture(R, C, lambda fg, mc: fg.os([10 ** 9] * C, [2 * 10 ** 9] * R, m, kl, kr, n, None, n_slices=4))
+    for rank in range(R * C):
+        base = (rank + 1) << 40
+        if C > 1:
+            assert (_coverage(caps, rank, 1 << 20, m * Kd * 2, base) == 1).all()
+        if R > 1:
+            assert (_coverage(caps, rank, 1 << 34, Kd * n * 2, base) == 1).all()
+        d = caps[rank]["d"]
+        assert d["K"] == Kd and d["M"] == m and d["N"] == n
+        if C == 1:
+            assert d["A"] == 10 ** 9 and "a_flag_mode" not in d
+        if R == 1:
+            assert d["B"] == 2 * 10 ** 9 and "b_flag_mode" not in d
+    # flag targets: every CTA of every contributing GPU bumps each chunk once
+    if R > 1 and C > 1:
+        _, chunks = caps[0]["plan"]
+        assert chunks[0][3] == 148 * R and all(ch[3] == 148 * C for ch in chunks[1:])
+        assert len(chunks) == 1 + caps[0]["d"]["n_slices"]
+
+
+@pytest.mark.parametrize("mesh", [(2, 4), (4, 2), (2, 2)])
+def test_ls_and_rs_plans(mesh):
+    R, C = mesh
+    m, kl, nr = 512, 256, 1024 * C          # LS: X [m, kl], W shard [nr, kl]
+    N = nr * R
+    nc = N // C
+    caps = _capture(R, C, lambda fg, mc: fg.ls(FakeT(5, kl), [3 * 10 ** 9] * R, m, kl, nr, None, n_slices=4))
+    for rank in range(R * C):
+        assert (_coverage(caps, rank, 1 << 34, N * kl * 2, (rank + 1) << 40) == 1).all()
+        d = caps[rank]["d"]
+        S = d["n_slices"]
+        assert (nr // 256) % S == 0 and (nc // 256) % S == 0
+        # arrivals per slice at an owner: C senders x its column blocks in the slice x row tiles x 4 warps
+        assert d["red_target"] == C * (nc // 256 // S) * (m // 128) * 4
+        assert len(d["push_base"]) == C and d["push_rows"] == m
+    kr, ml, n = 384, 512 * R, 512             # RS: X shard [kr, ml], W [kr, n]
+    M = ml * C
+    mr = M // R
+    caps = _capture(R, C, lambda fg, mc: fg.rs([7 * 10 ** 9] * C, FakeT(6, n), kr, ml, n, None, n_slices=2, cyc=2))
+    for rank in range(R * C):
+        assert (_coverage(caps, rank, 1 << 20, kr * M * 2, (rank + 1) << 40) == 1).all()
+        d = caps[rank]["d"]
+        S, cyc = d["n_slices"], d["cyc"]
+        assert (ml // 256) % (S * cyc) == 0 and (mr // 256) % (S * cyc) == 0
+        assert d["red_target"] == R * (mr // 128 // S) * (n // 256) * 4
+
+
+def test_shapes_that_break_the_tile_rules_are_rejected():
+    caps = {}
+    with pytest.raises(fz.FusedPlanError):
+        _capture(2, 2, lambda fg, mc: fg.ls(FakeT(5, 64), [1] * 2, 100, 64, 256, None))
+    with pytest.raises(fz.FusedPlanError):
+        _capture(2, 2, lambda fg, mc: fg.rs([1] * 2, FakeT(6, 100), 64, 256, 100, None))
+    assert fz.pick_slices(8, 4) == 4 and fz.pick_slices(6, 4) == 3 and fz.pick_slices(4, 4, 2) == 2
