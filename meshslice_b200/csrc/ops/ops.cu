@@ -89,7 +89,7 @@ ln_fwd_kernel(int mode, const uint4* __restrict__ x, const uint4* __restrict__ r
     const int64_t base = (int64_t)row * nvec;
 #pragma unroll
     for (int k = 0; k < MAXV; ++k) {
-      const int v = threadIdx.x + k * kLnThreads;
+      const int v = threadIdx.x + k * blockDim.x;
       if (v < nvec) {
         unpack8(x[base + v], vals[k]);
         if (mode != 2 && res != nullptr) {
@@ -126,7 +126,7 @@ ln_fwd_kernel(int mode, const uint4* __restrict__ x, const uint4* __restrict__ r
     }
 #pragma unroll
     for (int k = 0; k < MAXV; ++k) {
-      const int v = threadIdx.x + k * kLnThreads;
+      const int v = threadIdx.x + k * blockDim.x;
       if (v < nvec) {
         float g[8], b[8], o[8];
         if (gamma != nullptr) unpack8(gamma[v], g);
@@ -170,7 +170,7 @@ ln_bwd_kernel(int mode, const uint4* __restrict__ dy, const uint4* __restrict__ 
     float s1 = 0.f, s2 = 0.f;
 #pragma unroll
     for (int k = 0; k < MAXV; ++k) {
-      const int v = threadIdx.x + k * kLnThreads;
+      const int v = threadIdx.x + k * blockDim.x;
       if (v < nvec) {
         float d[8], hv[8], gm[8];
         unpack8(dy[base + v], d);
@@ -199,7 +199,7 @@ ln_bwd_kernel(int mode, const uint4* __restrict__ dy, const uint4* __restrict__ 
     const float m1 = s1 / (float)total_cols, m2 = s2 / (float)total_cols;
 #pragma unroll
     for (int k = 0; k < MAXV; ++k) {
-      const int v = threadIdx.x + k * kLnThreads;
+      const int v = threadIdx.x + k * blockDim.x;
       if (v < nvec) {
         float o[8];
 #pragma unroll
@@ -217,7 +217,7 @@ ln_bwd_kernel(int mode, const uint4* __restrict__ dy, const uint4* __restrict__ 
   if (want_param_grads) {
 #pragma unroll
     for (int k = 0; k < MAXV; ++k) {
-      const int v = threadIdx.x + k * kLnThreads;
+      const int v = threadIdx.x + k * blockDim.x;
       if (v < nvec) {
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
@@ -467,6 +467,16 @@ __global__ void embedding_bwd_pos_kernel(const uint4* __restrict__ dout, float* 
   }
 }
 
+// One CTA per row: as many threads as the row has 16-byte vectors (64..256), so that short
+// column-sharded rows do not leave half of the CTA idle.
+inline int ln_threads(int cols) {
+  const int nvec = cols / 8;
+  int t = (nvec + 31) / 32 * 32;
+  if (t < 64) t = 64;
+  if (t > kLnThreads) t = kLnThreads;
+  return t;
+}
+
 inline int grid_for(int64_t n, int threads, int cap = 148 * 16) {
   int64_t g = (n + threads - 1) / threads;
   if (g > cap) g = cap;
@@ -483,20 +493,23 @@ cudaError_t ln_fwd(int mode, const void* x, const void* res, void* h_out, void* 
                    const void* gamma, const void* beta, float* stats, float* mean_rstd, int rows,
                    int cols, int total_cols, float eps, cudaStream_t stream) {
   if (cols % 8 != 0 || cols > 8 * kLnThreads * 8) return cudaErrorInvalidValue;
-  const int grid = rows < 148 * 8 ? rows : 148 * 8;
+  const int grid = rows < 148 * 16 ? rows : 148 * 16;
   auto X = reinterpret_cast<const uint4*>(x);
   auto R = reinterpret_cast<const uint4*>(res);
   auto H = reinterpret_cast<uint4*>(h_out);
   auto Y = reinterpret_cast<uint4*>(y);
   auto G = reinterpret_cast<const uint4*>(gamma);
   auto B = reinterpret_cast<const uint4*>(beta);
-  const int nvec_per_thread = (cols / 8 + kLnThreads - 1) / kLnThreads;
-  if (nvec_per_thread <= 2)
-    ln_fwd_kernel<2><<<grid, kLnThreads, 0, stream>>>(mode, X, R, H, Y, G, B, stats, mean_rstd, rows, cols, total_cols, eps);
+  const int threads = ln_threads(cols);
+  const int nvec_per_thread = (cols / 8 + threads - 1) / threads;
+  if (nvec_per_thread <= 1)
+    ln_fwd_kernel<1><<<grid, threads, 0, stream>>>(mode, X, R, H, Y, G, B, stats, mean_rstd, rows, cols, total_cols, eps);
+  else if (nvec_per_thread <= 2)
+    ln_fwd_kernel<2><<<grid, threads, 0, stream>>>(mode, X, R, H, Y, G, B, stats, mean_rstd, rows, cols, total_cols, eps);
   else if (nvec_per_thread <= 4)
-    ln_fwd_kernel<4><<<grid, kLnThreads, 0, stream>>>(mode, X, R, H, Y, G, B, stats, mean_rstd, rows, cols, total_cols, eps);
+    ln_fwd_kernel<4><<<grid, threads, 0, stream>>>(mode, X, R, H, Y, G, B, stats, mean_rstd, rows, cols, total_cols, eps);
   else
-    ln_fwd_kernel<8><<<grid, kLnThreads, 0, stream>>>(mode, X, R, H, Y, G, B, stats, mean_rstd, rows, cols, total_cols, eps);
+    ln_fwd_kernel<8><<<grid, threads, 0, stream>>>(mode, X, R, H, Y, G, B, stats, mean_rstd, rows, cols, total_cols, eps);
   return cudaGetLastError();
 }
 
@@ -504,19 +517,22 @@ cudaError_t ln_bwd(int mode, const void* dy, const void* h, const void* gamma,
                    const float* mean_rstd, const void* dres, void* dx, float* stats, float* dgamma,
                    float* dbeta, int rows, int cols, int total_cols, cudaStream_t stream) {
   if (cols % 8 != 0 || cols > 8 * kLnThreads * 8) return cudaErrorInvalidValue;
-  const int grid = rows < 148 * 4 ? rows : 148 * 4;
+  const int grid = rows < 148 * 8 ? rows : 148 * 8;
   auto DY = reinterpret_cast<const uint4*>(dy);
   auto H = reinterpret_cast<const uint4*>(h);
   auto G = reinterpret_cast<const uint4*>(gamma);
   auto DR = reinterpret_cast<const uint4*>(dres);
   auto DX = reinterpret_cast<uint4*>(dx);
-  const int nvec_per_thread = (cols / 8 + kLnThreads - 1) / kLnThreads;
-  if (nvec_per_thread <= 2)
-    ln_bwd_kernel<2><<<grid, kLnThreads, 0, stream>>>(mode, DY, H, G, mean_rstd, DR, DX, stats, dgamma, dbeta, rows, cols, total_cols);
+  const int threads = ln_threads(cols);
+  const int nvec_per_thread = (cols / 8 + threads - 1) / threads;
+  if (nvec_per_thread <= 1)
+    ln_bwd_kernel<1><<<grid, threads, 0, stream>>>(mode, DY, H, G, mean_rstd, DR, DX, stats, dgamma, dbeta, rows, cols, total_cols);
+  else if (nvec_per_thread <= 2)
+    ln_bwd_kernel<2><<<grid, threads, 0, stream>>>(mode, DY, H, G, mean_rstd, DR, DX, stats, dgamma, dbeta, rows, cols, total_cols);
   else if (nvec_per_thread <= 4)
-    ln_bwd_kernel<4><<<grid, kLnThreads, 0, stream>>>(mode, DY, H, G, mean_rstd, DR, DX, stats, dgamma, dbeta, rows, cols, total_cols);
+    ln_bwd_kernel<4><<<grid, threads, 0, stream>>>(mode, DY, H, G, mean_rstd, DR, DX, stats, dgamma, dbeta, rows, cols, total_cols);
   else
-    ln_bwd_kernel<8><<<grid, kLnThreads, 0, stream>>>(mode, DY, H, G, mean_rstd, DR, DX, stats, dgamma, dbeta, rows, cols, total_cols);
+    ln_bwd_kernel<8><<<grid, threads, 0, stream>>>(mode, DY, H, G, mean_rstd, DR, DX, stats, dgamma, dbeta, rows, cols, total_cols);
   return cudaGetLastError();
 }
 
