@@ -41,7 +41,6 @@ __device__ __forceinline__ float warp_max(float v) {
 __device__ __forceinline__ void block_sum2(float& a, float& b, float* red) {
   a = warp_sum(a);
   b = warp_sum(b);
-  if (blockDim.x == 32) return;   // one warp per row: nothing to combine across warps
   const int w = threadIdx.x >> 5, l = threadIdx.x & 31, nw = blockDim.x >> 5;
   __syncthreads();
   if (l == 0) { red[w] = a; red[32 + w] = b; }
@@ -84,7 +83,7 @@ ln_fwd_kernel(int mode, const uint4* __restrict__ x, const uint4* __restrict__ r
               float* __restrict__ mean_rstd, int rows, int cols, int total_cols, float eps) {
   __shared__ float red[64];
   const int nvec = cols >> 3;
-  for (int row = blockIdx.x * blockDim.y + threadIdx.y; row < rows; row += gridDim.x * blockDim.y) {
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
     float vals[MAXV][8];
     float s = 0.f, ss = 0.f;
     const int64_t base = (int64_t)row * nvec;
@@ -164,7 +163,7 @@ ln_bwd_kernel(int mode, const uint4* __restrict__ dy, const uint4* __restrict__ 
     for (int i = 0; i < 8; ++i) { accg[k][i] = 0.f; accb[k][i] = 0.f; }
   const bool want_param_grads = mode != 2 && dgamma != nullptr;
 
-  for (int row = blockIdx.x * blockDim.y + threadIdx.y; row < rows; row += gridDim.x * blockDim.y) {
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
     const float mean = mean_rstd[2 * row], rstd = mean_rstd[2 * row + 1];
     const int64_t base = (int64_t)row * nvec;
     float g[MAXV][8], xh[MAXV][8];
@@ -478,31 +477,6 @@ inline int ln_threads(int cols) {
   return t;
 }
 
-// Rows of up to 2048 columns get one warp each (eight rows per CTA, shuffle-only reductions);
-// longer rows get one CTA each with as many threads as the row has 16-byte vectors.
-struct LnCfg {
-  dim3 block;
-  int grid;
-  int nvec_per_thread;
-};
-inline LnCfg ln_config(int rows, int cols, int max_ctas) {
-  LnCfg c;
-  const int nvec = cols / 8;
-  if (nvec <= 256) {
-    c.block = dim3(32, 8, 1);
-    c.nvec_per_thread = (nvec + 31) / 32;
-    const int need = (rows + 7) / 8;
-    c.grid = need < max_ctas ? need : max_ctas;
-  } else {
-    const int t = ln_threads(cols);
-    c.block = dim3(t, 1, 1);
-    c.nvec_per_thread = (nvec + t - 1) / t;
-    c.grid = rows < 2 * max_ctas ? rows : 2 * max_ctas;
-  }
-  if (c.grid < 1) c.grid = 1;
-  return c;
-}
-
 inline int grid_for(int64_t n, int threads, int cap = 148 * 16) {
   int64_t g = (n + threads - 1) / threads;
   if (g > cap) g = cap;
@@ -519,16 +493,15 @@ cudaError_t ln_fwd(int mode, const void* x, const void* res, void* h_out, void* 
                    const void* gamma, const void* beta, float* stats, float* mean_rstd, int rows,
                    int cols, int total_cols, float eps, cudaStream_t stream) {
   if (cols % 8 != 0 || cols > 8 * kLnThreads * 8) return cudaErrorInvalidValue;
+  const int grid = rows < 148 * 16 ? rows : 148 * 16;
   auto X = reinterpret_cast<const uint4*>(x);
   auto R = reinterpret_cast<const uint4*>(res);
   auto H = reinterpret_cast<uint4*>(h_out);
   auto Y = reinterpret_cast<uint4*>(y);
   auto G = reinterpret_cast<const uint4*>(gamma);
   auto B = reinterpret_cast<const uint4*>(beta);
-  LnCfg cfg = ln_config(rows, cols, 148 * 8);
-  const dim3 threads = cfg.block;
-  const int grid = cfg.grid;
-  const int nvec_per_thread = cfg.nvec_per_thread;
+  const int threads = ln_threads(cols);
+  const int nvec_per_thread = (cols / 8 + threads - 1) / threads;
   if (nvec_per_thread <= 1)
     ln_fwd_kernel<1><<<grid, threads, 0, stream>>>(mode, X, R, H, Y, G, B, stats, mean_rstd, rows, cols, total_cols, eps);
   else if (nvec_per_thread <= 2)
@@ -544,15 +517,14 @@ cudaError_t ln_bwd(int mode, const void* dy, const void* h, const void* gamma,
                    const float* mean_rstd, const void* dres, void* dx, float* stats, float* dgamma,
                    float* dbeta, int rows, int cols, int total_cols, cudaStream_t stream) {
   if (cols % 8 != 0 || cols > 8 * kLnThreads * 8) return cudaErrorInvalidValue;
+  const int grid = rows < 148 * 8 ? rows : 148 * 8;
   auto DY = reinterpret_cast<const uint4*>(dy);
   auto H = reinterpret_cast<const uint4*>(h);
   auto G = reinterpret_cast<const uint4*>(gamma);
   auto DR = reinterpret_cast<const uint4*>(dres);
   auto DX = reinterpret_cast<uint4*>(dx);
-  LnCfg cfg = ln_config(rows, cols, 148 * 4);
-  const dim3 threads = cfg.block;
-  const int grid = cfg.grid;
-  const int nvec_per_thread = cfg.nvec_per_thread;
+  const int threads = ln_threads(cols);
+  const int nvec_per_thread = (cols / 8 + threads - 1) / threads;
   if (nvec_per_thread <= 1)
     ln_bwd_kernel<1><<<grid, threads, 0, stream>>>(mode, DY, H, G, mean_rstd, DR, DX, stats, dgamma, dbeta, rows, cols, total_cols);
   else if (nvec_per_thread <= 2)

@@ -86,7 +86,12 @@ class GPTBlock:
         a = self.out_proj.forward(self.attn.forward(self.in_proj.forward(y)))
         y = self.ln2.forward(a, x)                # h = x + a
         h = self.ln2.h
-        m = self.ff2.forward(self.gelu.forward(self.ff1.forward(y)))
+        if self.ff1._fused and self.ff1.dataflow == "os":
+            g, pre = self.ff1.forward_gelu(y)          # GeLU in the GEMM epilogue
+            self.gelu.remember(pre)
+        else:
+            g = self.gelu.forward(self.ff1.forward(y))
+        m = self.ff2.forward(g)
         return h, m
 
     def backward(self, dh: ShardedTensor, dm: ShardedTensor):

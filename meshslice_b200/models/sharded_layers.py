@@ -72,6 +72,18 @@ class ShardedFFLayer:
         for k, g in self.grad.shards.items():
             g += dw.shards[k]
 
+    def forward_gelu(self, x: ShardedTensor):
+        """y = gelu(x @ W) with the activation applied in the GEMM epilogue (fused 'os' layers
+        only).  Returns (gelu output, pre-activation); the caller keeps the latter for backward."""
+        if not (self._fused and self.dataflow == "os"):
+            raise RuntimeError("forward_gelu needs a fused 'os' layer")
+        self._x = x
+        (key, xl), = x.shards.items()
+        m, n = xl.shape[0], self.weight.shards[key].shape[1]
+        pre = torch.empty(m, n, dtype=xl.dtype, device=xl.device)
+        y = self._OS(x, self.weight, act="gelu", pre_act=pre)
+        return y, ShardedTensor(self.mesh, {key: pre})
+
     def forward(self, x: ShardedTensor) -> ShardedTensor:
         self._x = x
         w = self.weight
@@ -208,6 +220,10 @@ class ShardedAttention:
 class GeLU:
     def __init__(self):
         self._x = None
+
+    def remember(self, pre_activation: ShardedTensor):
+        """Used when the forward pass was fused into the producing GEMM's epilogue."""
+        self._x = pre_activation
 
     def forward(self, x: ShardedTensor) -> ShardedTensor:
         self._x = x
