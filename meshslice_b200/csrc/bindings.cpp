@@ -97,6 +97,8 @@ void gemm_run(const py::dict& d) {
   if (a.n_slices < 1 || tiles_s % (a.n_slices * a.cyc) != 0)
     throw std::runtime_error("gemm: n_slices must divide the tile count of the sliced dimension");
   if (a.group < 1) a.group = 1;
+  a.rot = (int)geti(d, "rot", 0);
+  if (a.rot < 0 || a.rot >= tiles_s / a.n_slices) a.rot = 0;
   if (geti(d, "no_tiles")) a.tiles_m = 0;  // reduce phase only
   // pull side
   a.jobs = P<const PushJob>(getp(d, "jobs"));

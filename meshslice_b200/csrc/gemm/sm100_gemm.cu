@@ -97,7 +97,8 @@ __device__ __forceinline__ TileCoord tile_coord(int t, const GemmArgs& a) {
   const int geff = min(a.group, nb - g0);
   const int o = rr / geff;
   const int w = rr - o * geff;
-  const int jj = g0 + w;
+  int jj = g0 + w + a.rot;
+  if (jj >= nb) jj -= nb;
   const int cg = jj / a.cyc;
   const int blk_s = (cg * S + s) * a.cyc + (jj - cg * a.cyc);
   TileCoord c;

@@ -104,6 +104,8 @@ struct GemmArgs {
   int n_slices;        // block-cyclic slices of the sliced dimension (divides its tile count)
   int group;           // raster group size along the sliced dimension
   int cyc;             // tiles per cyclic block: slice s holds blocks (g*n_slices + s)*cyc + w
+  int rot;             // rotation of the block order inside a slice (ranks of a push group start at
+                       // different owners, so no owner's NVLink ingress is hit by all ranks at once)
   // ---- gather side (all-gather -> GEMM) ----
   const PushJob* jobs;
   const char* gather_src[2];   // local shards the jobs read from (so plans do not depend on them)

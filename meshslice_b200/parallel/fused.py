@@ -53,6 +53,13 @@ class FusedPlanError(ValueError):
     """The shapes do not meet the divisibility rules of the fused kernel."""
 
 
+def _push_rotation(index: int, group: int, blocks_per_slice: int) -> int:
+    """Block offset at which a rank starts every slice: the blocks of the *next* rank of its push
+    group.  All ranks walk the owners in the same cyclic order but from different starting points,
+    so at any time each owner receives from one rank, and a rank's own (local) blocks come last."""
+    return ((index + 1) % group) * (blocks_per_slice // group)
+
+
 def pick_slices(n_blocks_per_part: int, want: int, cyc: int = 1) -> int:
     """Largest slice count <= want such that slices * cyc divides the blocks of every part."""
     s = max(1, min(want, n_blocks_per_part // cyc if cyc else 1))
@@ -241,7 +248,8 @@ class FusedGemm:
                  push_counter=[self.world.flag_ptr(q, rt.COUNTER0) for q in peers],
                  red_n=mc.C, red_slots=ws.local(ws.slots), red_rows=m, red_cols=nc, red_ld=nc,
                  red_counter=ws.local(ws.flags + 4 * rt.COUNTER0),
-                 red_target=mc.C * (blocks_own // S) * (m // CTA_M) * 4, red_slice_dim=1)
+                 red_target=mc.C * (blocks_own // S) * (m // CTA_M) * 4, red_slice_dim=1,
+                 rot=_push_rotation(mc.c, mc.C, tiles_n // S))
         self._launch(d, exit_barrier=False, phase=phase, reset=reset)
         return out
 
@@ -300,6 +308,7 @@ class FusedGemm:
                  push_counter=[self.world.flag_ptr(q, rt.COUNTER0) for q in peers],
                  red_n=mc.R, red_slots=ws.local(ws.slots), red_rows=mr, red_cols=n, red_ld=n,
                  red_counter=ws.local(ws.flags + 4 * rt.COUNTER0),
-                 red_target=mc.R * ((mr // BM) // S) * 2 * tiles_n * 4, red_slice_dim=0)
+                 red_target=mc.R * ((mr // BM) // S) * 2 * tiles_n * 4, red_slice_dim=0,
+                 rot=_push_rotation(mc.r, mc.R, tiles_m // S))
         self._launch(d, exit_barrier=False, phase=phase, reset=reset)
         return out
