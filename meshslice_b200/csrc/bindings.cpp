@@ -119,6 +119,8 @@ void gemm_run(const py::dict& d) {
   if (a.push_n > kMaxPeers) throw std::runtime_error("gemm: too many owners");
   a.push_dim = (int)geti(d, "push_dim");
   a.push_extent = (int)geti(d, "push_extent", 1);
+  a.push_bufs = (int)geti(d, "push_bufs", 1);
+  a.push_mode = (int)geti(d, "push_mode", 0);
   a.push_ld = geti(d, "push_ld");
   if (a.push_n > 0) {
     auto pb = d["push_base"].cast<std::vector<uint64_t>>();

@@ -422,6 +422,10 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
   const int cluster_id = blockIdx.x >> 1, n_clusters = gridDim.x >> 1;
   const uint64_t tmo = a.timeout_ns;
   const int num_tiles = a.tiles_m * a.tiles_n;   // 256 x 256 cluster tiles
+  // Deep push staging gives up the last pipeline stage: its A and B buffers become the second and
+  // third staging buffer of each epilogue warp (more tensor stores in flight towards the owners).
+  const bool deep_push = a.push_n > 0 && a.push_bufs >= 3 && a.push_mode == 0;
+  const uint32_t nst = deep_push ? kStages - 1 : kStages;
   const int kblocks = (a.K + kBK - 1) / kBK;
 
   if (warp == 0 && lane == 0) {
@@ -499,7 +503,7 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
             for (int j = 0; j < kBN / 128; ++j)
               tma_load_2d_pair(db + j * (kBK * 128), &tma_b, fb, col_b + j * 64, kb * kBK);
           }
-          if (++stage == kStages) { stage = 0; phase ^= 1; }
+          if (++stage == nst) { stage = 0; phase ^= 1; }
         }
       }
     }
@@ -541,7 +545,7 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
           const uint32_t eb = smem_u32(empty_bar + stage);
           umma_commit_pair(eb);                // this CTA's stage is free again
           umma_commit_pair(mapa_u32(eb, 1));   // and so is the peer's
-          if (++stage == kStages) { stage = 0; phase ^= 1; }
+          if (++stage == nst) { stage = 0; phase ^= 1; }
         }
         if (ok) {
           const uint32_t tb = smem_u32(tfull_bar + acc);
@@ -558,6 +562,7 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
     int it = 0;
     bool pend_valid = false;   // push path: a tile whose arrival has not been counted yet
     int pend_owner = 0, pend_slice = 0;
+    int push_seq = 0;          // staging buffer of the next band (deep push: three per warp)
     for (int t = cluster_id; t < num_tiles && ok; t += n_clusters, ++it) {
       const TileCoord tc = tile_coord(t, a);
       const uint32_t acc = it & 1, acc_phase = (it >> 1) & 1;
@@ -575,6 +580,14 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
       }
       mbar_wait(tfull_bar + acc, acc_phase, tmo);  // already complete: orders this lane's reads
       tc_fence_after_sync();
+      if (a.push_mode == 1 && pend_valid) {
+        // Direct-store push: count the PREVIOUS tile at its owner.  Its stores were issued a whole
+        // tile ago, so the fence that orders them before the counter finds them already performed.
+        __threadfence_system();
+        __syncwarp();
+        if (lane == 0) red_add_release_sys(a.push_counter[pend_owner] + pend_slice, 1u);
+        pend_valid = false;
+      }
       const int64_t row = (int64_t)m_blk * kBM + q * 32 + lane;
       const bool row_ok = row < a.M;
       // destination of this tile
@@ -599,7 +612,10 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
         // Push path: 64 columns at a time go through this warp's 4 KiB staging buffer (128-byte
         // swizzled, so the lanes' row writes spread over the banks) and leave as ONE 2-D TMA
         // tensor store of 32 rows x 128 bytes into the owner's slot (posted writes over NVLink).
-        uint8_t* stage = sEpi + (warp - 2) * kEpiStageBytes;
+        uint8_t* stage_buf[3];
+        stage_buf[0] = sEpi + (warp - 2) * kEpiStageBytes;
+        stage_buf[1] = sA + (kStages - 1) * kAStageBytes + (warp - 2) * kEpiStageBytes;
+        stage_buf[2] = sB + (kStages - 1) * kBStageBytes + (warp - 2) * kEpiStageBytes;
         const CUtensorMap* omap = &pmaps.m[owner];
         const int32_t y0 = (int32_t)(orow - lane);   // first row of this warp's 32-row band
 #pragma unroll 1
@@ -613,7 +629,15 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
             tc_fence_before_sync();
             mbar_arrive_cluster(te_leader);
           }
-          if (lane == 0) bulk_wait_read<0>();   // the previous store has left the staging buffer
+          // the store that last used this staging buffer has left it
+          uint8_t* stage = stage_buf[0];
+          if (deep_push) {
+            stage = push_seq == 0 ? stage_buf[0] : (push_seq == 1 ? stage_buf[1] : stage_buf[2]);
+            if (++push_seq == 3) push_seq = 0;
+            if (lane == 0) bulk_wait_read<2>();
+          } else if (a.push_mode == 0) {
+            if (lane == 0) bulk_wait_read<0>();
+          }
           __syncwarp();
           uint8_t* srow = stage + lane * 128;
 #pragma unroll
@@ -627,6 +651,21 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
             u.w = pack_bf16(__uint_as_float(r[b + 6]), __uint_as_float(r[b + 7]));
             *reinterpret_cast<uint4*>(srow + ((k ^ (lane & 7)) << 4)) = u;
           }
+          if (a.push_mode == 1) {
+            // Read the band back row-major (4 rows x 128 bytes per instruction, conflict-free through
+            // the same swizzle) and write it with ordinary 16-byte stores: posted writes that the
+            // load/store units keep in flight by the hundred, unlike the bulk-store engine.
+            __syncwarp();
+            char* gband = reinterpret_cast<char*>(out) +
+                          (((orow - lane) * ld) + (tc.n_blk * kBN + c2 * 64 - ocol_shift)) * 2;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const int rr = i * 4 + (lane >> 3), ch = lane & 7;
+              const uint4 v = *reinterpret_cast<const uint4*>(stage + rr * 128 + ((ch ^ (rr & 7)) << 4));
+              *reinterpret_cast<uint4*>(gband + (int64_t)rr * ld * 2 + ch * 16) = v;
+            }
+            continue;
+          }
           fence_proxy_async_smem();
           __syncwarp();
           if (lane == 0) {
@@ -639,7 +678,7 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
         }
         // Count the PREVIOUS tile at its owner now: its row stores are the groups older than the
         // four just committed, so waiting for them costs no NVLink round trip on this tile.
-        if (pend_valid && lane == 0) {
+        if (a.push_mode == 0 && pend_valid && lane == 0) {
           bulk_wait_all<kBN / 64>();
           fence_proxy_async();
           __threadfence_system();
@@ -680,6 +719,12 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
           }
         }
       }
+    }
+    if (a.push_mode == 1 && pend_valid) {
+      __threadfence_system();
+      __syncwarp();
+      if (lane == 0) red_add_release_sys(a.push_counter[pend_owner] + pend_slice, 1u);
+      pend_valid = false;
     }
     if (pend_valid && lane == 0) {
       // last tile of this CTA: all of this warp's tensor stores must have completed

@@ -121,6 +121,8 @@ struct GemmArgs {
   int push_n;                  // number of owners (0: local epilogue)
   int push_dim;                // 0: owners split M, 1: owners split N
   int push_extent;             // rows (or columns) owned by each owner
+  int push_mode;               // 0: 2-D TMA tensor stores, 1: ordinary 16-byte stores from the staging buffer
+  int push_bufs;               // staging buffers per epilogue warp: 1, or 3 (then one pipeline stage fewer)
   void* push_base[kMaxPeers];  // owner o's slot for this source (bf16 [rows_local, ld])
   int64_t push_ld;
   uint32_t* push_counter[kMaxPeers];  // owner o's per-slice arrival counters

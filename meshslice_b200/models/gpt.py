@@ -12,6 +12,8 @@ the optimizer is one kernel launch per buffer; gradients mirror them.
 """
 from __future__ import annotations
 
+import os
+
 from dataclasses import dataclass, field
 from typing import List, Optional, Tuple
 
@@ -20,6 +22,9 @@ import torch
 from ..ops import functional as F
 from ..parallel.mesh import Mesh, ShardedTensor
 from .sharded_layers import GeLU, ShardedAttention, ShardedFFLayer, ShardedLayerNorm, _add
+
+# GeLU inside the ff1 GEMM epilogue (MSB_FUSED_GELU=0 runs the stand-alone kernel instead)
+_FUSE_GELU = os.environ.get("MSB_FUSED_GELU", "1") != "0"
 
 
 @dataclass
@@ -86,7 +91,7 @@ class GPTBlock:
         a = self.out_proj.forward(self.attn.forward(self.in_proj.forward(y)))
         y = self.ln2.forward(a, x)                # h = x + a
         h = self.ln2.h
-        if self.ff1._fused and self.ff1.dataflow == "os":
+        if self.ff1._fused and self.ff1.dataflow == "os" and _FUSE_GELU:
             g, pre = self.ff1.forward_gelu(y)          # GeLU in the GEMM epilogue
             self.gelu.remember(pre)
         else:

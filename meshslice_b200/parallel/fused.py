@@ -17,6 +17,8 @@ depend on the slice count.
 """
 from __future__ import annotations
 
+import os
+
 from dataclasses import dataclass
 from typing import List
 
@@ -57,6 +59,8 @@ def _push_rotation(index: int, group: int, blocks_per_slice: int) -> int:
     """Block offset at which a rank starts every slice: the blocks of the *next* rank of its push
     group.  All ranks walk the owners in the same cyclic order but from different starting points,
     so at any time each owner receives from one rank, and a rank's own (local) blocks come last."""
+    if os.environ.get("MSB_PUSH_ROT", "1") == "0":
+        return 0
     return ((index + 1) % group) * (blocks_per_slice // group)
 
 
@@ -100,6 +104,10 @@ class FusedGemm:
         self.use_barriers = use_barriers
         self.C = _native.load()
         self._cache = {}
+        # staging buffers per epilogue warp of the push kernels (3 costs one pipeline stage)
+        self.push_bufs = int(os.environ.get("MSB_PUSH_BUFS", "1"))
+        # how partial tiles reach their owner: 0 = 2-D TMA tensor stores, 1 = ordinary 16-byte stores
+        self.push_mode = int(os.environ.get("MSB_PUSH_MODE", "1"))
 
     # ------------------------------------------------------------------ helpers
     def _reset_flags(self, stream):
@@ -125,6 +133,9 @@ class FusedGemm:
         """phases 'comm' (gather only), 'gemm' (tiles only) and 'reduce' (slot sums only) split one
         launch in three; together with reset=False this lets a test run several emulated ranks
         one after another on one GPU without any launch waiting for a kernel that is not running."""
+        if d.get("push_n", 0):
+            d["push_bufs"] = self.push_bufs
+            d["push_mode"] = self.push_mode
         if reset:
             self._reset_flags(d["stream"])
         if phase == "comm":          # only move the gathered operands
