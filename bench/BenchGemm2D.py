@@ -43,6 +43,9 @@ def main():
     ap.add_argument("--shapes", type=int, nargs="*", default=[], help="M K N triples; default: the four headline shapes")
     ap.add_argument("--peak-tflops", type=float, default=1380.6)
     ap.add_argument("--link-gbs", type=float, default=770.0)
+    ap.add_argument("--baselines", nargs="*", default=[], choices=["summa", "wang", "cannon"],
+                    help="also time the OS product on these K-panel schedules")
+    ap.add_argument("--sub", type=int, default=2, help="sub-panels per owner for --baselines")
     ap.add_argument("--json", default="")
     args = ap.parse_args()
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
@@ -86,6 +89,15 @@ def main():
                 eng.check()
                 row["fused"][s] = dict(ms=t * 1e3, tflops=flops / t / 1e12, roofline_frac=roof / t,
                                        speedup_vs_nccl=t_base / t)
+            if df == "os" and args.baselines:
+                # SUMMA / Wang / Cannon on the same kernel: K panels consumed in that algorithm's order
+                row["k_panel"] = {}
+                for order in args.baselines:
+                    if order == "cannon" and R != C:
+                        continue
+                    t = timeit(lambda: eng.os_kpanel(x, w, order=order, sub=args.sub))
+                    eng.check()
+                    row["k_panel"][order] = dict(ms=t * 1e3, tflops=flops / t / 1e12, roofline_frac=roof / t)
             say(json.dumps(row))
             out.append(row)
     if rank == 0 and args.json:

@@ -114,6 +114,14 @@ void gemm_run(const py::dict& d) {
   a.b_flag_mode = (int)geti(d, "b_flag_mode");
   a.b_flag_base = (int)geti(d, "b_flag_base");
   a.b_flag_count = (int)geti(d, "b_flag_count");
+  a.a_kpanel = (int)geti(d, "a_kpanel", 1);
+  a.b_kpanel = (int)geti(d, "b_kpanel", 1);
+  a.kp_target = (uint32_t)geti(d, "kp_target", 0);
+  a.k_rot = (int)geti(d, "k_rot", 0);
+  if (a.a_kpanel < 1 || a.b_kpanel < 1 || a.k_rot < 0 || a.k_rot >= std::max<int64_t>(1, (a.K + kBK - 1) / kBK))
+    throw std::runtime_error("gemm: bad K-panel schedule");
+  if ((a.a_flag_mode == 3 || a.b_flag_mode == 3) && a.K % kBK != 0)
+    throw std::runtime_error("gemm: the K-panel schedule needs K to be a multiple of 64");
   // push side
   a.push_n = (int)geti(d, "push_n");
   if (a.push_n > kMaxPeers) throw std::runtime_error("gemm: too many owners");

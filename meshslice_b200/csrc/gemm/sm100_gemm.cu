@@ -139,7 +139,7 @@ __device__ __forceinline__ bool wait_chunk(const GemmArgs& a, int idx, uint64_t 
 // chunk pays for the system-scope flag reads.
 __device__ __forceinline__ bool wait_operand(const GemmArgs& a, int mode, int base, int count,
                                              int slice, uint64_t tmo, uint64_t& seen) {
-  if (mode == 0) return true;
+  if (mode == 0 || mode == 3) return true;   // mode 3 is waited for inside the contraction loop
   const int lo = mode == 1 ? base + slice : base;
   const int hi = mode == 1 ? lo + 1 : base + count;
   for (int i = lo; i < hi; ++i) {
@@ -148,6 +148,17 @@ __device__ __forceinline__ bool wait_operand(const GemmArgs& a, int mode, int ba
     if (!wait_chunk(a, i, tmo)) return false;
     if (i < 64) seen |= bit;
   }
+  return true;
+}
+
+// K-panel schedule: flag `idx` counts to kp_target (one source GPU per panel).
+__device__ __forceinline__ bool wait_panel(const GemmArgs& a, int idx, uint64_t tmo, uint64_t& seen,
+                                           bool& fresh) {
+  const uint64_t bit = 1ull << (idx & 63);
+  if (idx < 64 && (seen & bit)) return true;
+  if (!wait_flag_geq_sys(a.chunk_flags + idx, a.kp_target, tmo)) return false;
+  if (idx < 64) seen |= bit;
+  fresh = true;
   return true;
 }
 
@@ -465,6 +476,7 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
       }
       uint32_t stage = 0, phase = 0;
       uint64_t seen = 0;
+      const bool kpanels = a.a_flag_mode == 3 || a.b_flag_mode == 3;
       for (int t = cluster_id; t < num_tiles && ok; t += n_clusters) {
         const TileCoord tc = tile_coord(t, a);
         if (a.a_flag_mode | a.b_flag_mode) {
@@ -479,7 +491,22 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
         }
         const int row_a = (2 * tc.m_blk + (int)rank) * kBM;        // this CTA's 128 rows of A
         const int col_b = tc.n_blk * kBN + (int)rank * (kBN / 2);  // this CTA's 128 columns of B
-        for (int kb = 0; kb < kblocks; ++kb) {
+        for (int kb0 = 0; kb0 < kblocks; ++kb0) {
+          int kb = kb0 + a.k_rot;   // the contraction loop may start anywhere: sums commute
+          if (kb >= kblocks) kb -= kblocks;
+          if (kpanels) {
+            // K-panel schedule: the first k-block of a panel waits for the panel's flag
+            bool fresh = false;
+            if (a.a_flag_mode == 3 && (kb0 == 0 || kb % a.a_kpanel == 0))
+              ok = ok && wait_panel(a, a.a_flag_base + kb / a.a_kpanel, 3 * tmo, seen, fresh);
+            if (a.b_flag_mode == 3 && (kb0 == 0 || kb % a.b_kpanel == 0))
+              ok = ok && wait_panel(a, a.b_flag_base + kb / a.b_kpanel, 3 * tmo, seen, fresh);
+            if (!ok) {
+              report(a, kTimeoutChunk, t, 0x10000u + kb);
+              break;
+            }
+            if (fresh) fence_proxy_async();
+          }
           if (!mbar_wait(empty_bar + stage, phase ^ 1, 5 * tmo)) {
             report(a, kTimeoutEmpty, t, kb);
             ok = false;

@@ -117,6 +117,12 @@ struct GemmArgs {
   int a_flag_base, a_flag_count;
   int b_flag_mode;
   int b_flag_base, b_flag_count;
+  // flag mode 3 ("K panels", the SUMMA / ring schedules): the operand arrives in panels of the
+  // contraction dimension; k-block kb needs flag base + kb / kpanel, which counts to kp_target
+  int a_kpanel, b_kpanel;      // 64-wide k-blocks per panel
+  uint32_t kp_target;
+  int k_rot;                   // first k-block of every tile (the contraction loop wraps around), so
+                               // that a rank can start with the panel it already holds
   // ---- push side ----
   int push_n;                  // number of owners (0: local epilogue)
   int push_dim;                // 0: owners split M, 1: owners split N

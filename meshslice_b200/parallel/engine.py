@@ -81,6 +81,26 @@ class FusedEngine:
             out.copy_(y) if not accumulate else out.add_(y)
             return out
 
+    def os_kpanel(self, X, W, order: str = "summa", sub: int = 1, out: Optional[torch.Tensor] = None,
+                  accumulate=False):
+        """The OS product on the K-panel schedule of a baseline algorithm ('summa', 'wang',
+        'cannon'): panels of the contraction dimension are pushed by their owners and consumed
+        in the order of that algorithm, inside one kernel."""
+        X, W = _local(X), _local(W)
+        m, kl = X.shape
+        kr, n = W.shape
+        if out is None:
+            out = torch.empty(m, n, dtype=torch.bfloat16, device=X.device)
+        try:
+            X, W = X.contiguous(), W.contiguous()
+            xp = self._own(X, self.mesh.C, self.mesh.c)
+            wp = self._own(W, self.mesh.R, self.mesh.r)
+            return self.fg.os_kpanel(xp, wp, m, kl, kr, n, out, order=order, sub=sub, accumulate=accumulate)
+        except FusedPlanError as e:
+            y = self._fallback("os", e, X, W, sub)
+            out.copy_(y) if not accumulate else out.add_(y)
+            return out
+
     def ls(self, X, W, n_slices: int = 4, out: Optional[torch.Tensor] = None, accumulate=False):
         """Y[m, N/C] = RS_col( X[m, kl] @ AG_row(W)[N, kl]^T )."""
         X, W = _local(X), _local(W)

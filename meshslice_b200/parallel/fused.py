@@ -207,6 +207,89 @@ class FusedGemm:
         self._launch(d, exit_barrier=False, phase=phase, reset=reset)
         return out
 
+    # ------------------------------------------------------------------ OS, K-panel schedules
+    def os_kpanel(self, x_ptrs: List[int], w_ptrs: List[int], m: int, kl: int, kr: int, n: int, out,
+                  order: str = "summa", sub: int = 1, accumulate: bool = False,
+                  phase: str = "all", reset: bool = True):
+        """Y[m, n] = concat_c(X_c) @ concat_r(W_r) with the operands arriving in panels of the
+        contraction dimension, the schedule of the SUMMA / Wang / Cannon baselines on one kernel:
+
+        * ``summa``  every rank consumes the panels in the order 0, 1, 2, ...; the owner of a panel
+          broadcasts it (one read of its shard, one store per peer).
+        * ``wang``   a rank starts with the X panel it holds and walks the ring from there; a source
+          serves its peers in the order in which they will need its panel.
+        * ``cannon`` square meshes; rank (r, c) starts at panel (r + c) mod n, the skewed order of
+          Cannon's algorithm, for both operands.
+
+        ``sub`` splits every owner's panel into that many sub-panels (finer overlap).  On an NVSwitch
+        fabric a "ring step" is a direct store to the peer that needs the panel next."""
+        mc, ws = self.mesh, self.world.mine
+        Kd = mc.C * kl
+        if Kd != mc.R * kr:
+            raise FusedPlanError("K-panel OS: contraction sizes of X and W shards disagree")
+        if order not in ("summa", "wang", "cannon"):
+            raise ValueError(f"unknown K-panel order {order!r}")
+        if order == "cannon" and mc.R != mc.C:
+            raise FusedPlanError("Cannon's schedule needs a square mesh")
+        if kl % 64 or kr % 64 or n % 8 or m * Kd * 2 > ws.stage_a_bytes or Kd * n * 2 > ws.stage_b_bytes:
+            raise FusedPlanError("K-panel OS: shard does not fit the staging buffers / 64-wide k-blocks")
+        sub = max(1, sub)
+        while sub > 1 and (kl % (sub * 64) or kr % (sub * 64)):
+            sub -= 1
+        nA, nB = mc.C * sub, mc.R * sub
+        if nA + nB > rt.NCHUNK:
+            raise FusedPlanError("K-panel OS: too many panels")
+        pa, pb = kl // sub, kr // sub
+        stream = _native.stream_ptr()
+        xg, wg = ws.local(ws.stage_a), ws.local(ws.stage_b)
+        rowp, colp = mc.row_peers(), mc.col_peers()
+        x_mine, w_mine = x_ptrs[mc.c], w_ptrs[mc.r]
+        gather_w, gather_x = mc.R > 1, mc.C > 1
+
+        def start(r, c):      # first contraction index that rank (r, c) consumes
+            return {"summa": 0, "wang": c * kl, "cannon": ((r + c) % mc.C) * kl}[order]
+
+        def build():
+            recs = []         # (contraction distance at which the destinations need it, job, flags)
+            if gather_x:
+                groups = {}
+                for cc, q in enumerate(rowp):
+                    groups.setdefault((mc.c * kl - start(mc.r, cc)) % Kd, []).append(q)
+                for t, dests in groups.items():
+                    for s_ in range(sub):
+                        job = (0, s_ * pa * 2, m, pa * 2, kl * 2, Kd * 2,
+                               [self.world.ptr(q, ws.stage_a) + (mc.c * kl + s_ * pa) * 2 for q in dests])
+                        recs.append((t + s_ * pa, job, [self._chunk_flag(q, mc.c * sub + s_) for q in dests]))
+            if gather_w:
+                groups = {}
+                for rr, q in enumerate(colp):
+                    groups.setdefault((mc.r * kr - start(rr, mc.c)) % Kd, []).append(q)
+                for t, dests in groups.items():
+                    for s_ in range(sub):
+                        job = (1, s_ * pb * n * 2, pb, n * 2, n * 2, n * 2,
+                               [self.world.ptr(q, ws.stage_b) + (mc.r * kr + s_ * pb) * n * 2 for q in dests])
+                        recs.append((t + s_ * pb, job, [self._chunk_flag(q, nA + mc.r * sub + s_) for q in dests]))
+            recs.sort(key=lambda rec: rec[0])
+            jobs = [rec[1] for rec in recs]
+            chunks = [(i, i + 1, rec[2], self.grid) for i, rec in enumerate(recs)]
+            return jobs, chunks
+
+        d = self._common(out, accumulate, stream)
+        d.update(M=m, N=n, K=Kd, A=xg if gather_x else x_mine, B=wg if gather_w else w_mine, lda=Kd, ldb=n,
+                 a_mn_major=0, b_mn_major=1, slice_dim=0, n_slices=1, cyc=1, group=8,
+                 gather_src0=x_mine, gather_src1=w_mine, k_rot=start(mc.r, mc.c) // 64,
+                 kp_target=self.grid)
+        if gather_w or gather_x:
+            jt, ct, n_chunks = self._jobs(("os_kpanel", order, m, kl, kr, n, sub), build)
+            d.update(jobs=jt.data_ptr(), chunks=ct.data_ptr(), n_chunks=n_chunks,
+                     chunk_flags=ws.local(ws.flags + 4 * rt.CHUNK0))
+            if gather_x:
+                d.update(a_flag_mode=3, a_flag_base=0, a_kpanel=pa // 64)
+            if gather_w:
+                d.update(b_flag_mode=3, b_flag_base=nA, b_kpanel=pb // 64)
+        self._launch(d, exit_barrier=False, phase=phase, reset=reset)
+        return out
+
     # ------------------------------------------------------------------ LS
     def ls(self, x, w_ptrs: List[int], m: int, kl: int, nr: int, out, n_slices: int = 4,
            accumulate: bool = False, phase: str = "all", reset: bool = True):

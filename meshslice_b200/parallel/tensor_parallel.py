@@ -368,6 +368,15 @@ class SPMD:
 
     def _build(self, which: str, K: int) -> Callable:
         eng = self._fused()
+        ring_eng = getattr(self.mesh, "engine", None)
+        if (eng is None and self.backend != "collective" and which == "os" and hasattr(ring_eng, "os_kpanel")
+                and self.algorithm in ("summa", "wang", "cannon")):
+            # the OS product of the baseline algorithms on the fused kernel's K-panel schedule
+            mesh, order = self.mesh, self.algorithm
+            def run_panels(X, W, **kw):
+                y = ring_eng.os_kpanel(X, W, order=order, sub=max(1, K), **kw)
+                return ShardedTensor(mesh, {mesh.coords()[0]: y}) if isinstance(X, ShardedTensor) else y
+            return run_panels
         if eng is not None:
             fn, mesh = getattr(eng, which), self.mesh
             def run(X, W, **kw):

@@ -154,3 +154,46 @@ def test_shapes_that_break_the_tile_rules_are_rejected():
     with pytest.raises(fz.FusedPlanError):
         _capture(2, 2, lambda fg, mc: fg.rs([1] * 2, FakeT(6, 100), 64, 256, 100, None))
     assert fz.pick_slices(8, 4) == 4 and fz.pick_slices(6, 4) == 3 and fz.pick_slices(4, 4, 2) == 2
+
+
+@pytest.mark.parametrize("mesh,order,sub", [((2, 4), "summa", 2), ((2, 4), "wang", 1), ((4, 2), "wang", 2),
+                                            ((2, 2), "cannon", 2), ((1, 4), "summa", 1), ((4, 1), "wang", 1)])
+def test_k_panel_plans(mesh, order, sub):
+    """SUMMA / Wang / Cannon schedules of the OS product: every panel reaches every consumer once,
+    every panel flag is bumped by exactly one source, and a consumer's first panel is the first
+    thing its source sends."""
+    R, C = mesh
+    m, Kd, n = 512, 2048, 512
+    kl, kr = Kd // C, Kd // R
+    caps = _capture(R, C, lambda fg, mc: fg.os_kpanel([10 ** 9] * C, [2 * 10 ** 9] * R, m, kl, kr, n, None,
+                                                       order=order, sub=sub))
+    flag_hits = {}
+    for rank, cap in caps.items():
+        d = cap["d"]
+        base = (rank + 1) << 40
+        if C > 1:
+            assert (_coverage(caps, rank, 1 << 20, m * Kd * 2, base) == 1).all()
+            assert d["a_flag_mode"] == 3 and d["a_kpanel"] * 64 * sub == kl
+        if R > 1:
+            assert (_coverage(caps, rank, 1 << 34, Kd * n * 2, base) == 1).all()
+            assert d["b_flag_mode"] == 3 and d["b_kpanel"] * 64 * sub == kr and d["b_flag_base"] == C * sub
+        r, c = divmod(rank, C)
+        start = {"summa": 0, "wang": c * kl, "cannon": ((r + c) % C) * kl}[order]
+        assert d["k_rot"] == start // 64 and d["kp_target"] == 148
+        if "plan" in cap:
+            jobs, chunks = cap["plan"]
+            assert len(jobs) == len(chunks) and all(ch[1] - ch[0] == 1 and ch[3] == 148 for ch in chunks)
+            for ch in chunks:
+                for f in ch[2]:
+                    flag_hits[f] = flag_hits.get(f, 0) + 1
+    # one source per (destination, panel) flag; C*sub X panels and R*sub W panels per destination
+    assert all(v == 1 for v in flag_hits.values())
+    per_dest = (C * sub if C > 1 else 0) + (R * sub if R > 1 else 0)
+    assert len(flag_hits) == per_dest * R * C
+    if order == "wang" and C > 1:
+        # the first X chunk a source emits is the one its own consumer starts with (its own panel)
+        for rank, cap in caps.items():
+            jobs, chunks = cap["plan"]
+            first_x = next(i for i, j in enumerate(jobs) if j[0] == 0)
+            own_flag = ((rank + 1) << 40) + 4 * (rt.CHUNK0 + (rank % C) * sub)
+            assert chunks[first_x][2] == [own_flag]

@@ -58,6 +58,33 @@ def test_os_pull_both_operands(mesh, slices):
         _close(out, ref[r * m:(r + 1) * m, c * n:(c + 1) * n], Kd)
 
 
+@pytest.mark.parametrize("mesh,order,sub", [((2, 4), "summa", 2), ((2, 4), "wang", 1), ((2, 2), "cannon", 2),
+                                            ((4, 2), "wang", 2), ((1, 2), "summa", 1)])
+def test_os_k_panel_schedules(mesh, order, sub):
+    """SUMMA / Wang / Cannon schedules: panels of the contraction dimension, consumed in the
+    algorithm's order (rotated start of the contraction loop), give the dense product."""
+    from meshslice_b200 import _native
+    R, C = mesh
+    M, Kd, N = 512 * R, 1024, 256 * C
+    X = torch.randn(M, Kd, device="cuda").bfloat16()
+    W = torch.randn(Kd, N, device="cuda").bfloat16()
+    m, kl, kr, n = M // R, Kd // C, Kd // R, N // C
+    xs = {(r, c): X[r * m:(r + 1) * m, c * kl:(c + 1) * kl].contiguous() for r in range(R) for c in range(C)}
+    wsd = {(r, c): W[r * kr:(r + 1) * kr, c * n:(c + 1) * n].contiguous() for r in range(R) for c in range(C)}
+    ops, _ = _setup(R, C, m * Kd * 2, Kd * n * 2, 16)
+    ref = X.float() @ W.float()
+    outs = {k: torch.empty(m, n, device="cuda", dtype=torch.bfloat16) for k in ops}
+    for op in ops.values():
+        op._reset_flags(_native.stream_ptr())
+    for phase in ("comm", "gemm"):
+        for (r, c), op in ops.items():
+            op.os_kpanel([xs[(r, cc)].data_ptr() for cc in range(C)], [wsd[(rr, c)].data_ptr() for rr in range(R)],
+                         m, kl, kr, n, outs[(r, c)], order=order, sub=sub, phase=phase, reset=False)
+            _native.check_status()
+    for (r, c), out in outs.items():
+        _close(out, ref[r * m:(r + 1) * m, c * n:(c + 1) * n], Kd)
+
+
 @pytest.mark.parametrize("mesh,slices", [((2, 2), 2), ((2, 4), 1)])
 def test_ls_pull_weights_push_over_row(mesh, slices):
     from meshslice_b200 import _native
