@@ -1,5 +1,5 @@
 """Worker of the multi-GPU fused-kernel test: run under torchrun, one rank per GPU.
-Compares the fused OS / LS / RS kernels with the dense fp32 product of the global operands."""
+Compares the fused OS / LS / RS kernels (and the SUMMA / Wang / Cannon schedules of OS) with the dense fp32 product of the global operands."""
 import os
 import sys
 
@@ -44,6 +44,13 @@ def main():
                    W[r * kr:(r + 1) * kr, c * n:(c + 1) * n].contiguous(), n_slices=slices)
         eng.check()
         close("os", y, (X.float() @ W.float())[r * m:(r + 1) * m, c * n:(c + 1) * n], Kd)
+        # the same product on the K-panel schedules of the baseline algorithms
+        xl = X[r * m:(r + 1) * m, c * kl:(c + 1) * kl].contiguous()
+        wl = W[r * kr:(r + 1) * kr, c * n:(c + 1) * n].contiguous()
+        for order in ("summa", "wang") + (("cannon",) if R == C else ()):
+            y = eng.os_kpanel(xl, wl, order=order, sub=2)
+            eng.check()
+            close("os_" + order, y, (X.float() @ W.float())[r * m:(r + 1) * m, c * n:(c + 1) * n], Kd)
         # LS
         M, Kd, N = 256 * R, 256 * C, 512 * R * C
         X = torch.randn(M, Kd, generator=g).bfloat16().to(dev)
