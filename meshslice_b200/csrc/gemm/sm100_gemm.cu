@@ -32,7 +32,8 @@ constexpr uint32_t kSmemB = kSmemA + kStages * kAStageBytes;
 constexpr uint32_t kSmemComm = kSmemB + kStages * kBStageBytes;
 constexpr uint32_t kSmemEpi = kSmemComm + kCommBufs * kCommBufBytes;
 constexpr uint32_t kSmemBar = kSmemEpi + 4 * kEpiStageBytes;
-constexpr uint32_t kSmemTotal = kSmemBar + 256;
+constexpr uint32_t kSmemCnt = kSmemBar + 256;   // [4 epilogue warps][kMaxPeers] tile counts
+constexpr uint32_t kSmemTotal = kSmemCnt + 4 * kMaxPeers * 4;
 constexpr uint32_t kSmemAlloc = kSmemTotal + 1024;  // slack for manual 1024-byte alignment
 constexpr uint32_t kTmemCols = 512;
 constexpr int kEpiThreads = 128;
@@ -420,6 +421,7 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
   uint8_t* sComm = smem + kSmemComm;
   uint8_t* sEpi = smem + kSmemEpi;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kSmemBar);
+  uint32_t* sCnt = reinterpret_cast<uint32_t*>(smem + kSmemCnt);
   uint64_t* full_bar = bars;                   // [kStages]
   uint64_t* empty_bar = bars + kStages;        // [kStages]
   uint64_t* tfull_bar = bars + 2 * kStages;    // [2]
@@ -587,9 +589,30 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
     const __nv_bfloat16* bias = reinterpret_cast<const __nv_bfloat16*>(a.bias);
     bool ok = true;
     int it = 0;
-    bool pend_valid = false;   // push path: a tile whose arrival has not been counted yet
-    int pend_owner = 0, pend_slice = 0;
     int push_seq = 0;          // staging buffer of the next band (deep push: three per warp)
+    // Push path: arrivals are counted at the owners once per slice, not per tile.  Ordering a tile's
+    // stores before its counter costs an NVLink round trip (system-scope fence), so this warp sums
+    // its tiles per owner in shared memory and pays that round trip when the slice changes.
+    uint32_t* cnt = sCnt + (warp - 2) * kMaxPeers;
+    int cur_slice = -1;
+    if (lane < kMaxPeers) cnt[lane] = 0;
+    __syncwarp();
+    auto flush_counts = [&](int slice) {
+      if (a.push_mode == 0 && lane == 0) {
+        bulk_wait_all<0>();     // this warp's tensor stores have completed
+        fence_proxy_async();
+      }
+      __threadfence_system();
+      __syncwarp();
+      if (lane < a.push_n) {
+        const uint32_t c = cnt[lane];
+        if (c != 0) {
+          red_add_release_sys(a.push_counter[lane] + slice, c);
+          cnt[lane] = 0;
+        }
+      }
+      __syncwarp();
+    };
     for (int t = cluster_id; t < num_tiles && ok; t += n_clusters, ++it) {
       const TileCoord tc = tile_coord(t, a);
       const uint32_t acc = it & 1, acc_phase = (it >> 1) & 1;
@@ -607,13 +630,9 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
       }
       mbar_wait(tfull_bar + acc, acc_phase, tmo);  // already complete: orders this lane's reads
       tc_fence_after_sync();
-      if (a.push_mode == 1 && pend_valid) {
-        // Direct-store push: count the PREVIOUS tile at its owner.  Its stores were issued a whole
-        // tile ago, so the fence that orders them before the counter finds them already performed.
-        __threadfence_system();
-        __syncwarp();
-        if (lane == 0) red_add_release_sys(a.push_counter[pend_owner] + pend_slice, 1u);
-        pend_valid = false;
+      if (a.push_n > 0 && tc.slice != cur_slice) {
+        if (cur_slice >= 0) flush_counts(cur_slice);
+        cur_slice = tc.slice;
       }
       const int64_t row = (int64_t)m_blk * kBM + q * 32 + lane;
       const bool row_ok = row < a.M;
@@ -703,17 +722,7 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
             bulk_commit();
           }
         }
-        // Count the PREVIOUS tile at its owner now: its row stores are the groups older than the
-        // four just committed, so waiting for them costs no NVLink round trip on this tile.
-        if (a.push_mode == 0 && pend_valid && lane == 0) {
-          bulk_wait_all<kBN / 64>();
-          fence_proxy_async();
-          __threadfence_system();
-          red_add_release_sys(a.push_counter[pend_owner] + pend_slice, 1u);
-        }
-        pend_valid = true;
-        pend_owner = owner;
-        pend_slice = tc.slice;
+        if (lane == 0) cnt[owner] += 1;
       } else {
 #pragma unroll 1
         for (int c = 0; c < kBN / 32; ++c) {
@@ -747,19 +756,7 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
         }
       }
     }
-    if (a.push_mode == 1 && pend_valid) {
-      __threadfence_system();
-      __syncwarp();
-      if (lane == 0) red_add_release_sys(a.push_counter[pend_owner] + pend_slice, 1u);
-      pend_valid = false;
-    }
-    if (pend_valid && lane == 0) {
-      // last tile of this CTA: all of this warp's tensor stores must have completed
-      bulk_wait_all<0>();
-      fence_proxy_async();
-      __threadfence_system();
-      red_add_release_sys(a.push_counter[pend_owner] + pend_slice, 1u);
-    }
+    if (cur_slice >= 0) flush_counts(cur_slice);
   } else {
     // ===================== communication warp =====================
     comm_warp_main(a, sComm, comm_bar);
