@@ -100,7 +100,7 @@ void gemm_run(const py::dict& d) {
   a.rot = (int)geti(d, "rot", 0);
   if (a.rot < 0 || a.rot >= tiles_s / a.n_slices) a.rot = 0;
   if (geti(d, "no_tiles")) a.tiles_m = 0;  // reduce phase only
-  // pull side
+  // gather side
   a.jobs = P<const PushJob>(getp(d, "jobs"));
   a.chunks = P<const ChunkDesc>(getp(d, "chunks"));
   a.skip_comm = (int)geti(d, "skip_comm");
@@ -262,7 +262,7 @@ PYBIND11_MODULE(_C, m) {
   m.attr("PUSH_JOB_BYTES") = (int)sizeof(PushJob);
   m.attr("CHUNK_DESC_BYTES") = (int)sizeof(ChunkDesc);
 
-  m.def("gemm_run", &gemm_run, "persistent tcgen05 GEMM with optional fused pull / push");
+  m.def("gemm_run", &gemm_run, "persistent tcgen05 GEMM with optional fused gather / push");
   m.def("symm_alloc", &symm_alloc);
   m.def("symm_open", &symm_open);
   m.def("symm_close", &symm_close);

@@ -1,15 +1,20 @@
 // Persistent, warp-specialised tcgen05 GEMM for sm_100a with fused mesh collectives.
 // See sm100_gemm.h for the interface and the role of each argument.
 //
-// CTA layout (224 threads, one CTA per SM, static round-robin tile schedule):
-//   warp 0      TMA producer: waits for the chunk flags a tile depends on, then fills a
-//               4-stage ring of (A 128x64, B 256x64) bf16 tiles in 128-byte-swizzled smem
-//   warp 1      MMA issuer: one elected thread issues tcgen05.mma (M=128, N=256, K=16) into
-//               one of two 256-column fp32 accumulators in TMEM
-//   warps 2..5  epilogue: tcgen05.ld the finished accumulator (one TMEM lane quarter per
-//               warp), apply bias/GeLU, store to local memory or to the owner GPU's slot
-//   warp 6      communication: cross-GPU entry/exit barrier (CTA 0) and the pull side's
-//               bulk copies peer -> smem -> local staging, one flag per chunk
+// CTA pairs (clusters of two, 224 threads per CTA, one CTA per SM, static round-robin schedule of
+// 256x256 cluster tiles; each CTA holds 128 rows of A and 128 columns of B of the pair's tile):
+//   warp 0      TMA producer (both CTAs): waits for the chunk / panel flags a tile depends on, then
+//               fills a six-stage ring of (A 128x64, B 128x64) bf16 tiles in 128-byte-swizzled smem;
+//               the loads complete on the leader CTA's mbarrier
+//   warp 1      MMA issuer (leader CTA): one elected thread issues tcgen05.mma.cta_group::2
+//               (M=256, N=256, K=16) into one of two 256-column fp32 accumulators in TMEM
+//   warps 2..5  epilogue: tcgen05.ld the finished accumulator (one TMEM lane quarter per warp), then
+//               either bias / GeLU and a store to local memory, or the push of the bf16 partial tile
+//               into the owner GPU's slot (staged in smem, written with coalesced 16-byte stores or
+//               2-D TMA tensor stores) with one arrival count per slice and owner
+//   warp 6      communication: cross-GPU entry / exit barrier (CTA 0) and the gather side: pieces of
+//               the LOCAL shard go through smem to every GPU of the group (posted bulk stores), one
+//               flag per chunk on every destination
 // After its tiles every CTA joins the reduce phase, which sums the partial tiles that peers
 // pushed into this GPU's slots.
 //

@@ -148,9 +148,9 @@ struct GemmArgs {
   uint32_t* entry_flags[kMaxPeers];  // rank r's entry flag array (index: source rank)
   uint32_t* exit_flags[kMaxPeers];   // rank r's exit flag array
   uint32_t epoch;              // value for this launch (monotonic per workspace)
-  int exit_barrier;            // 1: wait for all peers to finish pulling before leaving
+  int exit_barrier;            // 1: wait for all peers to finish their transfers before leaving
   uint32_t* go_flag;           // local: set to epoch by CTA 0 once all peers have arrived
-  uint32_t* done_counter;      // local: CTAs that finished pulling (monotonic)
+  uint32_t* done_counter;      // local: CTAs that finished their transfers (monotonic)
   uint32_t done_target;
   // ---- status ----
   uint32_t* status;            // [4]: code, blockIdx, detail, detail2

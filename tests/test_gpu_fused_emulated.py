@@ -1,4 +1,4 @@
-"""Fused pull / push paths of the GEMM kernel on ONE GPU.
+"""Fused gather / push paths of the GEMM kernel on ONE GPU.
 
 Several mesh ranks are emulated one after another: every emulated rank has its own heap and
 workspace on the same device, "peer" pointers point into the other emulated ranks' buffers, and
@@ -35,7 +35,7 @@ def _close(out, ref, K):
 
 
 @pytest.mark.parametrize("mesh,slices", [((2, 2), 2), ((1, 4), 1), ((4, 2), 4)])
-def test_os_pull_both_operands(mesh, slices):
+def test_os_gathers_both_operands(mesh, slices):
     from meshslice_b200 import _native
     R, C = mesh
     M, Kd, N = 512 * R, 1024, 256 * C
@@ -86,7 +86,7 @@ def test_os_k_panel_schedules(mesh, order, sub):
 
 
 @pytest.mark.parametrize("mesh,slices", [((2, 2), 2), ((2, 4), 1)])
-def test_ls_pull_weights_push_over_row(mesh, slices):
+def test_ls_gathers_weights_pushes_over_row(mesh, slices):
     from meshslice_b200 import _native
     R, C = mesh
     M, Kd, N = 256 * R, 128 * C, 512 * R * C
@@ -110,7 +110,7 @@ def test_ls_pull_weights_push_over_row(mesh, slices):
 
 
 @pytest.mark.parametrize("mesh,slices,cyc", [((2, 2), 2, 1), ((2, 2), 1, 2), ((4, 2), 2, 2)])
-def test_rs_pull_inputs_push_over_column(mesh, slices, cyc):
+def test_rs_gathers_inputs_pushes_over_column(mesh, slices, cyc):
     from meshslice_b200 import _native
     R, C = mesh
     Kd, M, N = 192 * R, 512 * R * C, 256 * C
