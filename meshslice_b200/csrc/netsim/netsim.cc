@@ -198,6 +198,14 @@ Nic::Nic(Simulator& sim, Network& net, int node, NicParams p)
 void Nic::submit(std::function<void()> cmd) {
   // the host writes a 64-byte command over MMIO; the NIC dequeues one command per clock
   ++stats_.commands;
+  if (finished_) {
+    last_error = "node " + std::to_string(node_) + ": command after fini";
+    return;
+  }
+  if (direct_) {   // the command ring in front of this NIC already accounted for the MMIO write
+    cmd();
+    return;
+  }
   const Time arrive = std::max(sim_.now() + p_.host_cmd_latency, cmd_free_);
   cmd_free_ = arrive + p_.clock;
   sim_.at(arrive, std::move(cmd));
@@ -213,45 +221,75 @@ int Nic::create_rq(uint32_t key, int cq) {
   return (int)rqs_.size() - 1;
 }
 
-void Nic::recv_post(Buffer buf, uint32_t len, int rq, uint64_t context) {
-  submit([=]() { rqs_[rq].posted.push_back(PostedRecv{buf, len, context}); });
+bool Nic::destroy_cq(int cq) {
+  if (cq < 0 || cq >= (int)cqs_.size() || !cqs_[cq].alive) return false;
+  for (auto& q : rqs_)
+    if (q.alive && q.cq == cq) return false;
+  cqs_[cq].alive = false;
+  cqs_[cq].entries.clear();
+  cqs_[cq].waiters.clear();
+  return true;
 }
 
-void Nic::send_post(Buffer buf, uint32_t len, int dst, uint32_t rq_key, int cq, uint64_t context) {
-  submit([=]() {
+bool Nic::destroy_rq(int rq) {
+  if (rq < 0 || rq >= (int)rqs_.size() || !rqs_[rq].alive) return false;
+  rqs_[rq].alive = false;
+  rqs_[rq].posted.clear();
+  return true;
+}
+
+void Nic::fini() {
+  submit([this]() { finished_ = true; });
+}
+
+void Nic::recv_post(Buffer buf, uint32_t len, int rq, uint64_t context, uint64_t buf_off) {
+  submit([=, this]() {
+    if (rq < 0 || rq >= (int)rqs_.size() || !rqs_[rq].alive) {
+      last_error = "node " + std::to_string(node_) + ": receive posted to an unknown queue";
+      return;
+    }
+    rqs_[rq].posted.push_back(PostedRecv{buf, len, context, buf_off});
+  });
+}
+
+void Nic::send_post(Buffer buf, uint32_t len, int dst, uint32_t rq_key, int cq, uint64_t context,
+                    uint64_t buf_off) {
+  submit([=, this]() {
     SendEntry e;
     e.hdr.type = StreamType::Msg;
     e.hdr.length = len;
     e.hdr.key = rq_key;
-    e.dst = dst; e.vc = 0; e.cq = cq; e.context = context; e.src = buf; e.payload_len = len;
+    e.dst = dst; e.vc = 0; e.cq = cq; e.context = context; e.src = buf; e.src_off = buf_off; e.payload_len = len;
     start_send(std::move(e));
   });
 }
 
-void Nic::memory_reg(uint32_t key, Buffer buf) {
-  submit([=]() { regions_[key] = buf; });
+void Nic::memory_reg(uint32_t key, Buffer buf, uint64_t buf_off, uint64_t len) {
+  submit([=, this]() { regions_[key] = Region{buf, buf_off, len}; });
 }
 
 void Nic::memory_unreg(uint32_t key) {
-  submit([=]() { regions_.erase(key); });
+  submit([=, this]() { regions_.erase(key); });
 }
 
-void Nic::memory_write(uint32_t key, int dst, uint64_t offset, Buffer data, uint32_t len, int cq, uint64_t context) {
-  submit([=]() {
+void Nic::memory_write(uint32_t key, int dst, uint64_t offset, Buffer data, uint32_t len, int cq, uint64_t context,
+                       uint64_t data_off) {
+  submit([=, this]() {
     SendEntry e;
     e.hdr.type = StreamType::Write;
     e.hdr.length = len;
     e.hdr.key = key;
     e.hdr.offset = offset;
-    e.dst = dst; e.vc = 0; e.cq = cq; e.context = context; e.src = data; e.payload_len = len;
+    e.dst = dst; e.vc = 0; e.cq = cq; e.context = context; e.src = data; e.src_off = data_off; e.payload_len = len;
     start_send(std::move(e));
   });
 }
 
-void Nic::memory_read(uint32_t key, int dst, uint64_t offset, Buffer into, uint32_t len, int cq, uint64_t context) {
-  submit([=]() {
+void Nic::memory_read(uint32_t key, int dst, uint64_t offset, Buffer into, uint32_t len, int cq, uint64_t context,
+                      uint64_t into_off) {
+  submit([=, this]() {
     const uint32_t rk = next_resp_key_++;
-    reads_[rk] = PendingRead{into, cq, context};
+    reads_[rk] = PendingRead{into, cq, context, into_off};
     SendEntry e;
     e.hdr.type = StreamType::ReadReq;
     e.hdr.length = 0;
@@ -282,7 +320,12 @@ void Nic::complete(int cq, Completion c) {
   memq_.fence(2);
   memq_.request(0, 16, true, [this, cq, c]() mutable {
     c.time = sim_.now();
+    if (cq_sink_) {   // the entry lands in a completion ring in host memory
+      cq_sink_(cq, c);
+      return;
+    }
     CompQueue& q = cqs_[cq];
+    if (!q.alive) return;
     if (!q.waiters.empty()) {
       auto fn = std::move(q.waiters.front());
       q.waiters.pop_front();
@@ -408,7 +451,7 @@ void Nic::on_stream_first(const Packet& p) {
   switch (p.hdr.type) {
     case StreamType::Msg: {
       RecvQueue* rq = nullptr;
-      for (auto& q : rqs_) if (q.key == p.hdr.key) rq = &q;
+      for (auto& q : rqs_) if (q.alive && q.key == p.hdr.key) rq = &q;
       if (rq == nullptr || rq->posted.empty() || rq->posted.front().len < p.hdr.length) {
         last_error = "node " + std::to_string(node_) + ": no matching receive for key " + std::to_string(p.hdr.key);
         return;
@@ -416,6 +459,7 @@ void Nic::on_stream_first(const Packet& p) {
       PostedRecv pr = rq->posted.front();
       rq->posted.pop_front();
       rs.dst = pr.buf;
+      rs.dst_off = pr.off;
       rs.cq = rq->cq;
       rs.context = pr.context;
       break;
@@ -426,8 +470,12 @@ void Nic::on_stream_first(const Packet& p) {
         last_error = "node " + std::to_string(node_) + ": write to unregistered region " + std::to_string(p.hdr.key);
         return;
       }
-      rs.dst = it->second;
-      rs.dst_off = p.hdr.offset;
+      if (p.hdr.offset + p.hdr.length > it->second.len) {
+        last_error = "node " + std::to_string(node_) + ": write beyond region " + std::to_string(p.hdr.key);
+        return;
+      }
+      rs.dst = it->second.buf;
+      rs.dst_off = it->second.off + p.hdr.offset;
       rs.complete_notify = false;
       break;
     }
@@ -442,8 +490,12 @@ void Nic::on_stream_first(const Packet& p) {
       e.hdr.length = p.hdr.read_len;
       e.hdr.key = p.hdr.resp_key;
       e.dst = p.src; e.vc = 1; e.cq = -1; e.context = 0;
-      e.src = it->second;
-      e.src_off = p.hdr.offset;
+      if (p.hdr.offset + p.hdr.read_len > it->second.len) {
+        last_error = "node " + std::to_string(node_) + ": read beyond region " + std::to_string(p.hdr.key);
+        return;
+      }
+      e.src = it->second.buf;
+      e.src_off = it->second.off + p.hdr.offset;
       e.payload_len = p.hdr.read_len;
       start_send(std::move(e));
       rs.complete_notify = false;
@@ -456,6 +508,7 @@ void Nic::on_stream_first(const Packet& p) {
         return;
       }
       rs.dst = it->second.into;
+      rs.dst_off = it->second.off;
       rs.cq = it->second.cq;
       rs.context = it->second.context;
       reads_.erase(it);

@@ -96,14 +96,28 @@ class Nic {
   // ---- host API (the reference's librdma, tests/app/rdma/include/rdma.h:30-69) ----
   int node() const { return node_; }
   int num_nodes() const { return net_.nodes(); }
+  // Buffers are whole allocations; the trailing `*_off` arguments select where inside the
+  // allocation the transfer starts (a host program passes addresses, see host.h).
   int create_cq();
   int create_rq(uint32_t key, int cq);
-  void recv_post(Buffer buf, uint32_t len, int rq, uint64_t context);
-  void send_post(Buffer buf, uint32_t len, int dst, uint32_t rq_key, int cq, uint64_t context);
-  void memory_reg(uint32_t key, Buffer buf);
+  bool destroy_cq(int cq);      // false: unknown id or still referenced by a receive queue
+  bool destroy_rq(int rq);
+  void fini();                  // later commands are refused (last_error is set)
+  void recv_post(Buffer buf, uint32_t len, int rq, uint64_t context, uint64_t buf_off = 0);
+  void send_post(Buffer buf, uint32_t len, int dst, uint32_t rq_key, int cq, uint64_t context,
+                 uint64_t buf_off = 0);
+  void memory_reg(uint32_t key, Buffer buf, uint64_t buf_off = 0, uint64_t len = ~0ull);
   void memory_unreg(uint32_t key);
-  void memory_write(uint32_t key, int dst, uint64_t offset, Buffer data, uint32_t len, int cq, uint64_t context);
-  void memory_read(uint32_t key, int dst, uint64_t offset, Buffer into, uint32_t len, int cq, uint64_t context);
+  void memory_write(uint32_t key, int dst, uint64_t offset, Buffer data, uint32_t len, int cq, uint64_t context,
+                    uint64_t data_off = 0);
+  void memory_read(uint32_t key, int dst, uint64_t offset, Buffer into, uint32_t len, int cq, uint64_t context,
+                   uint64_t into_off = 0);
+  // A front end that models the MMIO command ring itself (host.h) switches the built-in
+  // command latency off and receives completion entries instead of the internal queues.
+  void set_direct(bool on) { direct_ = on; }
+  void set_cq_sink(std::function<void(int cq, const Completion&)> fn) { cq_sink_ = std::move(fn); }
+  Simulator& sim() { return sim_; }
+  const NicParams& params() const { return p_; }
   // Calls `fn` (once) as soon as the CQ has an entry; entries are delivered in completion order.
   void on_completion(int cq, std::function<void(const Completion&)> fn);
   void barrier(std::function<void()> done);
@@ -136,15 +150,22 @@ class Nic {
     Buffer buf;
     uint32_t len;
     uint64_t context;
+    uint64_t off = 0;
   };
   struct RecvQueue {
     uint32_t key;
     int cq;
     std::deque<PostedRecv> posted;
+    bool alive = true;
+  };
+  struct Region {
+    Buffer buf;
+    uint64_t off = 0, len = ~0ull;
   };
   struct CompQueue {
     std::deque<Completion> entries;
     std::deque<std::function<void(const Completion&)>> waiters;
+    bool alive = true;
   };
 
   void submit(std::function<void()> cmd);   // host -> command queue -> NIC
@@ -186,12 +207,15 @@ class Nic {
   std::unordered_map<uint64_t, RecvStream> recv_;  // key: (src << 32) | stream id
   std::vector<RecvQueue> rqs_;
   std::vector<CompQueue> cqs_;
-  std::map<uint32_t, Buffer> regions_;
+  std::map<uint32_t, Region> regions_;
   struct PendingRead {
     Buffer into;
     int cq;
     uint64_t context;
+    uint64_t off = 0;
   };
+  bool direct_ = false, finished_ = false;
+  std::function<void(int, const Completion&)> cq_sink_;
   std::map<uint32_t, PendingRead> reads_;
   // barrier state
   int bar_children_in_ = 0;

@@ -243,6 +243,7 @@ ScenarioResult allgather(const ScenarioConfig& c, bool ring) {
 
 ScenarioResult run_scenario(const ScenarioConfig& c) {
   if (c.nodes < 2) throw std::invalid_argument("scenarios need at least two nodes");
+  if (is_program(c.scenario)) return run_program(c);
   if (c.scenario == "msg") return msg(c);
   if (c.scenario == "write") return write_read(c);
   if (c.scenario == "incast") return incast(c);

@@ -5,9 +5,16 @@
 #include <map>
 #include <string>
 
-#include "nic.h"
+#include "mpi.h"
 
 namespace netsim {
+
+// Host memory as the NIC's DMA engine sees it: one latency and either a flat bandwidth ('simple')
+// or channels x per-channel bandwidth ('hbm', the reference's hbmmemory.py / hbmsystem.ini variant).
+struct MemoryParams {
+  std::string kind = "simple";
+  double gbs = 100, channels = 8, channel_gbs = 32, latency_ns = 80;
+};
 
 struct ScenarioConfig {
   std::string scenario = "msg";
@@ -17,6 +24,9 @@ struct ScenarioConfig {
   int repeat = 1;
   NetParams net;
   NicParams nic;
+  MemoryParams memory;
+  HostParams host;
+  MpiParams mpi;
 };
 
 struct ScenarioResult {
@@ -26,8 +36,15 @@ struct ScenarioResult {
   uint64_t packets = 0;       // packets that crossed the network
   uint64_t events = 0;
   std::map<std::string, double> values;  // scenario-specific numbers (bandwidth, message counts ...)
+  std::vector<std::string> lines;        // what the host programs printed
 };
 
 ScenarioResult run_scenario(const ScenarioConfig& cfg);
+
+// Host programs written against the RDMA library / the message-passing layer (apps.cc):
+// rdma-hello, rdma-msg, rdma-write, rdma-incast, rdma-incast-v2, rdma-barrier, rdma-sendrecv,
+// rdma-test, imb.  run_scenario dispatches to them by name.
+bool is_program(const std::string& scenario);
+ScenarioResult run_program(const ScenarioConfig& cfg);
 
 }  // namespace netsim

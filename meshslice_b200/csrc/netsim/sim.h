@@ -2,7 +2,7 @@
 //
 // It replaces the reference's network_simulator/ directory (an SST "rdmaNic" element that only
 // builds inside an SST-elements tree with Vanadis RISC-V cores and the merlin router model) by a
-// self-contained C++17 tool for offline analysis: the parts of the NIC that the reference owns
+// self-contained C++20 tool for offline analysis: the parts of the NIC that the reference owns
 // (command queue, send / receive engines, memory request queue, network queues, tree barrier;
 // rdmaNic.h:44-420) are modelled here, and what SST provided around them (cores, memory
 // hierarchy, routers) is reduced to parametric latency / bandwidth models.  It is never on the

@@ -15,15 +15,16 @@ pytestmark = pytest.mark.skipif(shutil.which("g++") is None, reason="no C++ comp
 @pytest.fixture(scope="module")
 def build(tmp_path_factory):
     out = tmp_path_factory.mktemp("netsim")
-    srcs = [os.path.join(SRC, f) for f in ("netsim.cc", "scenarios.cc")]
-    subprocess.run(["g++", "-std=c++17", "-O1", "-g", "-fsanitize=address,undefined", "-Wall", "-Werror", "-o",
-                    str(out / "netsim_test"), *srcs, os.path.join(SRC, "test.cc")], check=True)
-    subprocess.run(["g++", "-std=c++17", "-O2", "-o", str(out / "netsim"), *srcs, os.path.join(SRC, "main.cc")], check=True)
+    srcs = [os.path.join(SRC, f) for f in ("netsim.cc", "scenarios.cc", "host.cc", "mpi.cc", "apps.cc", "config.cc")]
+    subprocess.run(["g++", "-std=c++20", "-O1", "-g", "-fsanitize=address,undefined", "-Wall", "-Werror", "-Wno-psabi",
+                    "-o", str(out / "netsim_test"), *srcs, os.path.join(SRC, "test.cc")], check=True)
+    subprocess.run(["g++", "-std=c++20", "-O2", "-Wno-psabi", "-o", str(out / "netsim"), *srcs,
+                    os.path.join(SRC, "main.cc")], check=True)
     return out
 
 
 def test_cpp_unit_tests_pass_under_sanitizers(build):
-    r = subprocess.run([str(build / "netsim_test")], capture_output=True, text=True)
+    r = subprocess.run([str(build / "netsim_test")], capture_output=True, text=True, cwd=str(build))
     assert r.returncode == 0, r.stdout + r.stderr
     assert "netsim tests passed" in r.stdout
 
@@ -57,3 +58,36 @@ def test_bad_arguments_are_rejected(build):
     assert r.returncode == 2
     r = subprocess.run([str(build / "netsim"), "--topology", "torus:3x3", "--nodes", "8"], capture_output=True, text=True)
     assert r.returncode == 2
+
+
+def test_recorded_outputs_match(build):
+    """Deterministic regression runs against the recorded *.gold outputs (host programs on the RDMA
+    library, the message-passing benchmark, the three shipped system descriptions)."""
+    r = subprocess.run(["sh", os.path.join(SRC, "run_gold.sh"), str(build / "netsim")], capture_output=True, text=True)
+    assert r.returncode == 0, r.stdout + r.stderr
+    assert "netsim gold runs match" in r.stdout
+
+
+def test_host_programs_and_message_passing(build):
+    cfg = os.path.join(SRC, "configs", "sst_torus.ini")
+    for prog in ("rdma-hello", "rdma-msg", "rdma-write", "rdma-incast", "rdma-incast-v2", "rdma-barrier",
+                 "rdma-sendrecv", "rdma-test"):
+        out = _run(build, "--config", cfg, "--scenario", prog, "--nodes", "4", "--bytes", "2000")
+        assert out["ok"] and out["lines"], prog
+    imb = _run(build, "--config", cfg, "--scenario", "imb", "--nodes", "2", "--bytes", "1", "--repeat", "10")
+    # the host costs of this description were fitted to the reference's recorded 1-byte PingPong (7.23 us)
+    assert 6.0 < imb["PingPong_1_us"] < 9.0
+    big = _run(build, "--config", cfg, "--scenario", "imb", "--nodes", "4", "--bytes", "32768", "--repeat", "2")
+    assert big["rendezvous_sent"] > 0 and big["PingPong_32768_us"] > big["PingPong_4096_us"] > big["PingPong_1_us"]
+
+
+def test_config_errors_name_file_and_line(build, tmp_path):
+    bad = tmp_path / "bad.ini"
+    bad.write_text("[network]\nlink_gbs = 32\nlink_gbz = 1\n")
+    r = subprocess.run([str(build / "netsim"), "--config", str(bad)], capture_output=True, text=True)
+    assert r.returncode == 2 and "bad.ini:3" in r.stderr and "unknown key" in r.stderr
+    r = subprocess.run([str(build / "netsim"), "--set", "mpi.posted_recvs=8", "--scenario", "imb", "--nodes", "8",
+                        "--json"], capture_output=True, text=True)
+    assert r.returncode == 1 and "posted_recvs" in r.stdout
+    r = subprocess.run([str(build / "netsim"), "--dump-config"], capture_output=True, text=True)
+    assert "[mpi]" in r.stdout and "eager_limit = 4096" in r.stdout
