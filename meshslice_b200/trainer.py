@@ -124,7 +124,7 @@ class Trainer:
         stage_a = m * gath * 2
         stage_b = max(i * o // C for i, o, _ in lin) * 2
         slots = max(m * max((i if df == "os" else o) for i, o, df in lin), max(i * o // C for i, o, _ in lin)) * 2
-        send = m * gath // C * 2
+        send = 0      # gathers read the operands in place (push based): no send buffers
         return stage_a, stage_b, slots, send
 
     # ------------------------------------------------------------------ data

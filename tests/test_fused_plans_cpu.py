@@ -197,3 +197,38 @@ def test_k_panel_plans(mesh, order, sub):
             first_x = next(i for i, j in enumerate(jobs) if j[0] == 0)
             own_flag = ((rank + 1) << 40) + 4 * (rt.CHUNK0 + (rank % C) * sub)
             assert chunks[first_x][2] == [own_flag]
+
+
+@pytest.mark.parametrize("mesh", [(2, 4), (4, 2)])
+@pytest.mark.parametrize("model", [dict(d=4096, f=16384, mb=16), dict(d=12288, f=49152, mb=8)])
+def test_every_linear_of_the_benchmark_models_has_a_fused_plan(mesh, model):
+    """Forward, data-gradient and weight-gradient products of the four linears of a block
+    (6.7B-shaped and 175B-width) on both 8-GPU meshes: no shape falls back to the generic
+    formulation, and chunk flags / slice counters stay inside the flag block."""
+    R, C = mesh
+    d, f = model["d"], model["f"]
+    m = model["mb"] // R * 2048 if model["mb"] >= R else 2048          # tokens per rank and micro-batch
+    lin = [(d, 3 * d, "os"), (d, d, "ls"), (d, f, "os"), (f, d, "ls")]
+    for i, o, df in lin:
+        def run(fg, mc, i=i, o=o, df=df):
+            X = FakeT(5, i // C)
+            if df == "os":
+                fg.os([10 ** 9] * C, [2 * 10 ** 9] * R, m, i // C, i // R, o // C, None, n_slices=4)      # y = x W
+                fg.ls(FakeT(5, o // C), [3 * 10 ** 9] * R, m, o // C, i // R, None, n_slices=4)          # dx = dy W^T
+                fg.rs([7 * 10 ** 9] * C, FakeT(6, o // C), m, i // C, o // C, None, n_slices=4)          # dW = x^T dy
+            else:
+                fg.ls(X, [3 * 10 ** 9] * R, m, i // C, o // R, None, n_slices=4)                          # y = x W^T
+                fg.os([10 ** 9] * C, [2 * 10 ** 9] * R, m, o // C, o // R, i // C, None, n_slices=4)      # dx = dy W
+                fg.rs([7 * 10 ** 9] * C, FakeT(6, i // C), m, o // C, i // C, None, n_slices=4)          # dW = dy^T x
+        calls = []
+        def capture_all(fg, mc):
+            real_launch = fg._launch
+            fg._launch = lambda d_, exit_barrier, phase="all", reset=True: calls.append(d_)
+            run(fg, mc)
+        _capture(R, C, capture_all)
+        assert len(calls) == 3 * R * C
+        for d_ in calls:
+            assert d_.get("n_chunks", 0) <= rt.NCHUNK
+            assert d_["n_slices"] <= rt.NCOUNTER
+            for k in ("M", "N", "K"):
+                assert d_[k] > 0
