@@ -16,6 +16,8 @@
 
 #include <cuda_bf16.h>
 
+#include <cstdlib>
+
 #include "../common/ptx.cuh"
 #include "../gemm/sm100_gemm.h"  // make_tensor_map_2d
 
@@ -27,7 +29,12 @@ constexpr int kD = 128;         // head dim
 constexpr int kBlk = 128;       // query / key rows per tile
 constexpr int kTile = kBlk * kD * 2;  // 32 KiB: one [128 x 128] bf16 tile = two swizzle halves
 constexpr int kHalf = kTile / 2;
-constexpr int kAttnThreads = 192;
+// Element-wise warps (softmax in the forward pass, P / dS and the dQ drain in the backward pass)
+// are a template parameter of the kernels.  Four warps give one thread per tile row; eight give
+// two threads per row, each owning 64 of the 128 columns: the exponentials and the TMEM traffic
+// of a block, which sit in series with the MMAs, take half as long.  A warp may touch the TMEM
+// lanes 32 * (warp % 4) ... + 31, so warps 2-5 and 6-9 both cover all four lane quarters.
+constexpr int attn_threads(int ew_warps) { return 64 + 32 * ew_warps; }
 constexpr uint32_t kErrAttn = 20;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
@@ -58,6 +65,15 @@ __device__ __forceinline__ bool warp_wait(uint64_t* bar, uint32_t parity, uint64
   ok = __shfl_sync(0xffffffffu, ok, 0);
   if (ok) mbar_wait(bar, parity, tmo);  // already complete: orders this lane's later reads
   return ok != 0;
+}
+
+// 2^x on the special-function unit in one instruction (relative error 2^-22, denormal results
+// flushed to zero: probabilities below 2^-126 are zero anyway).  exp2f() wraps the same
+// instruction in range scaling that costs several more issue slots per element.
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
 }
 
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
@@ -99,8 +115,14 @@ __device__ __forceinline__ void load_tile(uint8_t* dst, const CUtensorMap* map, 
 // ==========================================================================================
 // forward
 // ==========================================================================================
-__global__ void __launch_bounds__(kAttnThreads, 1)
+template <int kEwWarps>
+__global__ void __launch_bounds__(attn_threads(kEwWarps), 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant__ AttnArgs a) {
+  static_assert(kEwWarps == 4 || kEwWarps == 8, "four or eight element-wise warps");
+  constexpr int kHalves = kEwWarps / 4;
+  constexpr int kColsPer = kBlk / kHalves;   // columns per thread
+  constexpr int kChunks = kColsPer / 32;     // 32-column TMEM loads per thread and block
+  constexpr int kEwThreads = 32 * kEwWarps;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
@@ -115,7 +137,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constan
   uint64_t* s_full = bars + 5;    // [2]
   uint64_t* p_ready = bars + 7;
   uint64_t* pv_done = bars + 8;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
+  uint64_t* xchg = bars + 9;      // the two threads of a row exchange their partial maximum / sum
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
+  float* sX = reinterpret_cast<float*>(smem + 6 * kTile + 256);   // [2 phases][2 halves][128 rows]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nblk = a.seq / kBlk;
@@ -134,8 +158,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constan
       mbar_init(kv_empty + i, 1);
       mbar_init(s_full + i, 1);
     }
-    mbar_init(p_ready, 128);
+    mbar_init(p_ready, kEwThreads);
     mbar_init(pv_done, 1);
+    mbar_init(xchg, kEwThreads);
     mbar_fence_init();
   }
   if (warp == 1) {
@@ -209,13 +234,29 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constan
       }
     }
   } else {
-    // ---------------- softmax / epilogue: one thread per query row ----------------
+    // ---------------- softmax / epilogue: kHalves threads per query row ----------------
     const int q4 = warp & 3;
+    const int half = (warp - 2) >> 2;         // which kColsPer columns of the row this thread owns
+    const int col0 = half * kColsPer;
     const int row = q4 * 32 + lane;           // row inside the tile == TMEM lane
     const uint32_t lane_off = static_cast<uint32_t>(q4 * 32) << 16;
     const float sl2 = a.scale * kLog2e;
     float m_used = -INFINITY, l = 0.f;
     bool ok = true;
+    int xphase = 0;
+    // both threads of a row leave this with the combined value (maximum or sum)
+    auto exchange = [&](float v, bool is_max, bool& good) -> float {
+      if (kHalves == 1) return v;
+      sX[(xphase * 2 + half) * kBlk + row] = v;
+      mbar_arrive(xchg);
+      if (!warp_wait(xchg, xphase, 6 * tmo)) {
+        good = false;
+        return v;
+      }
+      const float o = sX[(xphase * 2 + (half ^ 1)) * kBlk + row];
+      xphase ^= 1;
+      return is_max ? fmaxf(v, o) : v + o;
+    };
     for (int j = 0; j < n_kv; ++j) {
       const int sb = j & 1;
       if (!warp_wait(s_full + sb, (j >> 1) & 1, 6 * tmo)) {
@@ -224,19 +265,24 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constan
         break;
       }
       tc_fence_after_sync();
-      const uint32_t ts = tmem + lane_off + sb * 128;
+      const uint32_t ts = tmem + lane_off + sb * 128 + col0;
       const bool diag = a.causal && j == i_blk;
       float mx = -INFINITY;
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < kChunks; ++c) {
         uint32_t r[32];
         tmem_ld_32x32(ts + c * 32, r);
         tmem_ld_wait();
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
           const float v = __uint_as_float(r[i]);
-          if (!diag || c * 32 + i <= row) mx = fmaxf(mx, v);
+          if (!diag || col0 + c * 32 + i <= row) mx = fmaxf(mx, v);
         }
+      }
+      mx = exchange(mx, true, ok);
+      if (!ok) {
+        if (lane == 0) report(a.status, kErrAttn + 8, j, 0);
+        break;
       }
       const float m_blk = mx * sl2;
       if (j == 0) {
@@ -257,9 +303,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constan
             l *= alpha;
             m_used = m_new;
           }
-          const uint32_t to = tmem_o + lane_off;
+          const uint32_t to = tmem_o + lane_off + col0;
 #pragma unroll 1
-          for (int c = 0; c < 4; ++c) {
+          for (int c = 0; c < kChunks; ++c) {
             uint32_t r[32];
             tmem_ld_32x32(to + c * 32, r);
             tmem_ld_wait();
@@ -272,24 +318,28 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constan
       }
       float rowsum = 0.f;
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < kChunks; ++c) {
         uint32_t r[32];
         tmem_ld_32x32(ts + c * 32, r);
         tmem_ld_wait();
         float p[32];
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-          float e = exp2f(__uint_as_float(r[i]) * sl2 - m_used);
-          if (diag && c * 32 + i > row) e = 0.f;
+          float e = fast_exp2(__uint_as_float(r[i]) * sl2 - m_used);
+          if (diag && col0 + c * 32 + i > row) e = 0.f;
           p[i] = e;
           rowsum += e;
         }
-        store_tile_row32(sP, row, c * 32, p);
+        store_tile_row32(sP, row, col0 + c * 32, p);
       }
       l += rowsum;
       fence_proxy_async_smem();
       tc_fence_before_sync();
       mbar_arrive(p_ready);
+    }
+    if (ok) {
+      l = exchange(l, false, ok);   // the row's denominator: both halves
+      if (!ok && lane == 0) report(a.status, kErrAttn + 9, 0, 0);
     }
     if (ok) {
       if (!warp_wait(pv_done, (n_kv - 1) & 1, 6 * tmo)) {
@@ -301,10 +351,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constan
       tc_fence_after_sync();
       const float inv = 1.0f / l;
       __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(a.out) +
-                            (int64_t)(row0 + row) * (a.heads * kD) + h * kD;
-      const uint32_t to = tmem_o + lane_off;
+                            (int64_t)(row0 + row) * (a.heads * kD) + h * kD + col0;
+      const uint32_t to = tmem_o + lane_off + col0;
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < kChunks; ++c) {
         uint32_t r[32];
         tmem_ld_32x32(to + c * 32, r);
         tmem_ld_wait();
@@ -318,7 +368,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constan
           *reinterpret_cast<uint4*>(orow + c * 32 + q * 8) = u;
         }
       }
-      a.lse[((int64_t)b * a.heads + h) * a.seq + i_blk * kBlk + row] = m_used * kLn2 + logf(l);
+      if (half == 0) a.lse[((int64_t)b * a.heads + h) * a.seq + i_blk * kBlk + row] = m_used * kLn2 + logf(l);
     }
   }
   tc_fence_before_sync();
@@ -370,9 +420,14 @@ __global__ void attn_dq_store_kernel(const float4* __restrict__ dq_acc, __nv_bfl
   }
 }
 
-__global__ void __launch_bounds__(kAttnThreads, 1)
+template <int kEwWarps>
+__global__ void __launch_bounds__(attn_threads(kEwWarps), 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant__ CUtensorMap tm_do,
                 const __grid_constant__ AttnArgs a) {
+  static_assert(kEwWarps == 4 || kEwWarps == 8, "four or eight element-wise warps");
+  constexpr int kColsPer = kBlk / (kEwWarps / 4);
+  constexpr int kChunks = kColsPer / 32;
+  constexpr int kEwThreads = 32 * kEwWarps;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
@@ -408,9 +463,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constan
     mbar_init(qdo_full, 1);
     mbar_init(qdo_empty, 1);
     mbar_init(sdp_full, 1);
-    mbar_init(pds_ready, 128);
+    mbar_init(pds_ready, kEwThreads);
     mbar_init(mma_done, 1);
-    mbar_init(dq_drained, 128);
+    mbar_init(dq_drained, kEwThreads);
     mbar_fence_init();
   }
   if (warp == 1) {
@@ -484,8 +539,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constan
     }
   } else {
     const int q4 = warp & 3;
+    const int col0 = ((warp - 2) >> 2) * kColsPer;   // this thread's columns of every 128-wide row
     const int row = q4 * 32 + lane;
-    const uint32_t lane_off = static_cast<uint32_t>(q4 * 32) << 16;
+    const uint32_t lane_off = (static_cast<uint32_t>(q4 * 32) << 16) + col0;
     const float sl2 = a.scale * kLog2e;
     bool ok = true;
     for (int it = 0; it < n_it; ++it) {
@@ -502,7 +558,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constan
       tc_fence_after_sync();
       const bool diag = a.causal && i_blk == j_blk;
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < kChunks; ++c) {
         uint32_t rs[32], rp[32];
         tmem_ld_32x32(t_s + lane_off + c * 32, rs);
         tmem_ld_32x32(t_dp + lane_off + c * 32, rp);
@@ -510,13 +566,13 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constan
         float p[32], ds[32];
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-          float e = exp2f(__uint_as_float(rs[i]) * sl2 - lse2);
-          if (diag && c * 32 + i > row) e = 0.f;
+          float e = fast_exp2(__uint_as_float(rs[i]) * sl2 - lse2);
+          if (diag && col0 + c * 32 + i > row) e = 0.f;
           p[i] = e;
           ds[i] = e * (__uint_as_float(rp[i]) - dlt) * a.scale;
         }
-        store_tile_row32(sP, row, c * 32, p);
-        store_tile_row32(sdS, row, c * 32, ds);
+        store_tile_row32(sP, row, col0 + c * 32, p);
+        store_tile_row32(sdS, row, col0 + c * 32, ds);
       }
       fence_proxy_async_smem();
       tc_fence_before_sync();
@@ -527,9 +583,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constan
         break;
       }
       tc_fence_after_sync();
-      float* dq = a.dq_acc + qtok * (a.heads * kD) + h * kD;
+      float* dq = a.dq_acc + qtok * (a.heads * kD) + h * kD + col0;
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < kChunks; ++c) {
         uint32_t r[32];
         tmem_ld_32x32(t_s + lane_off + c * 32, r);
         tmem_ld_wait();
@@ -551,9 +607,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constan
 #pragma unroll 1
       for (int which = 0; which < 2; ++which) {
         const uint32_t t = (which == 0 ? t_dk : t_dv) + lane_off;
-        __nv_bfloat16* dst = base + (which == 0 ? kD : 2 * kD);
+        __nv_bfloat16* dst = base + (which == 0 ? kD : 2 * kD) + col0;
 #pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
+        for (int c = 0; c < kChunks; ++c) {
           uint32_t r[32];
           tmem_ld_32x32(t + c * 32, r);
           tmem_ld_wait();
@@ -576,7 +632,16 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constan
   if (warp == 1) tmem_dealloc(tmem, 512);
 }
 
-constexpr size_t kAttnSmem = 6 * kTile + 256 + 1024;
+constexpr size_t kAttnSmem = 6 * kTile + 256 + 2 * 2 * kBlk * sizeof(float) + 1024;
+
+// Element-wise warps per CTA: 8 unless MSB_ATTN_EW_WARPS=4 is set in the environment.
+int ew_warps() {
+  static const int v = [] {
+    const char* e = std::getenv("MSB_ATTN_EW_WARPS");
+    return (e != nullptr && e[0] == '4' && e[1] == '\0') ? 4 : 8;
+  }();
+  return v;
+}
 
 // The shared-memory attribute is per device: set it once on every device that launches.
 cudaError_t configure_device() {
@@ -585,9 +650,13 @@ cudaError_t configure_device() {
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return e;
   if (dev >= 0 && dev < 64 && configured[dev]) return cudaSuccess;
-  e = cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kAttnSmem);
+  e = cudaFuncSetAttribute(attn_fwd_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kAttnSmem);
   if (e != cudaSuccess) return e;
-  e = cudaFuncSetAttribute(attn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kAttnSmem);
+  e = cudaFuncSetAttribute(attn_fwd_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kAttnSmem);
+  if (e != cudaSuccess) return e;
+  e = cudaFuncSetAttribute(attn_bwd_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kAttnSmem);
+  if (e != cudaSuccess) return e;
+  e = cudaFuncSetAttribute(attn_bwd_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kAttnSmem);
   if (e != cudaSuccess) return e;
   if (dev >= 0 && dev < 64) configured[dev] = true;
   return cudaSuccess;
@@ -614,7 +683,8 @@ cudaError_t attention_fwd(const void* qkv, void* out, float* lse, int batch, int
   a.status = status;
   a.timeout_ns = 2000000000ull;
   dim3 grid(seq / kBlk, heads, batch);
-  attn_fwd_kernel<<<grid, kAttnThreads, kAttnSmem, stream>>>(tm, a);
+  if (ew_warps() == 8) attn_fwd_kernel<8><<<grid, attn_threads(8), kAttnSmem, stream>>>(tm, a);
+  else attn_fwd_kernel<4><<<grid, attn_threads(4), kAttnSmem, stream>>>(tm, a);
   return cudaGetLastError();
 }
 
@@ -650,7 +720,8 @@ cudaError_t attention_bwd(const void* qkv, const void* out, const void* dout, co
   a.status = status;
   a.timeout_ns = 2000000000ull;
   dim3 grid(seq / kBlk, heads, batch);
-  attn_bwd_kernel<<<grid, kAttnThreads, kAttnSmem, stream>>>(tq, td, a);
+  if (ew_warps() == 8) attn_bwd_kernel<8><<<grid, attn_threads(8), kAttnSmem, stream>>>(tq, td, a);
+  else attn_bwd_kernel<4><<<grid, attn_threads(4), kAttnSmem, stream>>>(tq, td, a);
   e = cudaGetLastError();
   if (e != cudaSuccess) return e;
   attn_dq_store_kernel<<<148 * 8, 256, 0, stream>>>(reinterpret_cast<const float4*>(dq_acc),
