@@ -161,8 +161,22 @@ class Trainer:
             return float(self._loss_dev.item())
         return self._loss_dev
 
-    def check(self):
-        _native.check_status()
+    def check(self, all_ranks: bool = False):
+        """Raise if a kernel of this rank reported an error status since the last check.  With
+        ``all_ranks`` the ranks first exchange their status codes (one small all-reduce), so an
+        error on any rank raises on every rank, naming the rank that failed."""
+        if not all_ranks or self.world == 1:
+            _native.check_status()
+            return
+        from .utils.health import agree_on_status
+        torch.cuda.synchronize()
+        st = _native.status()
+        code = st.read()[0]
+        try:
+            agree_on_status(code, device=self.device)
+        finally:
+            if code:
+                st.clear()
 
     def tflops(self, ms_per_step: float) -> float:
         """Model TFLOP/s of the whole job for a measured step time."""

@@ -62,3 +62,34 @@ def guarded_step(hb: Heartbeat, step: int, fn, timeout_s: float = 5.0):
     except Exception as e:
         hb.leave(f"{type(e).__name__}: {e}")
         raise
+
+
+class RemoteKernelError(RuntimeError):
+    """Another rank's kernel reported an error status."""
+
+
+def agree_on_status(local_code: int, group=None, device=None) -> None:
+    """Makes a kernel error of ANY rank an exception on EVERY rank of ``group``.
+
+    Every rank contributes the status code its own kernels reported since the last check (0 when
+    nothing went wrong); the codes are max-reduced together with the reporting rank, so all ranks
+    learn which rank failed and with what, and stop before the next step instead of running into
+    bounded waits one after another.  One small all-reduce: meant to be called once per step.
+    ``device`` selects where the two-element tensor lives (CPU for Gloo groups, the current GPU
+    for NCCL groups)."""
+    import torch
+    import torch.distributed as dist
+    if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size(group) == 1:
+        if local_code:
+            raise RemoteKernelError(f"kernel status {local_code} on this rank")
+        return
+    rank = dist.get_rank(group)
+    # code in the high part, rank in the low part: the maximum names the failing rank as well
+    packed = torch.tensor([int(local_code) * 65536 + (rank if local_code else 0)], dtype=torch.int64,
+                          device=device or "cpu")
+    dist.all_reduce(packed, op=dist.ReduceOp.MAX, group=group)
+    worst = int(packed.item())
+    if worst:
+        code, who = divmod(worst, 65536)
+        raise RemoteKernelError(f"kernel status {code} reported by rank {who}" +
+                                (" (this rank)" if who == rank and local_code == code else ""))

@@ -84,6 +84,14 @@ def main():
         except PeerLostError as e:
             print(f"rank {rank} PEER_LOST: {e}", flush=True)
         os._exit(0)
+    elif mode == "status_agreement":
+        from meshslice_b200.utils.health import RemoteKernelError, agree_on_status
+        agree_on_status(0)                       # nobody failed: no exception anywhere
+        try:
+            agree_on_status(5 if rank == 1 else 0)   # rank 1's kernel timed out waiting for a chunk
+            print(f"rank {rank} MISSED", flush=True)
+        except RemoteKernelError as e:
+            print(f"rank {rank} AGREED: {e}", flush=True)
     dist.barrier()
     dist.destroy_process_group()
 

@@ -52,3 +52,9 @@ def test_rank_that_raises_tells_the_others():
     r = _launch("rank_raises", 2, 29714)
     assert "rank 0 RAISED" in r.stdout
     assert "rank 1 PEER_LOST" in r.stdout and "bad shard file" in r.stdout, r.stdout + r.stderr[-2000:]
+
+
+def test_kernel_error_of_one_rank_raises_on_every_rank():
+    r = _launch("status_agreement", 3, 29715)
+    assert r.stdout.count("AGREED: kernel status 5 reported by rank 1") == 3, r.stdout + r.stderr[-2000:]
+    assert "MISSED" not in r.stdout
