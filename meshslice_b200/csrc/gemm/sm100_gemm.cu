@@ -661,8 +661,9 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * kBN;
       if (a.push_n > 0) {
         // Push path: 64 columns at a time go through this warp's 4 KiB staging buffer (128-byte
-        // swizzled, so the lanes' row writes spread over the banks) and leave as ONE 2-D TMA
-        // tensor store of 32 rows x 128 bytes into the owner's slot (posted writes over NVLink).
+        // swizzled, so the lanes' row writes spread over the banks) and leave for the owner's slot
+        // either as coalesced 16-byte stores read back row-major (push_mode 1) or as ONE 2-D TMA
+        // tensor store of 32 rows x 128 bytes (push_mode 0); both are posted writes over NVLink.
         uint8_t* stage_buf[3];
         stage_buf[0] = sEpi + (warp - 2) * kEpiStageBytes;
         stage_buf[1] = sA + (kStages - 1) * kAStageBytes + (warp - 2) * kEpiStageBytes;
