@@ -39,6 +39,7 @@ def timeit(fn, iters=5, warm=2):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--mesh", default="")
+    ap.add_argument("--meshes", nargs="*", default=[], help="several RxC meshes in one job, e.g. 2x4 4x2 1x8 8x1")
     ap.add_argument("--slices", type=int, nargs="+", default=[1, 2, 4, 8])
     ap.add_argument("--shapes", type=int, nargs="*", default=[], help="M K N triples; default: the four headline shapes")
     ap.add_argument("--peak-tflops", type=float, default=1380.6)
@@ -56,15 +57,26 @@ def main():
     from meshslice_b200.parallel.mesh import DistMesh, ShardedTensor
     from meshslice_b200.trainer import choose_mesh
 
-    R, C = [int(v) for v in args.mesh.split("x")] if args.mesh else choose_mesh(world)
-    mesh = DistMesh(R, C)
+    mesh_specs = args.meshes or ([args.mesh] if args.mesh else ["%dx%d" % choose_mesh(world)])
     shapes = [tuple(args.shapes[i:i + 3]) for i in range(0, len(args.shapes), 3)] or SHAPES
     big = max(max(M * K, K * N, M * N) for M, K, N in shapes)
-    eng = FusedEngine(mesh, 2 * big // R + (1 << 20), 2 * big // C + (1 << 20), 2 * big // min(R, C) + (1 << 20),
-                      2 * big // (R * C) + (1 << 20), extra_heap_bytes=2 * 2 * big // (R * C) + (4 << 20))
-    key = (mesh.r, mesh.c)
     out = []
     say = (lambda *a: print(*a, flush=True)) if rank == 0 else (lambda *a: None)
+    for spec in mesh_specs:      # every mesh gets its own process groups, heap and engine, in one job
+        R, C = [int(v) for v in spec.split("x")]
+        mesh = DistMesh(R, C)
+        eng = FusedEngine(mesh, 2 * big // R + (1 << 20), 2 * big // C + (1 << 20), 2 * big // min(R, C) + (1 << 20), 0)
+        run_mesh(args, mesh, eng, shapes, world, out, say, tp, ShardedTensor)
+        torch.cuda.empty_cache()
+    if rank == 0 and args.json:
+        json.dump(out, open(args.json, "w"), indent=1)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def run_mesh(args, mesh, eng, shapes, world, out, say, tp, ShardedTensor):
+    R, C = mesh.R, mesh.C
+    key = (mesh.r, mesh.c)
     for (M, K, N) in shapes:
         flops = 2.0 * M * K * N / world
         t_comp = flops / (args.peak_tflops * 1e12)
@@ -100,10 +112,6 @@ def main():
                     row["k_panel"][order] = dict(ms=t * 1e3, tflops=flops / t / 1e12, roofline_frac=roof / t)
             say(json.dumps(row))
             out.append(row)
-    if rank == 0 and args.json:
-        json.dump(out, open(args.json, "w"), indent=1)
-    dist.barrier()
-    dist.destroy_process_group()
 
 
 if __name__ == "__main__":
