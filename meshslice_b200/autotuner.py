@@ -412,6 +412,10 @@ def main(argv=None):
     p.add_argument("--sweep", action="store_true")
     p.add_argument("--fabric-json", type=str, default="", help="constants fitted by BenchCollectives2D")
     p.add_argument("--fabric", type=str, default="b200", choices=["b200", "tpuv4"])
+    p.add_argument("--netsim-config", type=str, default="",
+                   help="fit the fabric constants from simulated sweeps of this system description "
+                        "(a file, or the name of one shipped with the simulator)")
+    p.add_argument("--netsim-topology", type=str, default="crossbar", help="crossbar or torus (one ring per mesh axis)")
     p.add_argument("--tuned-json", type=str, default="", help="write the decision here")
     p.add_argument("--blocksize", type=int, default=64)
     p.add_argument("--measure-matmul", action="store_true", help="time the tcgen05 GEMM instead of the analytic model")
@@ -420,13 +424,18 @@ def main(argv=None):
     B = n if a.batchsize <= 0 else a.batchsize
     graph = build_transformerBlock(B, a.seqlen, a.nheads, a.headdim)
     graph.printGraph()
-    fabric = (FabricConstants.load(a.fabric_json) if a.fabric_json else
-              FabricConstants.from_dict(B200_NVSWITCH if a.fabric == "b200" else TPUV4))
+    if a.netsim_config:
+        from .utils import netsim
+        fabric = FabricConstants.from_dict(netsim.fit_fabric(a.nrows, a.ncols, a.netsim_config, a.netsim_topology))
+        print(f"fabric constants fitted from the simulator: {fabric.bws}")
+    else:
+        fabric = (FabricConstants.load(a.fabric_json) if a.fabric_json else
+                  FabricConstants.from_dict(B200_NVSWITCH if a.fabric == "b200" else TPUV4))
     matmul = CostModel.MeasuredMatmul() if a.measure_matmul else None
     shapes = candidate_shapes(n)
     print(shapes)
     tuner = Autotuner(graph, shapes, fabric=fabric, blocksize=a.blocksize, matmul=matmul,
-                      klist=[1, 2, 4, 8] if a.fabric == "b200" and not a.fabric_json else None)
+                      klist=[1, 2, 4, 8] if a.fabric == "b200" and not a.fabric_json and not a.netsim_config else None)
     tuner.emulatedFinetune(a.sweep)
     if a.tuned_json:
         json.dump(tuner.result(), open(a.tuned_json, "w"), indent=1)

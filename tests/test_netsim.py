@@ -91,3 +91,29 @@ def test_config_errors_name_file_and_line(build, tmp_path):
     assert r.returncode == 1 and "posted_recvs" in r.stdout
     r = subprocess.run([str(build / "netsim"), "--dump-config"], capture_output=True, text=True)
     assert "[mpi]" in r.stdout and "eager_limit = 4096" in r.stdout
+
+
+def test_python_front_end_fits_fabric_constants_for_the_autotuner(tmp_path, monkeypatch):
+    """Simulated sweeps -> fabric constants -> the tuner's pick: a switch with fast links keeps the
+    large activations in place and gathers weights (8 x 1); slow NIC links change the answer."""
+    from meshslice_b200 import autotuner as AT
+    from meshslice_b200.utils import netsim
+    monkeypatch.setenv("MSB_NETSIM_CACHE", str(tmp_path))
+    rec = netsim.run("rdma-msg", nodes=2, nbytes=400, config="sst_torus.ini")
+    assert rec["ok"] and "data ok" in rec["lines"][0]
+    with pytest.raises(netsim.NetsimError):
+        netsim.run("rdma-msg", nodes=2, settings={"network.link_gbz": 1})
+    sizes = (1 << 12, 1 << 14, 1 << 16, 1 << 18, 1 << 20)
+    fast = netsim.fit_fabric(2, 4, config="b200_nvswitch.ini", topology="crossbar", sizes=sizes)
+    slow = netsim.fit_fabric(2, 4, config="sst_torus.ini", topology="torus", sizes=sizes, flops_per_chip=2.66e14)
+    assert fast["fabric"] == "switch" and slow["fabric"] == "ring"
+    assert min(fast["bws"]["allgather"]) > 20 * max(slow["bws"]["allgather"])
+    graph = AT.build_transformerBlock(32, 2048, 32, 128)
+    picks = {}
+    for name, d in (("fast", fast), ("slow", slow)):
+        t = AT.Autotuner(graph, [(1, 8), (2, 4), (4, 2), (8, 1)], fabric=AT.FabricConstants.from_dict(d), blocksize=64,
+                         klist=[1, 2, 4, 8], verbose=False)
+        t.emulatedFinetune(sweep=True)
+        picks[name] = (tuple(t.result()["mesh"]), t.result()["predicted_time_s"])
+    assert picks["fast"][0] == (8, 1)
+    assert picks["slow"][1] > 3 * picks["fast"][1]
