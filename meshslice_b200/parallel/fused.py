@@ -20,7 +20,7 @@ from __future__ import annotations
 import os
 
 from dataclasses import dataclass
-from typing import List
+from typing import List, Optional
 
 import torch
 
@@ -96,7 +96,10 @@ class FusedGemm:
     """
 
     def __init__(self, mesh: MeshCoord, world: rt.World, grid: int, timeout_ns: int = 5_000_000_000,
-                 use_barriers: bool = True):
+                 use_barriers: bool = True, debug: Optional[bool] = None):
+        # debug (or MSB_DEBUG_PLANS=1): every address that a plan hands to the kernel is checked on
+        # the host against the workspace buffers before the launch (see validate_*)
+        self.debug = (os.environ.get("MSB_DEBUG_PLANS", "0") == "1") if debug is None else debug
         self.mesh = mesh
         self.world = world
         self.grid = grid
@@ -119,9 +122,73 @@ class FusedGemm:
                     accumulate=1 if accumulate else 0, status=_native.status().dev, grid=self.grid,
                     stream=stream, timeout_ns=self.timeout_ns)
 
+    # ------------------------------------------------------------------ plan validation
+    def _region(self, ptr: int, nbytes: int, what: str):
+        """(rank, buffer name) of the workspace buffer that holds [ptr, ptr + nbytes); raises
+        FusedPlanError when the range is not inside one staging / slot buffer of one rank."""
+        ws = self.world.mine
+        for rank in range(self.world.size):
+            for name, size in (("stage_a", ws.stage_a_bytes), ("stage_b", ws.stage_b_bytes), ("slots", ws.slot_bytes)):
+                base = self.world.ptr(rank, getattr(ws, name))
+                if base <= ptr and ptr + nbytes <= base + size:
+                    return rank, name
+        raise FusedPlanError(f"{what}: [{ptr:#x}, +{nbytes}) is outside every workspace buffer")
+
+    def validate_plan(self, jobs, chunks):
+        """Gather plan: every destination block lies inside a staging buffer, every signal is a chunk
+        flag of some rank, chunk job ranges are ordered and inside the job list."""
+        for i, (sel, src, rows, rb, sp, dp, dsts) in enumerate(jobs):
+            if rows <= 0 or rb <= 0 or rb % 16 or src % 16 or sp % 16 or dp % 16 or sel not in (0, 1):
+                raise FusedPlanError(f"job {i}: bad geometry (rows {rows}, row bytes {rb}, pitches {sp}/{dp})")
+            if not 0 < len(dsts) <= 8:
+                raise FusedPlanError(f"job {i}: {len(dsts)} destinations")
+            for dptr in dsts:
+                if dptr % 16:
+                    raise FusedPlanError(f"job {i}: destination not 16-byte aligned")
+                rank, name = self._region(dptr, (rows - 1) * dp + rb, f"job {i}")
+                if name == "slots":
+                    raise FusedPlanError(f"job {i}: gathers into the slot buffer of rank {rank}")
+        ws = self.world.mine
+        for i, (jb, je, sigs, target) in enumerate(chunks):
+            if not 0 <= jb <= je <= len(jobs) or target <= 0 or len(sigs) > 8:
+                raise FusedPlanError(f"chunk {i}: bad job range [{jb}, {je}) or target {target}")
+            for sp_ in sigs:
+                ok = False
+                for rank in range(self.world.size):
+                    word, rem = divmod(sp_ - self.world.ptr(rank, ws.flags), 4)
+                    ok |= rem == 0 and rt.CHUNK0 <= word < rt.CHUNK0 + rt.NCHUNK
+                if not ok:
+                    raise FusedPlanError(f"chunk {i}: signal {sp_:#x} is not a chunk flag")
+
+    def validate_launch(self, d):
+        """Push / reduce side of a launch: owners' slot ranges, counters, slice and flag counts."""
+        ws = self.world.mine
+        if d.get("n_slices", 1) > rt.NCOUNTER:
+            raise FusedPlanError("more slices than arrival counters")
+        if d.get("n_chunks", 0) > rt.NCHUNK:
+            raise FusedPlanError("more chunks than chunk flags")
+        for mode, base, per in (("a_flag_mode", "a_flag_base", "a_kpanel"), ("b_flag_mode", "b_flag_base", "b_kpanel")):
+            if d.get(mode, 0) == 3:
+                kblocks = (d["K"] + 63) // 64
+                if d.get(base, 0) + (kblocks + d[per] - 1) // d[per] > rt.NCHUNK:
+                    raise FusedPlanError("K-panel flags beyond the flag block")
+        if d.get("push_n", 0):
+            extent = d["push_rows"] * d["push_ld"] * 2
+            for o, (pb, pc) in enumerate(zip(d["push_base"], d["push_counter"])):
+                rank, name = self._region(pb, extent, f"push slot of owner {o}")
+                if name != "slots":
+                    raise FusedPlanError(f"owner {o}: partial tiles pushed into {name}")
+                if pc != self.world.flag_ptr(rank, rt.COUNTER0):
+                    raise FusedPlanError(f"owner {o}: counter pointer is not rank {rank}'s counter block")
+        if d.get("red_n", 0):
+            if d["red_n"] * d["red_rows"] * d["red_ld"] * 2 > ws.slot_bytes or d["red_slots"] != ws.local(ws.slots):
+                raise FusedPlanError("reduce phase reads beyond the slot buffer")
+
     def _jobs(self, key, builder):
         if key not in self._cache:
             jobs, chunks = builder()
+            if self.debug:
+                self.validate_plan(jobs, chunks)
             dev = torch.device("cuda", torch.cuda.current_device())
             self._cache[key] = rt.upload_push_plan(jobs, chunks, dev) + (len(chunks),)
         return self._cache[key]
@@ -133,6 +200,8 @@ class FusedGemm:
         """phases 'comm' (gather only), 'gemm' (tiles only) and 'reduce' (slot sums only) split one
         launch in three; together with reset=False this lets a test run several emulated ranks
         one after another on one GPU without any launch waiting for a kernel that is not running."""
+        if self.debug:
+            self.validate_launch(d)
         if d.get("push_n", 0):
             d["push_bufs"] = self.push_bufs
             d["push_mode"] = self.push_mode

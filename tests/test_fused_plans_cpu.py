@@ -232,3 +232,50 @@ def test_every_linear_of_the_benchmark_models_has_a_fused_plan(mesh, model):
             assert d_["n_slices"] <= rt.NCOUNTER
             for k in ("M", "N", "K"):
                 assert d_[k] > 0
+
+
+@pytest.mark.parametrize("mesh", [(2, 4), (4, 2), (2, 2)])
+def test_debug_validation_accepts_real_plans_and_rejects_corrupted_ones(mesh):
+    """The host-side bounds checks of the debug mode: every address of the OS / LS / RS / K-panel
+    plans lies inside a workspace buffer; a buffer that is too small, a stray destination, a wrong
+    counter pointer or a signal that is not a chunk flag are refused before any launch."""
+    R, C = mesh
+    m, kl, kr, n = 1024, 2048 // C, 2048 // R, 512
+    calls = {
+        "os": lambda fg, mc: fg.os([10 ** 9] * C, [2 * 10 ** 9] * R, m, kl, kr, n, None, n_slices=4),
+        "ls": lambda fg, mc: fg.ls(FakeT(5, 256), [3 * 10 ** 9] * R, 512, 256, 1024 * C, None, n_slices=4),
+        "rs": lambda fg, mc: fg.rs([7 * 10 ** 9] * C, FakeT(6, 512), 384, 512 * R, 512, None, n_slices=2, cyc=2),
+        "kp": lambda fg, mc: fg.os_kpanel([10 ** 9] * C, [2 * 10 ** 9] * R, m, kl, kr, n, None, order="wang", sub=2),
+    }
+    for name, call in calls.items():
+        caps = _capture(R, C, call)
+        for rank, cap in caps.items():
+            mc = fz.MeshCoord(R, C, *divmod(rank, C))
+            fg = fz.FusedGemm.__new__(fz.FusedGemm)
+            fg.mesh, fg.world = mc, FakeWorld(R * C, rank)
+            if "plan" in cap:
+                fg.validate_plan(*cap["plan"])
+            fg.validate_launch(cap["d"])
+            # the same plan against staging buffers that are too small
+            small = FakeWorld(R * C, rank)
+            for w in small.wss:
+                w.stage_a_bytes = w.stage_b_bytes = 4096
+                w.slot_bytes = 4096
+            fg.world = small
+            if "plan" in cap and cap["plan"][0]:
+                with pytest.raises(fz.FusedPlanError):
+                    fg.validate_plan(*cap["plan"])
+            if cap["d"].get("push_n", 0):
+                with pytest.raises(fz.FusedPlanError):
+                    fg.validate_launch(cap["d"])
+            fg.world = FakeWorld(R * C, rank)
+            if "plan" in cap and cap["plan"][1] and cap["plan"][1][0][2]:
+                jobs, chunks = cap["plan"]
+                bad = [(chunks[0][0], chunks[0][1], [chunks[0][2][0] + 4 * 1000], chunks[0][3])] + list(chunks[1:])
+                with pytest.raises(fz.FusedPlanError):
+                    fg.validate_plan(jobs, bad)
+            if cap["d"].get("push_n", 0):
+                d = dict(cap["d"])
+                d["push_counter"] = [p + 4 for p in d["push_counter"]]
+                with pytest.raises(fz.FusedPlanError):
+                    fg.validate_launch(d)
