@@ -64,6 +64,35 @@ def _push_rotation(index: int, group: int, blocks_per_slice: int) -> int:
     return ((index + 1) % group) * (blocks_per_slice // group)
 
 
+def tile_schedule(d: dict):
+    """The order in which the fused kernel visits its 256 x 256 cluster tiles, as a list of
+    (m_block, n_block, slice): a host-side mirror of the kernel's tile map (slice-major, raster
+    groups of ``group`` blocks along the sliced dimension, block-cyclic slices of ``cyc`` blocks,
+    rotation ``rot`` inside a slice).  Cluster c of n runs tiles c, c + n, c + 2n, ...  Used by tests
+    and for reasoning about which chunk a tile waits for."""
+    tiles_m = (d["M"] + BM - 1) // BM
+    tiles_n = (d["N"] + BN - 1) // BN
+    sd, S = d.get("slice_dim", 0), d.get("n_slices", 1)
+    group, cyc, rot = max(1, d.get("group", 8)), max(1, d.get("cyc", 1)), d.get("rot", 0)
+    tiles_s, tiles_o = (tiles_m, tiles_n) if sd == 0 else (tiles_n, tiles_m)
+    nb = tiles_s // S
+    if rot < 0 or rot >= nb:
+        rot = 0
+    out = []
+    for t in range(tiles_m * tiles_n):
+        s_, r = divmod(t, nb * tiles_o)
+        g, rr = divmod(r, group * tiles_o)
+        g0 = g * group
+        o, w = divmod(rr, min(group, nb - g0))
+        jj = g0 + w + rot
+        if jj >= nb:
+            jj -= nb
+        cg = jj // cyc
+        blk = (cg * S + s_) * cyc + (jj - cg * cyc)
+        out.append((blk, o, s_) if sd == 0 else (o, blk, s_))
+    return out
+
+
 def pick_slices(n_blocks_per_part: int, want: int, cyc: int = 1) -> int:
     """Largest slice count <= want such that slices * cyc divides the blocks of every part."""
     s = max(1, min(want, n_blocks_per_part // cyc if cyc else 1))

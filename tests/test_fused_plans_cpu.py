@@ -279,3 +279,101 @@ def test_debug_validation_accepts_real_plans_and_rejects_corrupted_ones(mesh):
                 d["push_counter"] = [p + 4 for p in d["push_counter"]]
                 with pytest.raises(fz.FusedPlanError):
                     fg.validate_launch(d)
+
+
+@pytest.mark.parametrize("mesh", [(2, 4), (4, 2), (2, 2), (1, 4), (4, 1)])
+@pytest.mark.parametrize("slices", [1, 2, 4])
+def test_tile_order_matches_the_gather_chunks_and_the_arrival_targets(mesh, slices):
+    """The kernel's tile map (mirrored by fused.tile_schedule) against the plans: every tile is
+    visited once; a tile of slice s only reads gathered blocks that chunk s delivers; the number
+    of partial tiles an owner counts per slice equals the reduce target."""
+    R, C = mesh
+    BMc, BNc = 256, 256
+
+    def blocks_of_chunks(plan, stage_off, unit_bytes, block_units):
+        """{chunk index: set of block indices (in tile units) that the chunk writes at rank 0}"""
+        jobs, chunks = plan
+        lo = (1 << 40) + stage_off
+        out = {}
+        for ci, (jb, je, _sigs, _t) in enumerate(chunks):
+            got = set()
+            for sel, src, rows, rb, sp, dp, dsts in jobs[jb:je]:
+                for dptr in dsts:
+                    if lo <= dptr < lo + (1 << 33):
+                        if block_units == "rows":      # blocks of rows of `unit_bytes` each
+                            first, span = (dptr - lo) // unit_bytes, rows
+                        else:                          # blocks of bf16 columns inside a row of pitch dp
+                            first, span = ((dptr - lo) % dp) // 2, rb // 2
+                        got.update(range(first // 256, (first + span + 255) // 256))
+            out[ci] = got
+        return out
+
+    # ---- OS: X row blocks, sliced along M; chunk 0 carries W when it is gathered
+    m, Kd, n = 2048, 1024, 512
+    caps = _capture(R, C, lambda fg, mc: fg.os([10 ** 9] * C, [2 * 10 ** 9] * R, m, Kd // C, Kd // R, n, None,
+                                               n_slices=slices))
+    d = caps[0]["d"]
+    sched = fz.tile_schedule(d)
+    assert sorted((a, b) for a, b, _ in sched) == [(i, j) for i in range(m // BMc) for j in range(-(-n // BNc))]
+    if C > 1:
+        xbase = 1 if R > 1 else 0
+        # union over all source ranks of the row blocks that chunk xbase + s delivers to rank 0
+        per_chunk = {}
+        for cap in caps.values():
+            for ci, blks in blocks_of_chunks(cap["plan"], 1 << 20, Kd * 2, "rows").items():
+                if ci >= xbase:
+                    per_chunk.setdefault(ci - xbase, set()).update(blks)
+        for mb, nb_, s_ in sched:
+            assert mb in per_chunk[s_]
+
+    # ---- LS: output columns sliced, partial tiles pushed to C owners
+    mm, kl, nr = 512, 256, 1024 * C
+    N = nr * R
+    caps = _capture(R, C, lambda fg, mc: fg.ls(FakeT(5, kl), [3 * 10 ** 9] * R, mm, kl, nr, None, n_slices=slices))
+    for rank, cap in caps.items():
+        d = cap["d"]
+        sched = fz.tile_schedule(d)
+        assert len(set((a, b) for a, b, _ in sched)) == len(sched) == (mm // BMc) * (N // BNc)
+        if C > 1:
+            nc = N // C
+            counts = {}
+            for mb, nb_, s_ in sched:
+                owner = nb_ * BNc // nc
+                counts[(owner, s_)] = counts.get((owner, s_), 0) + 2 * 4     # two CTAs x four epilogue warps
+            # every owner gets the same number from every sender: target = C senders x that number
+            assert all(v * C == d["red_target"] for v in counts.values())
+            assert len(counts) == C * d["n_slices"]
+            # ranks of one mesh row start their slices at different owners
+            first_owner = sched[0][1] * BNc // nc
+            assert first_owner == ((rank % C) + 1) % C
+
+    # ---- RS: output rows sliced (cyclic blocks of cyc tiles), pushed to R owners
+    kr, ml, nn = 384, 512 * R, 512
+    caps = _capture(R, C, lambda fg, mc: fg.rs([7 * 10 ** 9] * C, FakeT(6, nn), kr, ml, nn, None, n_slices=slices, cyc=2))
+    M = ml * C
+    for rank, cap in caps.items():
+        d = cap["d"]
+        sched = fz.tile_schedule(d)
+        assert len(set((a, b) for a, b, _ in sched)) == len(sched) == (M // BMc) * (nn // BNc)
+        if C > 1:
+            per_chunk = {}
+            # X columns (= output row blocks) of slice s come with chunk s
+            for src_rank, cap2 in caps.items():
+                if src_rank // C != rank // C:
+                    continue      # only the ranks of this mesh row feed this rank's staging buffer
+                jobs, chunks = cap2["plan"]
+                lo = ((rank + 1) << 40) + (1 << 20)
+                for ci, (jb, je, _s, _t) in enumerate(chunks):
+                    for sel, src, rows, rb, sp, dp, dsts in jobs[jb:je]:
+                        for dptr in dsts:
+                            if lo <= dptr < lo + (1 << 33):
+                                col0 = ((dptr - lo) % dp) // 2
+                                per_chunk.setdefault(ci, set()).update(range(col0 // 256, (col0 + rb // 2) // 256))
+            for mb, nb_, s_ in sched:
+                assert mb in per_chunk[s_]
+        if R > 1:
+            mr = M // R
+            counts = {}
+            for mb, nb_, s_ in sched:
+                counts[(mb * BMc // mr, s_)] = counts.get((mb * BMc // mr, s_), 0) + 8
+            assert all(v * R == d["red_target"] for v in counts.values())
