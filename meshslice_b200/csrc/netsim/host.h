@@ -56,7 +56,6 @@ class HostMemory {
 
 struct HostParams {
   Time call_overhead = 100 * kNs;   // CPU time of one library call before it touches the NIC
-  Time copy_bw_inv_ps_per_byte = 0; // unused by the library itself; programs model memcpy with compute()
 };
 
 struct HostStats {

@@ -28,7 +28,7 @@ class FusedEngine:
     def __init__(self, mesh: DistMesh, stage_a_bytes: int, stage_b_bytes: int, slot_bytes: int,
                  send_bytes: int, extra_heap_bytes: int = 0, timeout_ns: int = 20_000_000_000):
         self.mesh = mesh
-        total = stage_a_bytes + stage_b_bytes + slot_bytes + 2 * send_bytes + extra_heap_bytes + (8 << 20)
+        total = stage_a_bytes + stage_b_bytes + slot_bytes + extra_heap_bytes + (8 << 20)   # send_bytes: unused
         self.heap = rt.SymmHeap(total, group=mesh.group)
         self.ws = rt.Workspace(self.heap, stage_a_bytes, stage_b_bytes, slot_bytes, send_bytes)
         self.world = rt.World.real(self.ws)

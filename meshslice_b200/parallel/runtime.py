@@ -97,13 +97,11 @@ class Workspace:
     stage_a_bytes: int
     stage_b_bytes: int
     slot_bytes: int
-    send_bytes: int = 0
+    send_bytes: int = 0            # unused since the gathers read their operands in place; kept for callers
     flags: int = 0
     stage_a: int = 0
     stage_b: int = 0
     slots: int = 0
-    send_a: int = 0
-    send_b: int = 0
     epoch: int = 0
     _jobs_cache: Dict = field(default_factory=dict)
 
@@ -114,8 +112,6 @@ class Workspace:
         self.stage_a = h.alloc(max(self.stage_a_bytes, 16))
         self.stage_b = h.alloc(max(self.stage_b_bytes, 16))
         self.slots = h.alloc(max(self.slot_bytes, 16))
-        self.send_a = h.alloc(max(self.send_bytes, 16))
-        self.send_b = h.alloc(max(self.send_bytes, 16))
         torch.cuda.synchronize()
 
     # pointers into this rank's or a peer's copy of the workspace
