@@ -20,3 +20,18 @@ def test_block_benchmark_runs_on_an_emulated_mesh(capsys):
     assert ShardedLayers.main(["meshflow", "--iters", "1"]) == 0
     out = capsys.readouterr().out
     assert "forward" in out and "mesh 2x2" in out
+
+
+def test_notebook_cells_execute():
+    """The CPU walkthrough notebook stays runnable: its code cells are executed in order."""
+    import json
+    import os
+    path = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "notebooks", "MeshSliceCPU.ipynb")
+    nb = json.load(open(path))
+    ns = {}
+    ran = 0
+    for cell in nb["cells"]:
+        if cell["cell_type"] == "code":
+            exec(compile("".join(cell["source"]), f"<cell {ran}>", "exec"), ns)
+            ran += 1
+    assert ran >= 4 and all(ns["agree"].values()) and all(ns["checks"].values())
