@@ -1,0 +1,54 @@
+"""Run logging, report tables and trace helpers (no GPU)."""
+import json
+
+import torch
+
+from meshslice_b200.utils import report
+from meshslice_b200.utils.logging import RunLogger, read_jsonl
+from meshslice_b200.utils.timing import annotate, trace
+
+
+def test_run_logger_writes_one_json_object_per_event(tmp_path, capsys):
+    path = tmp_path / "run.jsonl"
+    log = RunLogger(str(path), rank=0)
+    log.log("config", mesh="2x4", layers=4)
+    for s in range(3):
+        log.log("step", step=s + 1, loss=10.0 - s, ms=100.0 + s, tokens_per_s=1e5, tflops_per_gpu=700.0)
+    log.close()
+    recs = read_jsonl(str(path))
+    assert [r["kind"] for r in recs] == ["config", "step", "step", "step"] and recs[3]["loss"] == 8.0
+    assert "step:" in capsys.readouterr().err
+    silent = RunLogger(str(tmp_path / "other.jsonl"), rank=3)      # only rank 0 writes
+    silent.log("step", step=1)
+    assert not (tmp_path / "other.jsonl").exists()
+    table = report.steps_table(report.read_records([str(path)]))
+    assert table.count("\n") == 4 and "| 3 | 8.000 | 102.0 |" in table
+
+
+def test_scaling_table_from_benchmark_lines(tmp_path):
+    lines = []
+    for n, v in ((1, 1000.0), (2, 1800.0), (8, 5600.0)):
+        lines.append(json.dumps({"metric": "m", "value": v, "unit": "TFLOP/s", "n_gpus": n, "ms_per_step": 2700.0 / (v / 1000),
+                                 "impl": "meshslice_b200", "config": {"parallelism": f"mesh {n}"},
+                                 "clocks": {"sm_mhz": 1500.0, "reasons": ["sw_power_cap"]}, "e2e": {"value": v - 1}}))
+    f = tmp_path / "bench.log"
+    f.write_text("NCCL version 2.28\nnot json {\n" + "\n".join(lines) + "\n{broken json}\n")
+    recs = report.read_records([str(f)])
+    assert len(recs) == 3
+    table = report.scaling_table(recs)
+    rows = table.splitlines()
+    assert len(rows) == 5 and "| 0.70 |" in rows[4] and "| 0.90 |" in rows[3] and "sw_power_cap" in rows[2]
+    assert report.main([str(f)]) == 0
+
+
+def test_annotate_and_trace_work_without_a_gpu(tmp_path):
+    with annotate("forward"):
+        x = torch.ones(8) * 2
+    assert x.sum().item() == 16
+    with trace(None) as prof:
+        assert prof is None
+    out = tmp_path / "trace.json"
+    with trace(str(out)):
+        torch.ones(64, 64) @ torch.ones(64, 64)
+    data = json.loads(out.read_text())
+    assert "traceEvents" in data and len(data["traceEvents"]) > 0
