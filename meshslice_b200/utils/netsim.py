@@ -44,8 +44,14 @@ def build(force: bool = False) -> Path:
     cxx = os.environ.get("CXX") or shutil.which("g++") or shutil.which("c++")
     if cxx is None:
         raise NetsimError("no C++ compiler found (set CXX)")
-    cache = Path(os.environ.get("MSB_NETSIM_CACHE", Path(tempfile.gettempdir()) / "meshslice_b200_netsim"))
-    cache.mkdir(parents=True, exist_ok=True)
+    cache = Path(os.environ.get("MSB_NETSIM_CACHE", SRC_DIR / ".build"))
+    try:
+        cache.mkdir(parents=True, exist_ok=True)
+        if not os.access(cache, os.W_OK):
+            raise PermissionError(str(cache))
+    except OSError:      # read-only installation: fall back to the system's scratch directory
+        cache = Path(tempfile.gettempdir()) / "meshslice_b200_netsim"
+        cache.mkdir(parents=True, exist_ok=True)
     exe = cache / f"netsim-{_fingerprint()}"
     if exe.exists() and not force:
         return exe
