@@ -141,14 +141,21 @@ def fit_fabric(rows: int, cols: int, config: Optional[str] = None, topology: str
         sr = sweep("sendrecv", sizes, "exchange_us", nodes=n, topology=topo, config=config)
         a_ag, b_ag = _fit(ag)
         a_sr, b_sr = _fit(sr)
-        per_axis[axis] = dict(ag=(a_ag, (n - 1) / b_ag), sr=(a_sr, 1.0 / b_sr))
+        per_axis[axis] = dict(ag=(a_ag, (n - 1) / b_ag, n - 1), sr=(a_sr, 1.0 / b_sr, 1))
     if not per_axis:
         raise NetsimError("a 1 x 1 mesh has no fabric to fit")
     first = next(iter(per_axis.values()))
+    ring = not topology.startswith("crossbar")
     for kind, key in (("allgather", "ag"), ("reducescatter", "ag"), ("sendrecv", "sr")):
-        a0 = min(v[key][0] for v in per_axis.values())
-        lat[kind] = min(a0 / 2, 5e-6)
-        base[kind] = max(a0 - lat[kind], 0.0)
+        if ring:
+            # a ring collective pays the per-step latency once per forwarding step: split the
+            # small-message time of every axis by its step count
+            lat[kind] = min(v[key][0] / v[key][2] for v in per_axis.values())
+            base[kind] = max(0.0, min(v[key][0] - lat[kind] * v[key][2] for v in per_axis.values()))
+        else:
+            a0 = min(v[key][0] for v in per_axis.values())
+            lat[kind] = min(a0 / 2, 5e-6)
+            base[kind] = max(a0 - lat[kind], 0.0)
         bws[kind] = [per_axis.get("rows", first)[key][1], per_axis.get("cols", first)[key][1]]
     return dict(latencies=lat, bws=bws, base_overheads=base,
                 fabric="switch" if topology.startswith("crossbar") else "ring",
