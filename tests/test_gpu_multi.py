@@ -22,10 +22,10 @@ def _run_worker(nproc, mesh, slices, port):
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
 def test_fused_dataflows_on_two_gpus():
-    _run_worker(2, "1x2", 2, 29711)
-    _run_worker(2, "2x1", 2, 29712)
+    _run_worker(2, "1x2", 2, 29731)
+    _run_worker(2, "2x1", 2, 29732)
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 4, reason="needs four GPUs")
 def test_fused_dataflows_on_a_2x2_mesh():
-    _run_worker(4, "2x2", 2, 29713)
+    _run_worker(4, "2x2", 2, 29733)
