@@ -55,7 +55,9 @@ def _stale(target: Path, deps) -> bool:
 
 
 def _headers():
-    return [str(p) for p in CSRC.rglob("*.h")] + [str(p) for p in CSRC.rglob("*.cuh")]
+    """Headers the CUDA / binding sources may include (the stand-alone simulator has its own build)."""
+    hs = list(CSRC.rglob("*.h")) + list(CSRC.rglob("*.cuh"))
+    return [str(p) for p in hs if "netsim" not in p.parts]
 
 
 def _run(cmd):
