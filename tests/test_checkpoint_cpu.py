@@ -82,3 +82,21 @@ def test_import_blocks_exported_per_device_coordinate(tmp_path):
     assert len(loaded) == 2
     assert torch.equal(mesh.unshard(model.blocks[0].in_proj.weight), W)
     assert torch.equal(model.blocks[0].ln1.gamma.shards[(1, 1)], g[32:])
+
+
+@pytest.mark.parametrize("chain", [[(1, 1), (2, 2), (4, 1), (1, 2)], [(2, 1), (1, 4), (2, 2), (1, 1)]])
+def test_reshard_chains_preserve_every_parameter(tmp_path, chain):
+    """Re-sharding through a chain of mesh shapes and back gives bit-identical global parameters."""
+    first = GPTModel(EmuMesh(*chain[0]), CFG)
+    save_checkpoint(str(tmp_path / "s0"), 7, first)
+    prev = str(tmp_path / "s0")
+    for i, shape in enumerate(chain[1:], 1):
+        out = str(tmp_path / f"s{i}")
+        reshard_checkpoint(prev, 7, shape, out)
+        prev = out
+    mesh = EmuMesh(*chain[-1])
+    last = GPTModel(mesh, dataclasses.replace(CFG, init_std=0.3))
+    meta = load_checkpoint(prev, 7, last)
+    assert meta["step"] == 7 and meta["mesh"] == list(chain[-1])
+    for (n, p, _, k), (_, q, _, _) in zip(first.parameters(), last.parameters()):
+        assert torch.equal(_full(first.mesh, p, k), _full(mesh, q, k)), n
