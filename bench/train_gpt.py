@@ -37,6 +37,8 @@ def main():
     p.add_argument("--ckpt-dir", default="")
     p.add_argument("--ckpt-every", type=int, default=0)
     p.add_argument("--resume-step", type=int, default=-1)
+    p.add_argument("--peer-timeout", type=float, default=60.0,
+                   help="seconds a rank waits for its peers' heartbeat before a step")
     p.add_argument("--trace", default="", help="write a Chrome trace of the last step here (rank 0)")
     a = p.parse_args()
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -73,19 +75,32 @@ def main():
         load_checkpoint(a.ckpt_dir, a.resume_step, tr.model, tr.opt)
         start = a.resume_step
         log.log("resume", step=start)
-    g = torch.Generator().manual_seed(1234)
+    hb = None
+    if world > 1:
+        # between steps every rank publishes its step counter in the job's store and looks at its
+        # peers' entries, so a rank that left or raised is reported before the next fused launch
+        from torch.distributed.distributed_c10d import _get_default_store
+        from meshslice_b200.utils.health import Heartbeat, guarded_step
+        hb = Heartbeat(_get_default_store(), rank, world)
     for step in range(start, a.steps):
+        # the batch of step k depends on k only, so a resumed run continues the same data stream
+        g = torch.Generator().manual_seed(1234 + step)
         ids = torch.randint(0, cfg.vocab, (a.batchsize, cfg.seq + 1), generator=g)
         ids = tr.rows_of_global_batch(ids).contiguous().pin_memory()
         last = step == a.steps - 1
         with trace(a.trace if (last and rank == 0) else None), annotate("train_step"), DeviceTimer() as t:
-            loss = tr.train_step(ids)
-        tr.check()
+            if hb is not None:
+                loss = guarded_step(hb, step + 1, lambda: tr.train_step(ids), timeout_s=a.peer_timeout)
+            else:
+                loss = tr.train_step(ids)
+        tr.check(all_ranks=True)      # a kernel error of any rank raises on every rank
         log.log("step", step=step + 1, loss=loss, ms=t.ms, tokens_per_s=tr.n_tokens / (t.ms * 1e-3),
                 tflops_per_gpu=tr.tflops(t.ms) / world,
                 grad_norm=float(tr.opt.last_grad_norm) if tr.opt.last_grad_norm is not None else -1.0)
         if a.ckpt_dir and a.ckpt_every and (step + 1) % a.ckpt_every == 0:
-            save_checkpoint(a.ckpt_dir, step + 1, tr.model, tr.opt, rank0=rank == 0)
+            save_checkpoint(a.ckpt_dir, step + 1, tr.model, tr.opt, rank0=rank == 0,
+                            extra={"data_seed": 1234, "next_step": step + 1},
+                            barrier=dist.barrier if world > 1 else None)
             log.log("checkpoint", step=step + 1)
     log.close()
     if world > 1:

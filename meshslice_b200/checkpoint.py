@@ -11,9 +11,16 @@ coordinate, which this format keeps (ShardedLayers.py:33-36, 93-100, 152-153):
 * LayerNorm / embedding parameters are P(None, col): coordinate (r, c) holds columns
   ``[c*n/C:(c+1)*n/C]`` and every row index holds the same values.
 
-Layout on disk: ``<dir>/step_<N>/shard_r<r>_c<c>.pt`` = {name: local block} (+ optimizer state
-under 'optim/...' with the same sharding) and ``<dir>/step_<N>/meta.json`` (mesh, per-parameter
-global shape / kind / dataflow / dtype, step, RNG state presence).
+Layout on disk: ``<dir>/step_<N>/shard_r<r>_c<c>.pt`` = {name: local block} plus, when an
+optimizer is saved, ``optim/master/<name>``, ``optim/m/<name>``, ``optim/v/<name>`` (fp32, same
+block as the parameter, so the optimizer state re-shards with the parameters) and
+``optim/step``; ``<dir>/step_<N>/meta.json`` (mesh, per-parameter global shape / kind / dataflow /
+dtype, step, whether optimizer state is present, caller's ``extra`` such as the data position).
+meta.json is written last, through a temporary file and an atomic rename: a step directory
+without it is an interrupted save.
+
+Loading parameters without optimizer state (an older checkpoint, imported weights) rebuilds the
+optimizer's fp32 master copies from the loaded parameters and clears the moments.
 """
 from __future__ import annotations
 
@@ -38,21 +45,31 @@ def _global_shape(local_shape, kind: str, R: int, C: int):
     return s
 
 
-def save_checkpoint(root: str, step: int, model, optimizer=None, extra: Optional[dict] = None, rank0: bool = True):
-    """Every process writes the coordinates it holds; the process with ``rank0`` writes meta.json."""
+_OPT_KEYS = ("master", "m", "v")
+
+
+def save_checkpoint(root: str, step: int, model, optimizer=None, extra: Optional[dict] = None, rank0: bool = True,
+                    barrier=None):
+    """Every process writes the coordinates it holds; the process with ``rank0`` writes meta.json
+    after ``barrier()`` (when given: a callable that returns once every process has written its
+    shard files, e.g. ``torch.distributed.barrier``)."""
     mesh: Mesh = model.mesh
     d = _step_dir(root, step)
     os.makedirs(d, exist_ok=True)
     params = model.parameters()
+    named = optimizer.named_state(params) if optimizer is not None else None
     for (r, c) in mesh.coords():
         blob = {name: p.shards[(r, c)].detach().cpu() for name, p, _, _ in params}
         if optimizer is not None:
-            sd = optimizer.state_dict()
-            blob["optim/step"] = torch.tensor(sd["step"])
-            for i, g in enumerate(sd["groups"]):
-                for k in ("master", "m", "v"):
-                    blob[f"optim/{i}/{k}"] = g[k].detach().cpu()
-        torch.save(blob, os.path.join(d, f"shard_r{r}_c{c}.pt"))
+            blob["optim/step"] = torch.tensor(optimizer.step_count)
+            for name, per in named.items():
+                for k, view in zip(_OPT_KEYS, per[(r, c)]):
+                    blob[f"optim/{k}/{name}"] = view.detach().cpu().clone()
+        tmp = os.path.join(d, f".shard_r{r}_c{c}.pt.tmp")
+        torch.save(blob, tmp)
+        os.replace(tmp, os.path.join(d, f"shard_r{r}_c{c}.pt"))
+    if barrier is not None:
+        barrier()
     if rank0:
         meta = {"format": "meshslice_b200.ckpt.v1", "mesh": [mesh.R, mesh.C], "step": step,
                 "has_optimizer": optimizer is not None, "extra": extra or {}, "params": {}}
@@ -70,8 +87,17 @@ def save_checkpoint(root: str, step: int, model, optimizer=None, extra: Optional
                                     "dataflow": dataflows.get(name),
                                     "orientation": "[out,in]" if dataflows.get(name) == "ls" else "[in,out]"
                                     if name in dataflows else None}
-        json.dump(meta, open(os.path.join(d, "meta.json"), "w"), indent=1)
+        _write_json_atomic(os.path.join(d, "meta.json"), meta)
     return d
+
+
+def _write_json_atomic(path: str, obj):
+    tmp = path + ".tmp"
+    with open(tmp, "w") as f:
+        json.dump(obj, f, indent=1)
+        f.flush()
+        os.fsync(f.fileno())
+    os.replace(tmp, path)
 
 
 def load_checkpoint(root: str, step: int, model, optimizer=None) -> dict:
@@ -83,6 +109,8 @@ def load_checkpoint(root: str, step: int, model, optimizer=None) -> dict:
     if meta["mesh"] != [mesh.R, mesh.C]:
         raise ValueError(f"checkpoint mesh {meta['mesh']} != model mesh {[mesh.R, mesh.C]}; re-shard it first")
     params = model.parameters()
+    with_opt = optimizer is not None and bool(meta.get("has_optimizer"))
+    named = optimizer.named_state(params) if with_opt else None
     for (r, c) in mesh.coords():
         path = os.path.join(d, f"shard_r{r}_c{c}.pt")
         if not os.path.exists(path):
@@ -98,11 +126,18 @@ def load_checkpoint(root: str, step: int, model, optimizer=None) -> dict:
             if tuple(blob[name].shape) != tuple(t.shape):
                 raise ValueError(f"{name}: shard shape {tuple(blob[name].shape)} != {tuple(t.shape)}")
             t.copy_(blob[name].to(t.dtype))
-        if optimizer is not None and meta.get("has_optimizer"):
-            groups = []
-            for i, g in enumerate(optimizer.groups):
-                groups.append({k: blob[f"optim/{i}/{k}"] for k in ("master", "m", "v")})
-            optimizer.load_state_dict({"step": int(blob["optim/step"]), "groups": groups})
+        if with_opt:
+            optimizer.step_count = int(blob["optim/step"])
+            for name, per in named.items():
+                for k, view in zip(_OPT_KEYS, per[(r, c)]):
+                    key = f"optim/{k}/{name}"
+                    if key not in blob:
+                        raise KeyError(f"{path} has no optimizer state {key}")
+                    view.copy_(blob[key].to(view.dtype))
+    if optimizer is not None and not with_opt:
+        # no optimizer state on disk: without this the first step would write the stale fp32
+        # master copies (the construction-time weights) over the parameters just loaded
+        optimizer.resync_from_params(step=int(meta.get("step", 0)))
     return meta
 
 
@@ -121,8 +156,9 @@ def _split(full: torch.Tensor, kind: str, R: int, C: int, r: int, c: int) -> tor
 
 
 def reshard_checkpoint(root: str, step: int, new_mesh: Tuple[int, int], out_root: str) -> str:
-    """Offline R x C -> R' x C' conversion of the parameters (optimizer state is not carried:
-    its flat layout depends on the mesh; a resumed run rebuilds it from the parameters)."""
+    """Offline R x C -> R' x C' conversion of the parameters and, when present, of the optimizer
+    state (fp32 master copies and both moments are stored per parameter with the parameter's own
+    sharding, so they are cut the same way)."""
     d = _step_dir(root, step)
     meta = json.load(open(os.path.join(d, "meta.json")))
     R, C = meta["mesh"]
@@ -131,25 +167,33 @@ def reshard_checkpoint(root: str, step: int, new_mesh: Tuple[int, int], out_root
              for r in range(R) for c in range(C)}
     out = _step_dir(out_root, step)
     os.makedirs(out, exist_ok=True)
-    fulls = {n: _assemble(blobs, n, info["kind"], R, C) for n, info in meta["params"].items()}
+    kinds = {n: info["kind"] for n, info in meta["params"].items()}
+    has_opt = bool(meta.get("has_optimizer"))
+    if has_opt:
+        for n, info in meta["params"].items():
+            for k in _OPT_KEYS:
+                kinds[f"optim/{k}/{n}"] = info["kind"]
+    fulls = {n: _assemble(blobs, n, kind, R, C) for n, kind in kinds.items()}
     for n, f in fulls.items():
-        k = meta["params"][n]["kind"]
+        k = kinds[n]
         if (k == "sharded" and (f.shape[0] % R2 or f.shape[1] % C2)) or (k != "sharded" and f.shape[-1] % C2):
             raise ValueError(f"{n} with global shape {tuple(f.shape)} does not divide over mesh {new_mesh}")
     for r in range(R2):
         for c in range(C2):
-            torch.save({n: _split(f, meta["params"][n]["kind"], R2, C2, r, c) for n, f in fulls.items()},
-                       os.path.join(out, f"shard_r{r}_c{c}.pt"))
-    meta2 = dict(meta, mesh=[R2, C2], has_optimizer=False)
-    json.dump(meta2, open(os.path.join(out, "meta.json"), "w"), indent=1)
+            blob = {n: _split(f, kinds[n], R2, C2, r, c) for n, f in fulls.items()}
+            if has_opt:
+                blob["optim/step"] = blobs[(0, 0)]["optim/step"].clone()
+            torch.save(blob, os.path.join(out, f"shard_r{r}_c{c}.pt"))
+    _write_json_atomic(os.path.join(out, "meta.json"), dict(meta, mesh=[R2, C2]))
     return out
 
 
-def import_jax_blocks(block_dir: str, model, name_map: Dict[str, str]) -> List[str]:
+def import_jax_blocks(block_dir: str, model, name_map: Dict[str, str], optimizer=None) -> List[str]:
     """Loads a pytree exported from the JAX reference as per-device ``.npy`` blocks named
     ``<param>.r<r>.c<c>.npy`` (one file per NamedSharding(mesh, P(row, col)) shard, or
     ``<param>.c<c>.npy`` for P(col) vectors).  ``name_map`` maps this model's parameter names to
-    the exported names.  Returns the parameters that were loaded."""
+    the exported names.  With ``optimizer`` its fp32 master copies are rebuilt from the imported
+    parameters.  Returns the parameters that were loaded."""
     import numpy as np
     mesh: Mesh = model.mesh
     loaded = []
@@ -167,4 +211,6 @@ def import_jax_blocks(block_dir: str, model, name_map: Dict[str, str]) -> List[s
                 raise ValueError(f"{fn}: block shape {tuple(arr.shape)} != {tuple(t.shape)}")
             t.copy_(arr.to(t.dtype))
         loaded.append(name)
+    if optimizer is not None:
+        optimizer.resync_from_params(step=0)
     return loaded

@@ -21,6 +21,7 @@ import torch
 
 from ..ops import functional as F
 from ..parallel.mesh import Mesh, ShardedTensor
+from ..parallel.tensor_parallel import init_block
 from .sharded_layers import GeLU, ShardedAttention, ShardedFFLayer, ShardedLayerNorm, _add
 
 # GeLU inside the ff1 GEMM epilogue (MSB_FUSED_GELU=0 runs the stand-alone kernel instead)
@@ -120,19 +121,21 @@ class GPTModel:
             raise ValueError("model width / heads / vocabulary must divide over the mesh columns")
         d, C = cfg.d_model, mesh.C
         a_rep = alloc_rep or (lambda shape, dtype, dev: torch.empty(shape, dtype=dtype, device=dev))
-        self.tok = ShardedTensor(mesh, {})
-        self.pos = ShardedTensor(mesh, {})
-        for (r, c) in mesh.coords():
-            g = torch.Generator().manual_seed(900001 + c)      # same along a mesh column
-            t = a_rep((cfg.vocab_padded, d // C), cfg.dtype, device)
-            t.copy_((torch.randn(cfg.vocab_padded, d // C, generator=g) * cfg.init_std).to(cfg.dtype))
-            p = a_rep((cfg.seq, d // C), cfg.dtype, device)
-            p.copy_((torch.randn(cfg.seq, d // C, generator=g) * cfg.init_std).to(cfg.dtype))
-            self.tok.shards[(r, c)], self.pos.shards[(r, c)] = t, p
         g_rep = grad_rep or (lambda shape, dtype, dev: torch.empty(shape, dtype=dtype, device=dev))
-        z32 = lambda shape: ShardedTensor(mesh, {k: g_rep(shape, torch.float32, device).zero_()
-                                                 for k in mesh.coords()})
-        self.dtok, self.dpos = z32((cfg.vocab_padded, d // C)), z32((cfg.seq, d // C))
+        self.tok, self.pos = ShardedTensor(mesh, {}), ShardedTensor(mesh, {})
+        self.dtok, self.dpos = ShardedTensor(mesh, {}), ShardedTensor(mesh, {})
+        # parameters and their gradients are carved in the same order, so a parameter and its
+        # gradient sit at the same offset of the flat parameter / gradient buffers
+        for (r, c) in mesh.coords():
+            t = a_rep((cfg.vocab_padded, d // C), cfg.dtype, device)
+            t.copy_(init_block((cfg.vocab_padded, d), cfg.init_std, 900001, 0, cfg.vocab_padded,
+                               c * (d // C), (c + 1) * (d // C), device=device).to(cfg.dtype))
+            p = a_rep((cfg.seq, d // C), cfg.dtype, device)
+            p.copy_(init_block((cfg.seq, d), cfg.init_std, 900002, 0, cfg.seq,
+                               c * (d // C), (c + 1) * (d // C), device=device).to(cfg.dtype))
+            self.tok.shards[(r, c)], self.pos.shards[(r, c)] = t, p
+            self.dtok.shards[(r, c)] = g_rep((cfg.vocab_padded, d // C), torch.float32, device).zero_()
+            self.dpos.shards[(r, c)] = g_rep((cfg.seq, d // C), torch.float32, device).zero_()
         self.blocks = [GPTBlock(mesh, cfg, i, device, alloc_sharded, alloc_rep, grad_sharded, grad_rep)
                        for i in range(cfg.n_layers)]
         self.ln_f = ShardedLayerNorm(mesh, d, affine=True, eps=cfg.eps, dtype=cfg.dtype, device=device, alloc=alloc_rep,

@@ -86,6 +86,44 @@ class AdamW:
         for g in self.groups:
             g.grad.zero_()
 
+    def resync_from_params(self, step: int = 0):
+        """Rebuild the optimizer state from the current bf16 parameters: the fp32 master copies
+        become the parameters, both moments are cleared and the step counter is set.  Needed after
+        parameters were written behind the optimizer's back (a checkpoint without optimizer
+        state, imported weights); otherwise the next step would overwrite them from the stale
+        master copies."""
+        self.step_count = int(step)
+        for g in self.groups:
+            g.master.copy_(g.param.float())
+            g.m.zero_()
+            g.v.zero_()
+
+    def named_state(self, params):
+        """Views of the flat master / m / v buffers per named parameter shard.
+
+        ``params`` is ``model.parameters()``.  Returns {name: {coord: (master, m, v)}} where each
+        view has the shape of the parameter shard; a parameter that does not live inside one of
+        this optimizer's flat buffers is an error.  This is what makes the optimizer state
+        save-able and re-shardable with the same rules as the parameters themselves."""
+        out = {}
+        spans = [(g, g.param.data_ptr(), g.param.data_ptr() + g.param.numel() * g.param.element_size())
+                 for g in self.groups]
+        for name, p, _, _ in params:
+            per = {}
+            for key, t in p.shards.items():
+                for g, lo, hi in spans:
+                    if lo <= t.data_ptr() < hi:
+                        if not t.is_contiguous():
+                            raise ValueError(f"{name}: parameter shard is not contiguous in its flat buffer")
+                        off = (t.data_ptr() - lo) // g.param.element_size()
+                        n = t.numel()
+                        per[key] = tuple(b[off:off + n].view(t.shape) for b in (g.master, g.m, g.v))
+                        break
+                else:
+                    raise ValueError(f"{name}: parameter shard {key} is outside the optimizer's flat buffers")
+            out[name] = per
+        return out
+
     def state_dict(self):
         return {"step": self.step_count,
                 "groups": [{"master": g.master, "m": g.m, "v": g.v, "kind": g.kind} for g in self.groups]}

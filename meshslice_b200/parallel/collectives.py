@@ -17,6 +17,33 @@ from . import runtime as rt
 from .mesh import DistMesh
 
 
+def validate_copy_jobs(jobs) -> None:
+    """The copy kernel moves whole 16-byte vectors: a job whose row size, pitches or base
+    addresses are not multiples of 16 would silently drop the tail of every row or fault on a
+    misaligned vector access.  Raises ValueError before anything is launched."""
+    for i, (src, dst, rows, row_bytes, sp, dp) in enumerate(jobs):
+        if rows <= 0 or row_bytes <= 0:
+            raise ValueError(f"copy job {i}: empty ({rows} rows of {row_bytes} bytes)")
+        for what, v in (("row size", row_bytes), ("source pitch", sp), ("destination pitch", dp),
+                        ("source address", src), ("destination address", dst)):
+            if v % 16:
+                raise ValueError(f"copy job {i}: {what} {v} is not a multiple of 16 bytes "
+                                 f"(bf16 rows must hold a multiple of 8 elements)")
+        if sp < row_bytes or dp < row_bytes:
+            raise ValueError(f"copy job {i}: pitch smaller than the row ({sp}/{dp} < {row_bytes})")
+
+
+def validate_reduce(srcs, src_cols: int, out_ptr: int, out_pitch: int, rows: int, cols: int) -> None:
+    """Same rule for the reduce kernel (8 bf16 per vector)."""
+    if rows <= 0 or cols <= 0 or cols % 8 or src_cols % 8 or out_pitch % 8:
+        raise ValueError(f"reduce: {rows} x {cols} (pitches {src_cols}/{out_pitch}) must be multiples of 8 bf16")
+    if not 0 < len(srcs) <= 8:
+        raise ValueError(f"reduce: {len(srcs)} sources")
+    for p in list(srcs) + [out_ptr]:
+        if p % 16:
+            raise ValueError("reduce: buffer not 16-byte aligned")
+
+
 class P2PCollectives:
     def __init__(self, mesh: DistMesh, heap: rt.SymmHeap, max_bytes: int, grid: int = 148, timeout_ns: int = 10_000_000_000):
         self.mesh, self.heap, self.grid, self.timeout_ns = mesh, heap, grid, timeout_ns
@@ -49,6 +76,7 @@ class P2PCollectives:
         return [m.r * m.C + c for c in range(m.C)] if axis == "col" else [r * m.C + m.c for r in range(m.R)]
 
     def _copy(self, jobs):
+        validate_copy_jobs(jobs)
         jt, _ = rt.upload_jobs(jobs, [0, len(jobs)], torch.device("cuda", torch.cuda.current_device()))
         self.C.p2p_copy(jt.data_ptr(), len(jobs), self._bar(self.grid), self.grid, _native.stream_ptr())
         return jt
@@ -99,7 +127,10 @@ class P2PCollectives:
             off = i * c_ * 2
         if out is None:
             out = torch.empty(r_, c_, dtype=torch.bfloat16, device="cuda")
+        if rows % (n if dim == 0 else 1) or cols % (1 if dim == 0 else n):
+            raise ValueError(f"reduce_scatter: {rows} x {cols} does not split {n} ways on dim {dim}")
         srcs = [self.heap.ptr(q, self.inp_off) + off for q in peers]
+        validate_reduce(srcs, cols, out.data_ptr(), c_, r_, c_)
         self.C.p2p_reduce(srcs, cols, out.data_ptr(), c_, r_, c_, self._bar(self.grid), self.grid,
                           _native.stream_ptr())
         return out

@@ -395,20 +395,46 @@ class SPMD:
         return self._build("rs", K)
 
 
+INIT_TILE = 256      # edge of the square tiles that random initial values are drawn in
+
+
+def init_block(global_shape, std: float, seed: int, r0: int, r1: int, c0: int, c1: int, device=None) -> torch.Tensor:
+    """Rows [r0, r1) x columns [c0, c1) of a virtual global N(0, std) fp32 matrix of ``global_shape``.
+
+    The global matrix is defined tile by tile: tile (i, j) of INIT_TILE x INIT_TILE elements is
+    drawn from its own generator, seeded by (seed, i, j).  A block is assembled from the tiles it
+    touches, so its values do not depend on how the matrix is cut: every mesh shape initialises
+    the same model, and no rank ever materialises more than its own block (plus tile borders)."""
+    d0, d1 = global_shape
+    on_gpu = device is not None and torch.device(device).type == "cuda"
+    dev = device if on_gpu else "cpu"
+    out = torch.empty(r1 - r0, c1 - c0, dtype=torch.float32, device=dev)
+    T = INIT_TILE
+    g = torch.Generator(device=dev)
+    tiles_j = (d1 + T - 1) // T
+    for i in range(r0 // T, (r1 - 1) // T + 1):
+        for j in range(c0 // T, (c1 - 1) // T + 1):
+            g.manual_seed((seed * 1000003 + i * tiles_j + j) * 2654435761 % (1 << 62))
+            tile = torch.randn(T, T, generator=g, device=dev, dtype=torch.float32)
+            a0, a1 = max(r0, i * T), min(r1, (i + 1) * T)
+            b0, b1 = max(c0, j * T), min(c1, (j + 1) * T)
+            out[a0 - r0:a1 - r0, b0 - c0:b1 - c0] = tile[a0 - i * T:a1 - i * T, b0 - j * T:b1 - j * T]
+    if std != 1.0:
+        out *= std
+    return out
+
+
 def createMultihostMatrix(mesh: Mesh, global_shape, dtype=torch.bfloat16, seed: int = 0, device=None,
                           std: float = 1.0) -> ShardedTensor:
-    """Random N(0, std) matrix block-sharded P(row, col) (TensorParallel.py:419-423).  Every
-    shard is drawn from its own seed, so no rank ever materialises the global matrix."""
+    """Random N(0, std) matrix block-sharded P(row, col) (TensorParallel.py:419-423).  No rank
+    materialises the global matrix, and (unlike the reference, which seeds by process index)
+    the global values do not depend on the mesh shape: see ``init_block``."""
     d0, d1 = global_shape
     if d0 % mesh.R or d1 % mesh.C:
         raise ValueError(f"shape {tuple(global_shape)} not divisible by mesh {mesh.shape}")
+    b0, b1 = d0 // mesh.R, d1 // mesh.C
     shards = {}
     for (r, c) in mesh.coords():
-        on_gpu = device is not None and torch.device(device).type == "cuda"
-        g = torch.Generator(device=device if on_gpu else "cpu").manual_seed(seed * 1000003 + r * mesh.C + c)
-        t = torch.randn(d0 // mesh.R, d1 // mesh.C, generator=g, device=device if on_gpu else None,
-                        dtype=torch.float32 if not on_gpu else dtype)
-        if std != 1.0:
-            t = t * std
+        t = init_block(global_shape, std, seed, r * b0, (r + 1) * b0, c * b1, (c + 1) * b1, device=device)
         shards[(r, c)] = t.to(dtype).to(device) if device is not None else t.to(dtype)
     return ShardedTensor(mesh, shards)

@@ -24,6 +24,17 @@ class Heartbeat:
     def _key(self, r):
         return f"{self.prefix}/{r}"
 
+    def _peek(self, key: str) -> str:
+        """Value of ``key`` or "" when nobody has set it yet.  ``store.get`` blocks until the key
+        exists (for the store's own timeout, minutes by default), which would stall every survivor
+        behind a peer that died before its first beat; ``check`` asks without blocking first."""
+        try:
+            if hasattr(self.store, "check") and not self.store.check([key]):
+                return ""
+            return self.store.get(key).decode()
+        except Exception:
+            return ""
+
     def beat(self, step: int):
         self.store.set(self._key(self.rank), f"step:{step}")
 
@@ -39,10 +50,7 @@ class Heartbeat:
             if r == self.rank:
                 continue
             while True:
-                try:
-                    v = self.store.get(self._key(r)).decode()
-                except Exception:
-                    v = ""
+                v = self._peek(self._key(r))
                 if v.startswith("gone:"):
                     raise PeerLostError(f"rank {r} left the job ({v[5:]}) before step {step}")
                 if v.startswith("step:") and int(v[5:]) >= step:

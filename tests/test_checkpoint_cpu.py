@@ -100,3 +100,116 @@ def test_reshard_chains_preserve_every_parameter(tmp_path, chain):
     assert meta["step"] == 7 and meta["mesh"] == list(chain[-1])
     for (n, p, _, k), (_, q, _, _) in zip(first.parameters(), last.parameters()):
         assert torch.equal(_full(first.mesh, p, k), _full(mesh, q, k)), n
+
+
+# ---------------------------------------------------------------------------------------------
+# optimizer state: save / resume / re-shard
+# ---------------------------------------------------------------------------------------------
+from meshslice_b200.optim import AdamW, FlatGroup
+from meshslice_b200.parallel.mesh import ShardedTensor
+from meshslice_b200.trainer import Arena, param_elems
+
+
+def _flat_model(shape, cfg=CFG, init_std=None):
+    """GPT model of an emulated mesh on flat parameter / gradient buffers with AdamW, the way the
+    trainer lays one rank out (here all coordinates share the buffers)."""
+    R, C = shape
+    mesh = EmuMesh(R, C)
+    n_sh, n_rep = param_elems(cfg, R, C)
+    n_sh, n_rep = n_sh * R * C, n_rep * R * C
+    p_sh, g_sh = torch.zeros(n_sh), torch.zeros(n_sh)
+    p_rep, g_rep = torch.zeros(n_rep), torch.zeros(n_rep)
+    a = [Arena(t) for t in (p_sh, g_sh, p_rep, g_rep)]
+    c = cfg if init_std is None else dataclasses.replace(cfg, init_std=init_std)
+    model = GPTModel(mesh, c, alloc_sharded=a[0].alloc, alloc_rep=a[2].alloc, grad_sharded=a[1].alloc,
+                     grad_rep=a[3].alloc)
+    opt = AdamW([FlatGroup(p_sh, g_sh, "sharded"), FlatGroup(p_rep, g_rep, "row_replicated")], lr=1e-2,
+                max_grad_norm=None)
+    return mesh, model, opt
+
+
+def _step(mesh, model, opt, step):
+    B = 4
+    ids = torch.randint(0, CFG.vocab, (B, CFG.seq + 1), generator=torch.Generator().manual_seed(100 + step))
+    per = B // mesh.R
+    tok = ShardedTensor(mesh, {(r, c): ids[r * per:(r + 1) * per, :-1].reshape(-1) for (r, c) in mesh.coords()})
+    tgt = ShardedTensor(mesh, {(r, c): ids[r * per:(r + 1) * per, 1:].reshape(-1) for (r, c) in mesh.coords()})
+    loss = model.forward_backward(tok, tgt, B * CFG.seq)
+    model.sync_replicated_grads()
+    opt.step()
+    opt.zero_grad()
+    return sum(loss.shards[(r, 0)] for r in range(mesh.R)).item()
+
+
+def _globals(mesh, model):
+    return {n: _full(mesh, p, k).clone() for n, p, _, k in model.parameters()}
+
+
+def test_resume_with_optimizer_state_reproduces_the_uninterrupted_run_bit_for_bit(tmp_path):
+    mesh, model, opt = _flat_model((2, 2))
+    losses = [_step(mesh, model, opt, s) for s in range(2)]
+    save_checkpoint(str(tmp_path), 2, model, opt)
+    losses += [_step(mesh, model, opt, s) for s in range(2, 4)]
+    want = _globals(mesh, model)
+    # a fresh process: different initial weights, then resume at step 2
+    mesh2, model2, opt2 = _flat_model((2, 2), init_std=0.3)
+    meta = load_checkpoint(str(tmp_path), 2, model2, opt2)
+    assert meta["has_optimizer"] and opt2.step_count == 2
+    resumed = [_step(mesh2, model2, opt2, s) for s in range(2, 4)]
+    assert resumed == losses[2:]
+    got = _globals(mesh2, model2)
+    for n in want:
+        assert torch.equal(want[n], got[n]), n
+
+
+def test_reshard_carries_optimizer_state_and_the_next_step_is_the_adamw_update(tmp_path):
+    mesh, model, opt = _flat_model((2, 2))
+    for s in range(2):
+        _step(mesh, model, opt, s)
+    save_checkpoint(str(tmp_path / "a"), 2, model, opt)
+    loaded = _globals(mesh, model)
+    _step(mesh, model, opt, 2)
+    want = _globals(mesh, model)
+    reshard_checkpoint(str(tmp_path / "a"), 2, (1, 4), str(tmp_path / "b"))
+    mesh2, model2, opt2 = _flat_model((1, 4), init_std=0.3)
+    meta = load_checkpoint(str(tmp_path / "b"), 2, model2, opt2)
+    assert meta["has_optimizer"] and meta["mesh"] == [1, 4] and opt2.step_count == 2
+    for n, t in _globals(mesh2, model2).items():
+        assert torch.equal(t, loaded[n]), n
+    # moments travelled too: the next step on 1x4 is the step the 2x2 run took
+    _step(mesh2, model2, opt2, 2)
+    got = _globals(mesh2, model2)
+    for n in want:
+        assert torch.allclose(want[n], got[n], atol=2e-5, rtol=1e-4), n
+        assert not torch.equal(got[n], loaded[n]) or n.endswith("bias"), n
+
+
+def test_loading_parameters_without_optimizer_state_refreshes_the_master_copies(tmp_path):
+    mesh, model, _ = _flat_model((2, 2))
+    save_checkpoint(str(tmp_path), 5, model)                       # parameters only
+    mesh2, model2, opt2 = _flat_model((2, 2), init_std=0.3)
+    load_checkpoint(str(tmp_path), 5, model2, opt2)
+    assert opt2.step_count == 5
+    for g in opt2.groups:
+        assert torch.equal(g.master, g.param.float())
+        assert not g.m.any() and not g.v.any()
+    before = _globals(mesh2, model2)
+    _step(mesh2, model2, opt2, 0)
+    after = _globals(mesh2, model2)
+    # one AdamW step with lr 1e-2 moves a weight by at most about lr: the loaded weights survive
+    for n in before:
+        assert (after[n] - before[n]).abs().max() <= 1.01e-2 + 1e-6, n
+
+
+def test_interrupted_save_has_no_meta_json(tmp_path):
+    mesh, model, opt = _flat_model((1, 1))
+    class Stop(Exception):
+        pass
+    def barrier():
+        raise Stop()
+    with pytest.raises(Stop):
+        save_checkpoint(str(tmp_path), 1, model, opt, barrier=barrier)
+    assert os.path.exists(tmp_path / "step_1" / "shard_r0_c0.pt")
+    assert not os.path.exists(tmp_path / "step_1" / "meta.json")
+    with pytest.raises(FileNotFoundError):
+        load_checkpoint(str(tmp_path), 1, model, opt)

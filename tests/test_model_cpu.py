@@ -129,3 +129,47 @@ def test_reference_transformer_block_forward_backward():
     assert torch.allclose(_full(mesh, y), Yd.detach(), atol=2e-4, rtol=1e-3)
     dx = blk.backward(mesh.shard(dY))
     assert torch.allclose(_full(mesh, dx), X.grad, atol=2e-4, rtol=1e-3)
+
+
+def test_initial_weights_do_not_depend_on_the_mesh_shape():
+    ref = GPTModel(EmuMesh(1, 1), CFG)
+    want = {n: (p.shards[(0, 0)], k) for n, p, _, k in ref.parameters()}
+    for shape in ((1, 2), (2, 2), (2, 4), (4, 1)):
+        mesh = EmuMesh(*shape)
+        for n, p, _, k in GPTModel(mesh, CFG).parameters():
+            got = _full(mesh, p) if k == "sharded" else _cols(mesh, p)
+            assert torch.equal(got, want[n][0]), (shape, n)
+
+
+def test_loss_curve_is_the_same_on_every_mesh_shape():
+    """Four optimizer steps from the same initial weights on the same batches: the loss of every
+    step agrees across 1x1, 1x2, 2x2 and 2x4 (fp32 on the emulated mesh: to rounding)."""
+    from meshslice_b200.optim import AdamW, FlatGroup
+    from meshslice_b200.trainer import Arena, param_elems
+    curves = {}
+    for shape in ((1, 1), (1, 2), (2, 2), (2, 4)):
+        R, C = shape
+        mesh = EmuMesh(R, C)
+        n_sh, n_rep = (n * R * C for n in param_elems(CFG, R, C))
+        bufs = [torch.zeros(n_sh), torch.zeros(n_sh), torch.zeros(n_rep), torch.zeros(n_rep)]
+        a = [Arena(t) for t in bufs]
+        model = GPTModel(mesh, CFG, alloc_sharded=a[0].alloc, grad_sharded=a[1].alloc, alloc_rep=a[2].alloc,
+                         grad_rep=a[3].alloc)
+        opt = AdamW([FlatGroup(bufs[0], bufs[1], "sharded"), FlatGroup(bufs[2], bufs[3], "row_replicated")],
+                    lr=1e-3, max_grad_norm=None)
+        B, losses = 4, []
+        for step in range(4):
+            ids = torch.randint(0, CFG.vocab, (B, CFG.seq + 1), generator=torch.Generator().manual_seed(50 + step % 2))
+            per = B // R
+            tok = ShardedTensor(mesh, {(r, c): ids[r * per:(r + 1) * per, :-1].reshape(-1) for (r, c) in mesh.coords()})
+            tgt = ShardedTensor(mesh, {(r, c): ids[r * per:(r + 1) * per, 1:].reshape(-1) for (r, c) in mesh.coords()})
+            loss = model.forward_backward(tok, tgt, B * CFG.seq)
+            model.sync_replicated_grads()
+            opt.step()
+            opt.zero_grad()
+            losses.append(sum(loss.shards[(r, 0)] for r in range(R)).item())
+        curves[shape] = losses
+    ref = curves[(1, 1)]
+    assert ref[2] < ref[0] and ref[3] < ref[1]      # the two batches repeat: the model learns them
+    for shape, c in curves.items():
+        assert all(abs(x - y) < 2e-4 for x, y in zip(c, ref)), (shape, c, ref)

@@ -52,3 +52,22 @@ def test_annotate_and_trace_work_without_a_gpu(tmp_path):
         torch.ones(64, 64) @ torch.ones(64, 64)
     data = json.loads(out.read_text())
     assert "traceEvents" in data and len(data["traceEvents"]) > 0
+
+
+def test_p2p_copy_jobs_are_checked_before_launch():
+    import pytest
+    from meshslice_b200.parallel.collectives import validate_copy_jobs, validate_reduce
+    validate_copy_jobs([(4096, 8192, 4, 64, 64, 128)])
+    for bad in [(4096, 8192, 4, 60, 64, 64),      # row of 30 bf16: the tail would be dropped
+                (4096, 8200, 4, 64, 64, 64),      # destination not 16-byte aligned
+                (4100, 8192, 4, 64, 64, 64),
+                (4096, 8192, 4, 64, 72, 64),
+                (4096, 8192, 4, 64, 64, 32),      # pitch smaller than the row
+                (4096, 8192, 0, 64, 64, 64)]:
+        with pytest.raises(ValueError):
+            validate_copy_jobs([bad])
+    validate_reduce([4096, 8192], 64, 16384, 32, 8, 32)
+    with pytest.raises(ValueError):
+        validate_reduce([4096, 8192], 64, 16384, 30, 8, 30)
+    with pytest.raises(ValueError):
+        validate_reduce([4096, 8194], 64, 16384, 32, 8, 32)
