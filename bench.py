@@ -53,14 +53,18 @@ class ClockSampler:
          "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
          "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
-    def __init__(self):
+    def __init__(self, gpu_ids=None):
+        """``gpu_ids``: nvidia-smi identifiers (UUIDs or indices) of the GPUs of this job; the
+        other GPUs of a shared box idle at low clocks and would drag the median down."""
         self.proc = None
+        self.gpu_ids = list(gpu_ids or [])
         self.path = f"/tmp/bench_clocks_{os.getpid()}.csv"
 
     def start(self):
         try:
             self.f = open(self.path, "w")
-            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+            sel = ["-i", ",".join(self.gpu_ids)] if self.gpu_ids else []
+            self.proc = subprocess.Popen(["nvidia-smi", *sel, f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
                                           "-lms", "200"], stdout=self.f, stderr=subprocess.DEVNULL)
         except Exception:
             self.proc = None
@@ -168,7 +172,14 @@ def main():
         trainer.train_step(dev[i % n_slots], read_loss=False)
     trainer.check()
 
-    sampler = ClockSampler()
+    def _uuid(i):
+        u = str(torch.cuda.get_device_properties(i).uuid)
+        return u if u.startswith("GPU-") else "GPU-" + u
+    try:       # the job's ranks use the first `world` visible devices of this node
+        ids = [_uuid(i) for i in range(min(world, torch.cuda.device_count()))]
+    except Exception:
+        ids = [str(i) for i in range(world)]
+    sampler = ClockSampler(ids)
     C_ = _native.load()
     if rank == 0:
         sampler.start()

@@ -65,7 +65,7 @@ def main():
     for spec in mesh_specs:      # every mesh gets its own process groups, heap and engine, in one job
         R, C = [int(v) for v in spec.split("x")]
         mesh = DistMesh(R, C)
-        eng = FusedEngine(mesh, 2 * big // R + (1 << 20), 2 * big // C + (1 << 20), 2 * big // min(R, C) + (1 << 20), 0)
+        eng = FusedEngine(mesh, 2 * big // R + (1 << 20), 2 * big // C + (1 << 20), 2 * big // min(R, C) + (1 << 20))
         run_mesh(args, mesh, eng, shapes, world, out, say, tp, ShardedTensor)
         torch.cuda.empty_cache()
     if rank == 0 and args.json:

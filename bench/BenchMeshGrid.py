@@ -49,7 +49,7 @@ def main():
         mesh = DistMesh(R, C)
         m = T // R
         eng = FusedEngine(mesh, m * 4 * d * 2 + (1 << 20), 4 * d * d // C * 2 + (1 << 20),
-                          max(m * 4 * d, 4 * d * d // min(R, C)) * 2 + (1 << 20), 1 << 20)
+                          max(m * 4 * d, 4 * d * d // min(R, C)) * 2 + (1 << 20), exchange_rows=m)
         for k in a.slices:
             kw = dict(device=dev, std=0.02)
             layers = [ShardedFFLayer(mesh, "meshslice", "ls", k, d, d, seed=1, **kw),

@@ -50,7 +50,7 @@ def main():
         if world > 1:
             m = T // a.nrows
             FusedEngine(mesh, m * 4 * d * 2, 4 * d * d // a.ncols * 2 + (1 << 20), m * 4 * d * 2 + (1 << 20),
-                        m * 4 * d // a.ncols * 2 + (1 << 20))
+                        exchange_rows=m)
         else:
             LocalGemmEngine(mesh)
 

@@ -38,7 +38,7 @@ def main(argv=None):
         T, d = B * S, H * D
         m = T // mesh.R
         FusedEngine(mesh, m * 4 * d * 2 + (1 << 20), 4 * d * d // mesh.C * 2 + (1 << 20),
-                    max(m * 4 * d, 4 * d * d // min(mesh.R, mesh.C)) * 2 + (1 << 20), 0)
+                    max(m * 4 * d, 4 * d * d // min(mesh.R, mesh.C)) * 2 + (1 << 20), exchange_rows=m)
         rank0 = dist.get_rank() == 0
     else:
         B, S, H, D = 4, 128, 8, 64

@@ -62,6 +62,45 @@ BarrierArgs parse_barrier(const py::dict& d) {
   return b;
 }
 
+// Row exchange descriptor from a dict (None or empty: no exchange).  Keys: n, me, dst[n], slots,
+// stride, counter[n], my_counter, target, timeout_ns, status.
+struct ParsedExchange {
+  RowExchange ex;
+  bool on;
+  const RowExchange* ptr() const { return on ? &ex : nullptr; }
+};
+ParsedExchange parse_exchange(const py::object& o) {
+  ParsedExchange r;
+  std::memset(&r.ex, 0, sizeof(r.ex));
+  r.on = false;
+  if (o.is_none()) return r;
+  py::dict d = o.cast<py::dict>();
+  const int n = (int)geti(d, "n");
+  if (n <= 1) return r;
+  if (n > kExMaxPeers) throw std::runtime_error("row exchange: too many GPUs in the group");
+  r.ex.n = n;
+  r.ex.me = (int)geti(d, "me");
+  auto dst = d["dst"].cast<std::vector<uint64_t>>();
+  auto cnt = d["counter"].cast<std::vector<uint64_t>>();
+  if ((int)dst.size() != n || (int)cnt.size() != n || r.ex.me < 0 || r.ex.me >= n)
+    throw std::runtime_error("row exchange: need one slot area and one counter per GPU of the group");
+  for (int i = 0; i < n; ++i) {
+    if (dst[i] == 0 || (dst[i] & 15) || cnt[i] == 0) throw std::runtime_error("row exchange: bad pointer");
+    r.ex.dst[i] = P<float>(dst[i]);
+    r.ex.counter[i] = P<uint32_t>(cnt[i]);
+  }
+  r.ex.slots = P<const float>(getp(d, "slots"));
+  r.ex.stride = geti(d, "stride");
+  r.ex.my_counter = P<const uint32_t>(getp(d, "my_counter"));
+  r.ex.target = (uint32_t)geti(d, "target");
+  r.ex.timeout_ns = (uint64_t)geti(d, "timeout_ns", 20000000000LL);
+  r.ex.status = P<uint32_t>(getp(d, "status"));
+  if (r.ex.slots == nullptr || r.ex.my_counter == nullptr || r.ex.status == nullptr || r.ex.stride <= 0)
+    throw std::runtime_error("row exchange: slots, my_counter, status and stride are required");
+  r.on = true;
+  return r;
+}
+
 // ---------------------------------------------------------------------------------------
 // GEMM
 // ---------------------------------------------------------------------------------------
@@ -97,6 +136,7 @@ void gemm_run(const py::dict& d) {
   if (a.n_slices < 1 || tiles_s % (a.n_slices * a.cyc) != 0)
     throw std::runtime_error("gemm: n_slices must divide the tile count of the sliced dimension");
   if (a.group < 1) a.group = 1;
+  a.stages = (int)geti(d, "stages", 7);
   a.rot = (int)geti(d, "rot", 0);
   if (a.rot < 0 || a.rot >= tiles_s / a.n_slices) a.rot = 0;
   if (geti(d, "no_tiles")) a.tiles_m = 0;  // reduce phase only
@@ -114,6 +154,8 @@ void gemm_run(const py::dict& d) {
   a.b_flag_mode = (int)geti(d, "b_flag_mode");
   a.b_flag_base = (int)geti(d, "b_flag_base");
   a.b_flag_count = (int)geti(d, "b_flag_count");
+  a.b_nchunk = (int)geti(d, "b_nchunk", 1);
+  if (a.b_nchunk < 1) a.b_nchunk = 1;
   a.a_kpanel = (int)geti(d, "a_kpanel", 1);
   a.b_kpanel = (int)geti(d, "b_kpanel", 1);
   a.kp_target = (uint32_t)geti(d, "kp_target", 0);
@@ -173,12 +215,15 @@ void gemm_run(const py::dict& d) {
 
   CUtensorMap ta, tb;
   int r;
+  const bool try3d = geti(d, "map3d", 1) != 0;
   if (!a.a_mn_major) r = make_tensor_map_2d(&ta, P<void>(A), a.K, a.M, lda * 2, kBK, kBM);
+  else if (try3d && make_tensor_map_mn3d(&ta, P<void>(A), a.M, a.K, lda * 2, kBM / 64) == 0) { r = 0; a.a_map3d = 1; }
   else r = make_tensor_map_2d(&ta, P<void>(A), a.M, a.K, lda * 2, 64, kBK);
   if (r != 0) throw std::runtime_error("gemm: tensor map for A failed, code " + std::to_string(r));
   const bool plain = a.n_chunks == 0 && a.n_ranks == 0 && a.red_n == 0 && a.push_n == 0 && a.tiles_m > 0;
   const bool pair = plain && geti(d, "two_cta", 1) != 0;
   if (!a.b_mn_major) r = make_tensor_map_2d(&tb, P<void>(B), a.K, a.N, ldb * 2, kBK, kBN / 2);
+  else if (try3d && make_tensor_map_mn3d(&tb, P<void>(B), a.N, a.K, ldb * 2, kBN / 128) == 0) { r = 0; a.b_map3d = 1; }
   else r = make_tensor_map_2d(&tb, P<void>(B), a.N, a.K, ldb * 2, 64, kBK);
   if (r != 0) throw std::runtime_error("gemm: tensor map for B failed, code " + std::to_string(r));
 
@@ -259,6 +304,7 @@ PYBIND11_MODULE(_C, m) {
   m.attr("BK") = kBK;
   m.attr("MAX_PEERS") = kMaxPeers;
   m.attr("COPY_JOB_BYTES") = (int)sizeof(CopyJob);
+  m.attr("AUX_WARPS") = (int)kAuxWarps;   // communication warps per CTA: each bumps a chunk flag once
   m.attr("PUSH_JOB_BYTES") = (int)sizeof(PushJob);
   m.attr("CHUNK_DESC_BYTES") = (int)sizeof(ChunkDesc);
 
@@ -302,18 +348,26 @@ PYBIND11_MODULE(_C, m) {
   // ---- ops ----
   m.def("ln_fwd", [](int mode, uint64_t x, uint64_t res, uint64_t h_out, uint64_t y, uint64_t gamma,
                      uint64_t beta, uint64_t stats, uint64_t mean_rstd, int rows, int cols,
-                     int total_cols, float eps, uint64_t stream) {
+                     int total_cols, float eps, uint64_t stream, py::object exch) {
+    const ParsedExchange e = parse_exchange(exch);
     check(ln_fwd(mode, P<void>(x), P<void>(res), P<void>(h_out), P<void>(y), P<void>(gamma),
                  P<void>(beta), P<float>(stats), P<float>(mean_rstd), rows, cols, total_cols, eps,
-                 S(stream)), "ln_fwd");
-  });
+                 S(stream), e.ptr()), "ln_fwd");
+  }, py::arg("mode"), py::arg("x"), py::arg("res"), py::arg("h_out"), py::arg("y"), py::arg("gamma"),
+     py::arg("beta"), py::arg("stats"), py::arg("mean_rstd"), py::arg("rows"), py::arg("cols"),
+     py::arg("total_cols"), py::arg("eps"), py::arg("stream"), py::arg("exch") = py::none());
   m.def("ln_bwd", [](int mode, uint64_t dy, uint64_t h, uint64_t gamma, uint64_t mean_rstd,
                      uint64_t dres, uint64_t dx, uint64_t stats, uint64_t dgamma, uint64_t dbeta,
-                     int rows, int cols, int total_cols, uint64_t stream) {
+                     int rows, int cols, int total_cols, uint64_t stream, py::object exch) {
+    const ParsedExchange e = parse_exchange(exch);
     check(ln_bwd(mode, P<void>(dy), P<void>(h), P<void>(gamma), P<float>(mean_rstd), P<void>(dres),
                  P<void>(dx), P<float>(stats), P<float>(dgamma), P<float>(dbeta), rows, cols,
-                 total_cols, S(stream)), "ln_bwd");
-  });
+                 total_cols, S(stream), e.ptr()), "ln_bwd");
+  }, py::arg("mode"), py::arg("dy"), py::arg("h"), py::arg("gamma"), py::arg("mean_rstd"), py::arg("dres"),
+     py::arg("dx"), py::arg("stats"), py::arg("dgamma"), py::arg("dbeta"), py::arg("rows"), py::arg("cols"),
+     py::arg("total_cols"), py::arg("stream"), py::arg("exch") = py::none());
+  m.def("ln_grid", &ln_grid, "CTAs of the LayerNorm kernels for a row count (0: forward, 1: backward)");
+  m.def("ce_grid", &ce_grid, "CTAs of the cross-entropy kernels for a row count");
   m.def("gelu_fwd", [](uint64_t x, uint64_t y, int64_t n, uint64_t stream) {
     check(gelu_fwd(P<void>(x), P<void>(y), n, S(stream)), "gelu_fwd");
   });
@@ -338,17 +392,23 @@ PYBIND11_MODULE(_C, m) {
   });
   m.def("ce_partial", [](uint64_t logits, int64_t ld, uint64_t targets, int rows, int cols,
                          int col_offset, int vocab, uint64_t row_max, uint64_t row_sumexp,
-                         uint64_t tgt_logit, uint64_t stream) {
+                         uint64_t tgt_logit, uint64_t stream, py::object exch) {
+    const ParsedExchange e = parse_exchange(exch);
     check(ce_partial(P<void>(logits), ld, P<int64_t>(targets), rows, cols, col_offset, vocab,
-                     P<float>(row_max), P<float>(row_sumexp), P<float>(tgt_logit), S(stream)),
+                     P<float>(row_max), P<float>(row_sumexp), P<float>(tgt_logit), S(stream), e.ptr()),
           "ce_partial");
-  });
+  }, py::arg("logits"), py::arg("ld"), py::arg("targets"), py::arg("rows"), py::arg("cols"),
+     py::arg("col_offset"), py::arg("vocab"), py::arg("row_max"), py::arg("row_sumexp"), py::arg("tgt_logit"),
+     py::arg("stream"), py::arg("exch") = py::none());
   m.def("ce_grad", [](uint64_t logits, int64_t ld, uint64_t targets, int rows, int cols,
                       int col_offset, int vocab, uint64_t gmax, uint64_t gsum, float scale,
-                      uint64_t stream) {
+                      uint64_t stream, uint64_t row_loss, py::object exch) {
+    const ParsedExchange e = parse_exchange(exch);
     check(ce_grad(P<void>(logits), ld, P<int64_t>(targets), rows, cols, col_offset, vocab,
-                  P<float>(gmax), P<float>(gsum), scale, S(stream)), "ce_grad");
-  });
+                  P<float>(gmax), P<float>(gsum), scale, S(stream), P<float>(row_loss), e.ptr()), "ce_grad");
+  }, py::arg("logits"), py::arg("ld"), py::arg("targets"), py::arg("rows"), py::arg("cols"),
+     py::arg("col_offset"), py::arg("vocab"), py::arg("gmax"), py::arg("gsum"), py::arg("scale"),
+     py::arg("stream"), py::arg("row_loss") = 0, py::arg("exch") = py::none());
   m.def("embedding_fwd", [](uint64_t tokens, uint64_t tok, uint64_t pos, uint64_t out, int n_tokens,
                             int seq, int cols, uint64_t stream) {
     check(embedding_fwd(P<int64_t>(tokens), P<void>(tok), P<void>(pos), P<void>(out), n_tokens, seq,

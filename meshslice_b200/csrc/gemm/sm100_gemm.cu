@@ -12,11 +12,14 @@
 //               either bias / GeLU and a store to local memory, or the push of the bf16 partial tile
 //               into the owner GPU's slot (staged in smem, written with coalesced 16-byte stores or
 //               2-D TMA tensor stores) with one arrival count per slice and owner
-//   warp 6      communication: cross-GPU entry / exit barrier (CTA 0) and the gather side: pieces of
-//               the LOCAL shard go through smem to every GPU of the group (posted bulk stores), one
-//               flag per chunk on every destination
-// After its tiles every CTA joins the reduce phase, which sums the partial tiles that peers
-// pushed into this GPU's slots.
+//   warps 6..9  communication and reduction (kAuxWarps of them; warp 6 of CTA 0 also runs the
+//               cross-GPU entry / exit barrier).  Gather side: the warps of all CTAs share the pieces
+//               of the LOCAL shard; a piece is read once with coalesced 16-byte loads (several per
+//               lane in flight) and written with 16-byte stores to every GPU of the group (posted
+//               writes over NVLink), one flag per chunk on every destination.  Reduce side: after
+//               the gather the same warps sum, slice by slice and as soon as a slice's arrival
+//               counter is complete, the partial tiles that peers pushed into this GPU's slots, so
+//               the sums of slice s run under the tensor-core work of slice s + 1.
 //
 // Every wait is bounded (ptx.cuh); on expiry the kernel records a code in `status`, leaves
 // its loops, frees TMEM and returns.
@@ -34,8 +37,7 @@ constexpr uint32_t kAStageBytes = kBM * kBK * 2;        // 16 KiB: this CTA's 12
 constexpr uint32_t kBStageBytes = (kBN / 2) * kBK * 2;  // 16 KiB: this CTA's 128 columns of B
 constexpr uint32_t kSmemA = 0;
 constexpr uint32_t kSmemB = kSmemA + kStages * kAStageBytes;
-constexpr uint32_t kSmemComm = kSmemB + kStages * kBStageBytes;
-constexpr uint32_t kSmemEpi = kSmemComm + kCommBufs * kCommBufBytes;
+constexpr uint32_t kSmemEpi = kSmemB + kStages * kBStageBytes;
 constexpr uint32_t kSmemBar = kSmemEpi + 4 * kEpiStageBytes;
 constexpr uint32_t kSmemCnt = kSmemBar + 256;   // [4 epilogue warps][kMaxPeers] tile counts
 constexpr uint32_t kSmemTotal = kSmemCnt + 4 * kMaxPeers * 4;
@@ -67,6 +69,14 @@ __device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorM
       "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
       " [%0], [%1, {%3, %4}], [%2];"
       ::"r"(smem_u32(smem_dst)), "l"(map), "r"(leader_bar), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_3d_pair(void* smem_dst, const CUtensorMap* map, uint32_t leader_bar,
+                                                 int32_t x, int32_t y, int32_t z) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(map), "r"(leader_bar), "r"(x), "r"(y), "r"(z)
       : "memory");
 }
 __device__ __forceinline__ void umma_f16_pair(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc,
@@ -144,10 +154,10 @@ __device__ __forceinline__ bool wait_chunk(const GemmArgs& a, int idx, uint64_t 
 // `seen` remembers chunks already observed complete, so that only the first tile that needs a
 // chunk pays for the system-scope flag reads.
 __device__ __forceinline__ bool wait_operand(const GemmArgs& a, int mode, int base, int count,
-                                             int slice, uint64_t tmo, uint64_t& seen) {
+                                             int slice, int col_chunk, uint64_t tmo, uint64_t& seen) {
   if (mode == 0 || mode == 3) return true;   // mode 3 is waited for inside the contraction loop
-  const int lo = mode == 1 ? base + slice : base;
-  const int hi = mode == 1 ? lo + 1 : base + count;
+  const int lo = mode == 1 ? base + slice : (mode == 4 ? base + col_chunk : base);
+  const int hi = (mode == 1 || mode == 4) ? lo + 1 : base + count;
   for (int i = lo; i < hi; ++i) {
     const uint64_t bit = 1ull << (i & 63);
     if (i < 64 && (seen & bit)) continue;
@@ -169,94 +179,168 @@ __device__ __forceinline__ bool wait_panel(const GemmArgs& a, int idx, uint64_t 
 }
 
 // ------------------------------------------------------------------------------------------
-// communication warp: one piece = at most kCommBufBytes
+// communication / reduce warps
 // ------------------------------------------------------------------------------------------
-struct Piece {
-  const char* src;
-  uint32_t rows;
-  uint32_t row_bytes;
-  uint64_t sp, dp;
-  uint64_t dst_off;       // byte offset of this piece inside every destination block
-  const PushJob* job;
-};
+constexpr uint32_t kPieceBytes = 16384;   // work unit of the gather: one warp copies one piece
+constexpr int kGatherUnroll = 8;          // 16-byte loads in flight per lane
 
-struct PieceCursor {
-  const PushJob* jobs;
-  const char* srcs[2];
-  int job, job_end;
-  uint32_t next_in_job;   // next piece index of this CTA inside the current job
-  uint32_t pieces_in_job;
-  uint32_t rows_per_piece, segs_per_row;
-  uint32_t running;       // pieces of earlier jobs of the chunk (for the round-robin)
-  __device__ void open_job() {
-    while (job < job_end) {
-      const PushJob& j = jobs[job];
-      if (j.row_bytes >= (uint32_t)kCommBufBytes) {
-        segs_per_row = (j.row_bytes + kCommBufBytes - 1) / kCommBufBytes;
-        rows_per_piece = 1;
-        pieces_in_job = j.rows * segs_per_row;
-      } else {
-        segs_per_row = 1;
-        rows_per_piece = kCommBufBytes / j.row_bytes;
-        pieces_in_job = (j.rows + rows_per_piece - 1) / rows_per_piece;
+__device__ __forceinline__ uint4 ld_nc_v4(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+__device__ __forceinline__ void st_v4(void* p, const uint4& v) {
+  asm volatile("st.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+               : "memory");
+}
+__device__ __forceinline__ void aux_bar_sync() {   // the kAuxWarps warps of this CTA (named barrier 1)
+  asm volatile("bar.sync 1, %0;" ::"n"(32 * kAuxWarps) : "memory");
+}
+
+// Copies `nvec` 16-byte vectors of a 2-D block (vpr vectors per row) from the local shard to every
+// destination; vector v of the piece is element (v / vpr, v % vpr) counted from the piece's origin.
+__device__ __forceinline__ void gather_piece(const char* src, uint64_t sp, uint64_t dp, uint32_t vpr,
+                                             uint32_t nvec, const PushJob& job, uint64_t dst_off, int lane) {
+  for (uint32_t v0 = 0; v0 < nvec; v0 += 32 * kGatherUnroll) {
+    uint4 val[kGatherUnroll];
+    uint64_t doff[kGatherUnroll];
+#pragma unroll
+    for (int u = 0; u < kGatherUnroll; ++u) {
+      const uint32_t v = v0 + u * 32 + lane;
+      if (v < nvec) {
+        const uint32_t r = v / vpr, c = v - r * vpr;
+        val[u] = ld_nc_v4(src + (uint64_t)r * sp + ((uint64_t)c << 4));
+        doff[u] = dst_off + (uint64_t)r * dp + ((uint64_t)c << 4);
       }
-      const uint32_t g = gridDim.x;
-      next_in_job = (blockIdx.x + g - (running % g)) % g;
-      if (next_in_job < pieces_in_job) return;
-      running += pieces_in_job;
-      ++job;
+    }
+    for (uint32_t d = 0; d < job.n_dst; ++d) {
+      char* dst = job.dst[d];
+#pragma unroll
+      for (int u = 0; u < kGatherUnroll; ++u)
+        if (v0 + u * 32 + lane < nvec) st_v4(dst + doff[u], val[u]);
     }
   }
-  __device__ void init(const PushJob* js, const char* const* bases, int jb, int je) {
-    jobs = js;
-    srcs[0] = bases[0];
-    srcs[1] = bases[1];
-    job = jb;
-    job_end = je;
-    running = 0;
-    open_job();
-  }
-  __device__ bool next(Piece& p) {
-    if (job >= job_end) return false;
-    const PushJob& j = jobs[job];
-    const char* base = srcs[j.src_sel & 1];
-    const uint32_t idx = next_in_job;
-    if (segs_per_row > 1) {
-      const uint32_t row = idx / segs_per_row, seg = idx - row * segs_per_row;
-      const uint32_t off = seg * kCommBufBytes;
-      p.src = base + j.src_off + (uint64_t)row * j.src_pitch + off;
-      p.dst_off = (uint64_t)row * j.dst_pitch + off;
-      p.rows = 1;
-      p.row_bytes = min((uint32_t)kCommBufBytes, j.row_bytes - off);
-    } else {
-      const uint32_t row0 = idx * rows_per_piece;
-      p.src = base + j.src_off + (uint64_t)row0 * j.src_pitch;
-      p.dst_off = (uint64_t)row0 * j.dst_pitch;
-      p.rows = min(rows_per_piece, j.rows - row0);
-      p.row_bytes = j.row_bytes;
-    }
-    p.sp = j.src_pitch;
-    p.dp = j.dst_pitch;
-    p.job = &j;
-    next_in_job += gridDim.x;
-    if (next_in_job >= pieces_in_job) {
-      running += pieces_in_job;
-      ++job;
-      open_job();
-    }
-    return true;
-  }
-};
+}
 
-__device__ void comm_warp_main(const GemmArgs& a, uint8_t* comm_smem, uint64_t* comm_bar) {
+// Sums ROWS consecutive rows (8 columns per lane) over the first `n` of SLOTS slots in fixed
+// order and writes them: ROWS x SLOTS 16-byte loads are in flight per lane.
+template <int ROWS, int SLOTS>
+__device__ __forceinline__ void reduce_rows(const GemmArgs& a, const __nv_bfloat16* slots, int64_t slot_stride,
+                                            int n, int64_t row0, int col, const float (&bv)[8]) {
+  uint4 x[ROWS][SLOTS];
+#pragma unroll
+  for (int rr = 0; rr < ROWS; ++rr) {
+#pragma unroll
+    for (int sl = 0; sl < SLOTS; ++sl)
+      if (sl < n && row0 + rr < a.red_rows)
+        x[rr][sl] = *reinterpret_cast<const uint4*>(slots + sl * slot_stride + (row0 + rr) * a.red_ld + col);
+  }
+#pragma unroll
+  for (int rr = 0; rr < ROWS; ++rr) {
+    const int64_t row = row0 + rr;
+    if (row >= a.red_rows) continue;
+    float acc[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+#pragma unroll
+    for (int sl = 0; sl < SLOTS; ++sl)
+      if (sl < n) {
+        const uint4 v = x[rr][sl];
+        acc[0] += bf16_lo(v.x); acc[1] += bf16_hi(v.x);
+        acc[2] += bf16_lo(v.y); acc[3] += bf16_hi(v.y);
+        acc[4] += bf16_lo(v.z); acc[5] += bf16_hi(v.z);
+        acc[6] += bf16_lo(v.w); acc[7] += bf16_hi(v.w);
+      }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] += bv[i];
+    if (a.c_fp32) {
+      float* p = reinterpret_cast<float*>(a.C) + row * a.ldc + col;
+      float4 lo = make_float4(acc[0], acc[1], acc[2], acc[3]);
+      float4 hi = make_float4(acc[4], acc[5], acc[6], acc[7]);
+      if (a.accumulate) {
+        const float4 c0 = *reinterpret_cast<const float4*>(p);
+        const float4 c1 = *reinterpret_cast<const float4*>(p + 4);
+        lo.x += c0.x; lo.y += c0.y; lo.z += c0.z; lo.w += c0.w;
+        hi.x += c1.x; hi.y += c1.y; hi.z += c1.z; hi.w += c1.w;
+      }
+      *reinterpret_cast<float4*>(p) = lo;
+      *reinterpret_cast<float4*>(p + 4) = hi;
+    } else {
+      __nv_bfloat16* p = reinterpret_cast<__nv_bfloat16*>(a.C) + row * a.ldc + col;
+      if (a.accumulate) {
+        const uint4 c = *reinterpret_cast<const uint4*>(p);
+        acc[0] += bf16_lo(c.x); acc[1] += bf16_hi(c.x);
+        acc[2] += bf16_lo(c.y); acc[3] += bf16_hi(c.y);
+        acc[4] += bf16_lo(c.z); acc[5] += bf16_hi(c.z);
+        acc[6] += bf16_lo(c.w); acc[7] += bf16_hi(c.w);
+      }
+      uint4 o4;
+      o4.x = pack_bf16(acc[0], acc[1]);
+      o4.y = pack_bf16(acc[2], acc[3]);
+      o4.z = pack_bf16(acc[4], acc[5]);
+      o4.w = pack_bf16(acc[6], acc[7]);
+      *reinterpret_cast<uint4*>(p) = o4;
+    }
+  }
+}
+
+// Sums the partial tiles of slice `s` that the push group's ranks wrote into this GPU's slots.
+// Work unit: 32 rows x 256 columns of one block; units are dealt round-robin to the aux warps of all
+// CTAs.  Fixed summation order (slot 0, 1, ...): the result does not depend on arrival order.
+__device__ void reduce_slice(const GemmArgs& a, int s, int worker, int n_workers, int lane) {
+  const int RB = a.red_slice_dim == 0 ? 2 * kBM : kBM;
+  const int tiles_r = (a.red_rows + RB - 1) / RB;
+  const int tiles_c = (a.red_cols + kBN - 1) / kBN;
+  const int tiles_s = a.red_slice_dim == 0 ? tiles_r : tiles_c;
+  const int tiles_o = a.red_slice_dim == 0 ? tiles_c : tiles_r;
+  const int S = a.n_slices;
+  const int nb = tiles_s / S;
+  const int sub = RB / 32;                       // units per block
+  const int n_units = nb * tiles_o * sub;
+  const __nv_bfloat16* slots = reinterpret_cast<const __nv_bfloat16*>(a.red_slots);
+  const __nv_bfloat16* bias = reinterpret_cast<const __nv_bfloat16*>(a.bias);
+  const int64_t slot_stride = (int64_t)a.red_rows * a.red_ld;
+  for (int u = worker; u < n_units; u += n_workers) {
+    const int blk = u / sub, part = u - blk * sub;
+    const int j = blk / tiles_o, o = blk - j * tiles_o;
+    const int cg = j / a.cyc;
+    const int blk_s = (cg * S + s) * a.cyc + (j - cg * a.cyc);
+    const int rb = a.red_slice_dim == 0 ? blk_s : o;
+    const int cb = a.red_slice_dim == 0 ? o : blk_s;
+    const int col = cb * kBN + lane * 8;
+    if (col >= a.red_cols) continue;
+    float bv[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    if (bias != nullptr) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) bv[i] = __bfloat162float(bias[col + i]);
+    }
+    const int64_t row0 = (int64_t)rb * RB + part * 32;
+    if (a.red_n <= 2) {
+#pragma unroll 1
+      for (int r = 0; r < 32; r += 8) reduce_rows<8, 2>(a, slots, slot_stride, a.red_n, row0 + r, col, bv);
+    } else if (a.red_n <= 4) {
+#pragma unroll 1
+      for (int r = 0; r < 32; r += 4) reduce_rows<4, 4>(a, slots, slot_stride, a.red_n, row0 + r, col, bv);
+    } else {
+#pragma unroll 1
+      for (int r = 0; r < 32; r += 2) reduce_rows<2, 8>(a, slots, slot_stride, a.red_n, row0 + r, col, bv);
+    }
+  }
+}
+
+__device__ void aux_warp_main(const GemmArgs& a, int aux) {
   const int lane = threadIdx.x & 31;
   const uint64_t tmo = a.timeout_ns;
+  const int worker = blockIdx.x * kAuxWarps + aux;
+  const int n_workers = gridDim.x * kAuxWarps;
   bool ok = true;
 
-  // ---- entry barrier: CTA 0 tells every rank that this GPU's earlier work is complete and
-  //      waits for the same message from every rank, then releases the local CTAs.
+  // ---- entry barrier: warp 6 of CTA 0 tells every rank that this GPU's earlier work is complete
+  //      and waits for the same message from every rank, then releases the local CTAs.
   if (a.n_ranks > 0) {
-    if (blockIdx.x == 0) {
+    if (blockIdx.x == 0 && aux == 0) {
       if (lane < a.n_ranks && lane != a.my_rank) {
         st_release_sys(a.entry_flags[lane] + a.my_rank, a.epoch);
         if (!wait_flag_geq_sys(a.entry_flags[a.my_rank] + lane, a.epoch, tmo)) {
@@ -277,83 +361,83 @@ __device__ void comm_warp_main(const GemmArgs& a, uint8_t* comm_smem, uint64_t* 
     }
   }
 
-  // ---- gather side: read a piece of the local shard once, write it to every GPU of the group
-  if (lane == 0 && ok && a.n_chunks > 0 && !a.skip_comm) {
-    uint32_t issued = 0, stored = 0;
-    Piece q[kCommBufs];
-    for (int c = 0; c < a.n_chunks && ok; ++c) {
+  // ---- gather side: the pieces of every chunk are dealt round-robin to the aux warps of all CTAs
+  if (ok && a.n_chunks > 0 && !a.skip_comm) {
+    uint32_t running = 0;   // pieces of earlier jobs (keeps the round-robin going across jobs)
+    for (int c = 0; c < a.n_chunks; ++c) {
       const ChunkDesc& cd = a.chunks[c];
-      PieceCursor cur;
-      cur.init(a.jobs, a.gather_src, cd.job_begin, cd.job_end);
-      bool more = true;
-      while (ok) {
-        while (more && issued - stored < 2) {
-          Piece p;
-          more = cur.next(p);
-          if (!more) break;
-          bulk_wait_read<0>();  // the stores that last read this buffer have finished reading
-          const uint32_t b = issued % kCommBufs;
-          uint8_t* buf = comm_smem + b * kCommBufBytes;
-          const uint32_t total = p.rows * p.row_bytes;
-          mbar_expect_tx(comm_bar + b, total);
-          if (p.rows == 1 || p.sp == p.row_bytes) {
-            bulk_g2s(buf, p.src, total, comm_bar + b);
-          } else {
-            for (uint32_t r = 0; r < p.rows; ++r)
-              bulk_g2s(buf + r * p.row_bytes, p.src + r * p.sp, p.row_bytes, comm_bar + b);
-          }
-          q[b] = p;
-          ++issued;
+      for (int jn = cd.job_begin; jn < cd.job_end; ++jn) {
+        const PushJob& j = a.jobs[jn];
+        const char* base = a.gather_src[j.src_sel & 1] + j.src_off;
+        const uint32_t vpr = j.row_bytes >> 4;
+        uint32_t segs = 1, rows_pp, pieces;
+        if (j.row_bytes > kPieceBytes) {          // long rows: segments of one row
+          segs = (j.row_bytes + kPieceBytes - 1) / kPieceBytes;
+          rows_pp = 1;
+          pieces = j.rows * segs;
+        } else {
+          rows_pp = kPieceBytes / j.row_bytes;
+          pieces = (j.rows + rows_pp - 1) / rows_pp;
         }
-        if (stored == issued) break;
-        const uint32_t b = stored % kCommBufs;
-        if (!mbar_wait(comm_bar + b, (stored / kCommBufs) & 1, tmo)) {
-          report(a, kTimeoutComm, c, stored);
-          ok = false;
-          break;
-        }
-        const Piece& p = q[b];
-        const uint8_t* buf = comm_smem + b * kCommBufBytes;
-        const PushJob& jb = *p.job;
-        for (uint32_t d = 0; d < jb.n_dst; ++d) {
-          char* dst = jb.dst[d] + p.dst_off;
-          if (p.rows == 1 || p.dp == p.row_bytes) {
-            bulk_s2g(dst, buf, p.rows * p.row_bytes);
+        uint32_t first = ((uint32_t)worker + (uint32_t)n_workers - running % (uint32_t)n_workers) % (uint32_t)n_workers;
+        for (uint32_t pi = first; pi < pieces; pi += n_workers) {
+          if (segs > 1) {
+            const uint32_t row = pi / segs, seg = pi - row * segs;
+            const uint32_t off = seg * kPieceBytes;
+            const uint32_t bytes = min(kPieceBytes, j.row_bytes - off);
+            gather_piece(base + (uint64_t)row * j.src_pitch + off, j.src_pitch, j.dst_pitch, bytes >> 4,
+                         bytes >> 4, j, (uint64_t)row * j.dst_pitch + off, lane);
           } else {
-            for (uint32_t r = 0; r < p.rows; ++r)
-              bulk_s2g(dst + r * p.dp, buf + r * p.row_bytes, p.row_bytes);
+            const uint32_t row0 = pi * rows_pp;
+            const uint32_t rows = min(rows_pp, j.rows - row0);
+            gather_piece(base + (uint64_t)row0 * j.src_pitch, j.src_pitch, j.dst_pitch, vpr, rows * vpr, j,
+                         (uint64_t)row0 * j.dst_pitch, lane);
           }
         }
-        bulk_commit();   // one group per piece, whatever the number of destinations
-        ++stored;
+        running += pieces;
       }
-      // this CTA's share of the chunk has been written everywhere: tell every destination
-      bulk_wait_all<0>();
-      fence_proxy_async();
+      // this warp's share of the chunk has been written everywhere: tell every destination
       __threadfence_system();
-      if (ok)
-        for (uint32_t d = 0; d < cd.n_sig; ++d) red_add_release_sys(cd.sig[d], 1u);
+      __syncwarp();
+      if (lane < (int)cd.n_sig) red_add_release_sys(cd.sig[lane], 1u);
+      __syncwarp();
     }
-    bulk_wait_all<0>();
   }
 
   // ---- optional exit barrier: nobody leaves before every rank has finished its transfers
   if (a.n_ranks > 0 && a.exit_barrier) {
-    if (lane == 0) red_add_release_gpu(a.done_counter, 1u);
-    if (blockIdx.x == 0) {
-      bool ok2 = ok;
-      if (lane == 0 && ok2) {
-        if (!wait_flag_geq_gpu(a.done_counter, a.done_target, 6 * tmo)) {
-          report(a, kTimeoutExit, 0xffffffffu, a.epoch);
-          ok2 = false;
+    aux_bar_sync();   // all aux warps of this CTA are done with the gather
+    if (aux == 0) {
+      if (lane == 0) red_add_release_gpu(a.done_counter, 1u);
+      if (blockIdx.x == 0) {
+        bool ok2 = ok;
+        if (lane == 0 && ok2) {
+          if (!wait_flag_geq_gpu(a.done_counter, a.done_target, 6 * tmo)) {
+            report(a, kTimeoutExit, 0xffffffffu, a.epoch);
+            ok2 = false;
+          }
+        }
+        ok2 = __all_sync(0xffffffffu, ok2);
+        if (ok2 && lane < a.n_ranks && lane != a.my_rank) {
+          st_release_sys(a.exit_flags[lane] + a.my_rank, a.epoch);
+          if (!wait_flag_geq_sys(a.exit_flags[a.my_rank] + lane, a.epoch, 6 * tmo))
+            report(a, kTimeoutExit, lane, a.epoch);
         }
       }
-      ok2 = __all_sync(0xffffffffu, ok2);
-      if (ok2 && lane < a.n_ranks && lane != a.my_rank) {
-        st_release_sys(a.exit_flags[lane] + a.my_rank, a.epoch);
-        if (!wait_flag_geq_sys(a.exit_flags[a.my_rank] + lane, a.epoch, 6 * tmo))
-          report(a, kTimeoutExit, lane, a.epoch);
+    }
+  }
+
+  // ---- reduce side: slice by slice, as soon as every partial tile of the slice has arrived
+  if (a.red_n > 0) {
+    for (int s = 0; s < a.n_slices && ok; ++s) {
+      if (lane == 0) {
+        if (!wait_flag_geq_sys(a.red_counter + s, a.red_target, 8 * tmo)) {
+          report(a, kTimeoutReduce, s, worker);
+          ok = false;
+        }
       }
+      ok = __all_sync(0xffffffffu, ok);
+      if (ok) reduce_slice(a, s, worker, n_workers, lane);
     }
   }
 }
@@ -378,7 +462,9 @@ __device__ __forceinline__ void store_row32(const GemmArgs& a, void* base, int64
         *reinterpret_cast<float4*>(p + i) = o;
       }
     } else {
-      for (int i = 0; i < ncols_valid; ++i) p[i] = accumulate ? p[i] + v[i] : v[i];
+#pragma unroll
+      for (int i = 0; i < 32; ++i)
+        if (i < ncols_valid) p[i] = accumulate ? p[i] + v[i] : v[i];
     }
   } else {
     __nv_bfloat16* p = reinterpret_cast<__nv_bfloat16*>(base) + row * ld + col0;
@@ -401,7 +487,9 @@ __device__ __forceinline__ void store_row32(const GemmArgs& a, void* base, int64
         *reinterpret_cast<uint4*>(p + i) = o;
       }
     } else {
-      for (int i = 0; i < ncols_valid; ++i) {
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        if (i >= ncols_valid) continue;
         float x = v[i];
         if (accumulate) x += __bfloat162float(p[i]);
         p[i] = __float2bfloat16_rn(x);
@@ -423,7 +511,6 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
                                              ~static_cast<uintptr_t>(1023));
   uint8_t* sA = smem + kSmemA;
   uint8_t* sB = smem + kSmemB;
-  uint8_t* sComm = smem + kSmemComm;
   uint8_t* sEpi = smem + kSmemEpi;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kSmemBar);
   uint32_t* sCnt = reinterpret_cast<uint32_t*>(smem + kSmemCnt);
@@ -431,8 +518,7 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
   uint64_t* empty_bar = bars + kStages;        // [kStages]
   uint64_t* tfull_bar = bars + 2 * kStages;    // [2]
   uint64_t* tempty_bar = tfull_bar + 2;        // [2]
-  uint64_t* comm_bar = tempty_bar + 2;         // [kCommBufs]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(comm_bar + kCommBufs);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -457,7 +543,6 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
       mbar_init(tfull_bar + i, 1);                  // one per CTA
       mbar_init(tempty_bar + i, 2 * kEpiThreads);   // used in the leader: both CTAs' epilogues
     }
-    for (int i = 0; i < kCommBufs; ++i) mbar_init(comm_bar + i, 1);
     mbar_fence_init();
   }
   if (warp == 1) {
@@ -488,8 +573,9 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
         const TileCoord tc = tile_coord(t, a);
         if (a.a_flag_mode | a.b_flag_mode) {
           const uint64_t before = seen;
-          if (!wait_operand(a, a.a_flag_mode, a.a_flag_base, a.a_flag_count, tc.slice, 3 * tmo, seen) ||
-              !wait_operand(a, a.b_flag_mode, a.b_flag_base, a.b_flag_count, tc.slice, 3 * tmo, seen)) {
+          const int cc = tc.n_blk / a.b_nchunk;   // column chunk of B (flag mode 4)
+          if (!wait_operand(a, a.a_flag_mode, a.a_flag_base, a.a_flag_count, tc.slice, 0, 3 * tmo, seen) ||
+              !wait_operand(a, a.b_flag_mode, a.b_flag_base, a.b_flag_count, tc.slice, cc, 3 * tmo, seen)) {
             report(a, kTimeoutChunk, t, tc.slice);
             ok = false;
             break;
@@ -523,8 +609,12 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
           if (rank == 0) mbar_expect_tx(full_bar + stage, 2 * (kAStageBytes + kBStageBytes));
           uint8_t* da = sA + stage * kAStageBytes;
           uint8_t* db = sB + stage * kBStageBytes;
+          // an MN-major operand is one 3-D box per stage (two 64-wide blocks of 64 k-rows) when its
+          // extent allows it, else two 2-D boxes: the producer's issue rate is what bounds the pipe
           if (!a.a_mn_major) {
             tma_load_2d_pair(da, &tma_a, fb, kb * kBK, row_a);
+          } else if (a.a_map3d) {
+            tma_load_3d_pair(da, &tma_a, fb, 0, kb * kBK, row_a >> 6);
           } else {
 #pragma unroll
             for (int j = 0; j < kBM / 64; ++j)
@@ -532,6 +622,8 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
           }
           if (!a.b_mn_major) {
             tma_load_2d_pair(db, &tma_b, fb, kb * kBK, col_b);
+          } else if (a.b_map3d) {
+            tma_load_3d_pair(db, &tma_b, fb, 0, kb * kBK, col_b >> 6);
           } else {
 #pragma unroll
             for (int j = 0; j < kBN / 128; ++j)
@@ -764,8 +856,8 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
     }
     if (cur_slice >= 0) flush_counts(cur_slice);
   } else {
-    // ===================== communication warp =====================
-    comm_warp_main(a, sComm, comm_bar);
+    // ===================== communication / reduce warps =====================
+    aux_warp_main(a, warp - 6);
   }
 
   // ---- all roles of both CTAs of the pair are done with TMEM, barriers and the pipeline
@@ -776,87 +868,6 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
     asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols)
                  : "memory");
 
-  // ===================== reduce phase =====================
-  if (a.red_n > 0) {
-    // row slices follow the 256-row cluster tiles of the senders, column slices the 256 columns
-    const int RB = a.red_slice_dim == 0 ? 2 * kBM : kBM;
-    const int tiles_r = (a.red_rows + RB - 1) / RB;
-    const int tiles_c = (a.red_cols + kBN - 1) / kBN;
-    const int tiles_s = a.red_slice_dim == 0 ? tiles_r : tiles_c;
-    const int tiles_o = a.red_slice_dim == 0 ? tiles_c : tiles_r;
-    const int S = a.n_slices;
-    const int nb = tiles_s / S;
-    const int n_items = tiles_r * tiles_c;
-    const __nv_bfloat16* slots = reinterpret_cast<const __nv_bfloat16*>(a.red_slots);
-    const __nv_bfloat16* bias = reinterpret_cast<const __nv_bfloat16*>(a.bias);
-    const int64_t slot_stride = (int64_t)a.red_rows * a.red_ld;
-    for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
-      // slice-major order so that early slices are summed while late ones are in flight
-      const int s = item / (nb * tiles_o);
-      const int r = item - s * (nb * tiles_o);
-      const int j = r / tiles_o, o = r - j * tiles_o;
-      const int cg = j / a.cyc;
-      const int blk_s = (cg * S + s) * a.cyc + (j - cg * a.cyc);
-      const int rb = a.red_slice_dim == 0 ? blk_s : o;
-      const int cb = a.red_slice_dim == 0 ? o : blk_s;
-      int ok = 1;
-      if (threadIdx.x == 0) {
-        if (!wait_flag_geq_sys(a.red_counter + s, a.red_target, 8 * tmo)) {
-          report(a, kTimeoutReduce, s, item);
-          ok = 0;
-        }
-      }
-      ok = __syncthreads_and(ok);
-      if (!ok) break;
-      // RB x 256 block, 8 bf16 per vector
-      for (int vi = threadIdx.x; vi < RB * (kBN / 8); vi += kGemmThreads) {
-        const int rr = vi / (kBN / 8), cv = vi - rr * (kBN / 8);
-        const int64_t row = (int64_t)rb * RB + rr;
-        const int col = cb * kBN + cv * 8;
-        if (row >= a.red_rows || col >= a.red_cols) continue;
-        float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-        for (int sl = 0; sl < a.red_n; ++sl) {
-          const uint4 x = *reinterpret_cast<const uint4*>(slots + sl * slot_stride + row * a.red_ld + col);
-          acc[0] += bf16_lo(x.x); acc[1] += bf16_hi(x.x);
-          acc[2] += bf16_lo(x.y); acc[3] += bf16_hi(x.y);
-          acc[4] += bf16_lo(x.z); acc[5] += bf16_hi(x.z);
-          acc[6] += bf16_lo(x.w); acc[7] += bf16_hi(x.w);
-        }
-        if (bias != nullptr) {
-#pragma unroll
-          for (int i = 0; i < 8; ++i) acc[i] += __bfloat162float(bias[col + i]);
-        }
-        if (a.c_fp32) {
-          float* p = reinterpret_cast<float*>(a.C) + row * a.ldc + col;
-          float4 lo = make_float4(acc[0], acc[1], acc[2], acc[3]);
-          float4 hi = make_float4(acc[4], acc[5], acc[6], acc[7]);
-          if (a.accumulate) {
-            const float4 c0 = *reinterpret_cast<const float4*>(p);
-            const float4 c1 = *reinterpret_cast<const float4*>(p + 4);
-            lo.x += c0.x; lo.y += c0.y; lo.z += c0.z; lo.w += c0.w;
-            hi.x += c1.x; hi.y += c1.y; hi.z += c1.z; hi.w += c1.w;
-          }
-          *reinterpret_cast<float4*>(p) = lo;
-          *reinterpret_cast<float4*>(p + 4) = hi;
-        } else {
-          __nv_bfloat16* p = reinterpret_cast<__nv_bfloat16*>(a.C) + row * a.ldc + col;
-          if (a.accumulate) {
-            const uint4 c = *reinterpret_cast<const uint4*>(p);
-            acc[0] += bf16_lo(c.x); acc[1] += bf16_hi(c.x);
-            acc[2] += bf16_lo(c.y); acc[3] += bf16_hi(c.y);
-            acc[4] += bf16_lo(c.z); acc[5] += bf16_hi(c.z);
-            acc[6] += bf16_lo(c.w); acc[7] += bf16_hi(c.w);
-          }
-          uint4 o4;
-          o4.x = pack_bf16(acc[0], acc[1]);
-          o4.y = pack_bf16(acc[2], acc[3]);
-          o4.z = pack_bf16(acc[4], acc[5]);
-          o4.w = pack_bf16(acc[6], acc[7]);
-          *reinterpret_cast<uint4*>(p) = o4;
-        }
-      }
-    }
-  }
 }
 
 // ------------------------------------------------------------------------------------------
@@ -901,6 +912,27 @@ int make_tensor_map_2d(CUtensorMap* map, const void* base, uint64_t inner, uint6
   cuuint32_t box[2] = {box_inner, box_outer};
   cuuint32_t estr[2] = {1, 1};
   CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides,
+                  box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : (int)r;
+}
+
+int make_tensor_map_mn3d(CUtensorMap* map, const void* base, uint64_t mn_extent, uint64_t k_rows,
+                         uint64_t pitch_bytes, uint32_t blocks_per_box) {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres);
+    if (e != cudaSuccess || p == nullptr) return -1;
+    fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  if (mn_extent % 64 != 0) return -2;
+  cuuint64_t dims[3] = {64, k_rows, mn_extent / 64};
+  cuuint64_t strides[2] = {pitch_bytes, 128};
+  cuuint32_t box[3] = {64, (cuuint32_t)kBK, blocks_per_box};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides,
                   box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? 0 : (int)r;

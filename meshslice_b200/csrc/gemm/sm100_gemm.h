@@ -26,9 +26,8 @@ constexpr int kBK = 64;
 #endif
 constexpr int kStages = MSB_STAGES;
 constexpr int kMaxPeers = 8;
-constexpr int kGemmThreads = 224;  // 7 warps: TMA, MMA, 4x epilogue, communication
-constexpr int kCommBufBytes = 7168;
-constexpr int kCommBufs = 2;
+constexpr int kAuxWarps = 2;       // communication / reduce warps per CTA
+constexpr int kGemmThreads = 32 * (6 + kAuxWarps);  // TMA, MMA, 4x epilogue, kAuxWarps x communication
 constexpr int kEpiStageBytes = 32 * 128;  // per epilogue warp: 32 rows x 64 bf16 columns, 128-byte swizzled
 
 // Error codes written to the status word (first error wins).
@@ -90,6 +89,8 @@ struct GemmArgs {
   int M, N, K;
   int a_mn_major;  // 0: A stored [M,K] row-major; 1: A stored [K,M] row-major
   int b_mn_major;  // 0: B stored [N,K] row-major; 1: B stored [K,N] row-major
+  int a_map3d;     // the tensor map of an MN-major A / B is the 3-D form of make_tensor_map_mn3d
+  int b_map3d;
   // ---- local epilogue (used when push_n == 0) ----
   void* C;
   int64_t ldc;
@@ -113,10 +114,12 @@ struct GemmArgs {
   int n_chunks;
   int skip_comm;               // 1: this launch moves no data (the chunks were filled earlier)
   uint32_t* chunk_flags;       // [n_chunks] local flags, bumped by every contributing CTA
-  int a_flag_mode;             // 0: none, 1: flag a_flag_base + slice(tile), 2: all of [base, base+count)
+  int a_flag_mode;             // 0: none, 1: flag a_flag_base + slice(tile), 2: all of [base, base+count),
+                               // 3: K panels (below), 4 (B only): flag b_flag_base + n_block / b_nchunk
   int a_flag_base, a_flag_count;
   int b_flag_mode;
   int b_flag_base, b_flag_count;
+  int b_nchunk;                // flag mode 4: 256-column blocks of B per chunk (>= 1)
   // flag mode 3 ("K panels", the SUMMA / ring schedules): the operand arrives in panels of the
   // contraction dimension; k-block kb needs flag base + kb / kpanel, which counts to kp_target
   int a_kpanel, b_kpanel;      // 64-wide k-blocks per panel
@@ -152,6 +155,8 @@ struct GemmArgs {
   uint32_t* go_flag;           // local: set to epoch by CTA 0 once all peers have arrived
   uint32_t* done_counter;      // local: CTAs that finished their transfers (monotonic)
   uint32_t done_target;
+  // ---- tuning of the plain (two-CTA) kernel ----
+  int stages;                  // smem pipeline stages: 6 or 7
   // ---- status ----
   uint32_t* status;            // [4]: code, blockIdx, detail, detail2
   uint64_t timeout_ns;
@@ -172,6 +177,13 @@ cudaError_t launch_sm100_gemm2(const CUtensorMap& tma_a, const CUtensorMap& tma_
 // `outer` the number of rows, `pitch_bytes` the row pitch.  Returns 0 on success.
 int make_tensor_map_2d(CUtensorMap* map, const void* base, uint64_t inner, uint64_t outer,
                        uint64_t pitch_bytes, uint32_t box_inner, uint32_t box_outer);
+
+// Tensor map of an MN-major operand (stored [k_rows, mn_extent] row-major, mn_extent % 64 == 0) as
+// {64 elements, k_rows, mn_extent / 64 blocks}: one box of {64, kBK, blocks_per_box} fills the
+// shared-memory layout of `blocks_per_box` consecutive 64-wide blocks with ONE TMA instruction.
+// Returns 0 on success (callers fall back to the 2-D map and one instruction per block).
+int make_tensor_map_mn3d(CUtensorMap* map, const void* base, uint64_t mn_extent, uint64_t k_rows,
+                         uint64_t pitch_bytes, uint32_t blocks_per_box);
 
 size_t sm100_gemm_smem_bytes();
 

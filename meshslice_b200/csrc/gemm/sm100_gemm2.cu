@@ -5,7 +5,8 @@
 // per stage, so six stages fit) and owns the 128 accumulator rows that land in its own TMEM.  Only
 // the leader CTA (even rank) issues MMAs; it reads both CTAs' shared memory.  Synchronisation:
 //   full[stage]    lives in the leader; both CTAs' TMA loads complete on it (the .cta_group::2
-//                  load form with the leader barrier's cluster address)
+//                  load form with the leader barrier's cluster address); two arrivals: the leader's
+//                  A producer and B producer each announce their operand's bytes
 //   empty[stage]   one per CTA; the leader commits to its own and to the peer's (mapa address)
 //   tfull[acc]     one per CTA, committed by the leader to both
 //   tempty[acc]    lives in the leader, 256 arrivals: 128 local, 128 from the peer's epilogue
@@ -19,13 +20,10 @@ namespace msb {
 
 namespace {
 
-constexpr int kStages2 = 6;
 constexpr uint32_t kAStage2 = kBM * kBK * 2;        // 16 KiB: this CTA's 128 rows of A
 constexpr uint32_t kBStage2 = (kBN / 2) * kBK * 2;  // 16 KiB: this CTA's 128 columns of B
-constexpr uint32_t kSmemB2 = kStages2 * kAStage2;
-constexpr uint32_t kSmemBar2 = kSmemB2 + kStages2 * kBStage2;
-constexpr uint32_t kSmemAlloc2 = kSmemBar2 + 256 + 1024;
-constexpr int kThreads2 = 192;
+constexpr uint32_t smem_alloc2(int stages) { return stages * (kAStage2 + kBStage2) + 256 + 1024; }
+constexpr int kThreads2 = 224;   // warps: A producer, MMA, 4x epilogue, B producer
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
   uint32_t r;
@@ -50,6 +48,14 @@ __device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorM
       "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
       " [%0], [%1, {%3, %4}], [%2];"
       ::"r"(smem_u32(smem_dst)), "l"(map), "r"(leader_bar), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_3d_pair(void* smem_dst, const CUtensorMap* map, uint32_t leader_bar,
+                                                 int32_t x, int32_t y, int32_t z) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(map), "r"(leader_bar), "r"(x), "r"(y), "r"(z)
       : "memory");
 }
 __device__ __forceinline__ void umma_f16_pair(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc,
@@ -103,7 +109,9 @@ __device__ __forceinline__ void store32(void* base, int64_t ld, bool fp32, bool 
         *reinterpret_cast<float4*>(p + i) = o;
       }
     } else {
-      for (int i = 0; i < nvalid; ++i) p[i] = accumulate ? p[i] + v[i] : v[i];
+#pragma unroll
+      for (int i = 0; i < 32; ++i)
+        if (i < nvalid) p[i] = accumulate ? p[i] + v[i] : v[i];
     }
   } else {
     __nv_bfloat16* p = reinterpret_cast<__nv_bfloat16*>(base) + row * ld + col0;
@@ -126,7 +134,9 @@ __device__ __forceinline__ void store32(void* base, int64_t ld, bool fp32, bool 
         *reinterpret_cast<uint4*>(p + i) = o;
       }
     } else {
-      for (int i = 0; i < nvalid; ++i) {
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        if (i >= nvalid) continue;
         float x = v[i];
         if (accumulate) x += __bfloat162float(p[i]);
         p[i] = __float2bfloat16_rn(x);
@@ -148,12 +158,15 @@ __device__ __forceinline__ void tile2(int t, int tiles_m2, int tiles_n, int grou
 
 }  // namespace
 
+template <int kStages2>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads2, 1)
 sm100_gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                    const __grid_constant__ GemmArgs a) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
+  constexpr uint32_t kSmemB2 = kStages2 * kAStage2;
+  constexpr uint32_t kSmemBar2 = kSmemB2 + kStages2 * kBStage2;
   uint8_t* sA = smem;
   uint8_t* sB = smem + kSmemB2;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kSmemBar2);
@@ -177,7 +190,7 @@ sm100_gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_const
     tma_prefetch_desc(&tma_a);
     tma_prefetch_desc(&tma_b);
     for (int i = 0; i < kStages2; ++i) {
-      mbar_init(full_bar + i, 1);
+      mbar_init(full_bar + i, 2);    // the leader's two producers announce their operand's bytes
       mbar_init(empty_bar + i, 1);
     }
     for (int i = 0; i < 2; ++i) {
@@ -197,9 +210,13 @@ sm100_gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_const
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (warp == 0) {
-    // ===================== TMA producer (both CTAs) =====================
+  if (warp == 0 || warp == 6) {
+    // ===================== TMA producers (both CTAs): warp 0 loads A, warp 6 loads B ==========
+    // One thread issuing every load of a stage is what bounded the tensor pipe with MN-major
+    // operands (two boxes per operand): the operands have a producer each, and an MN-major
+    // operand is one 3-D box when its extent allows it.
     if (lane == 0) {
+      const bool is_a = warp == 0;
       uint32_t stage = 0, phase = 0;
       bool ok = true;
       for (int t = cluster_id; t < num_tiles && ok; t += n_clusters) {
@@ -214,22 +231,30 @@ sm100_gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_const
             break;
           }
           const uint32_t fb = mapa_u32(smem_u32(full_bar + stage), 0);   // the leader's barrier
-          if (rank == 0) mbar_expect_tx(full_bar + stage, 2 * (kAStage2 + kBStage2));
-          uint8_t* da = sA + stage * kAStage2;
-          uint8_t* db = sB + stage * kBStage2;
-          if (!a.a_mn_major) {
-            tma_load_2d_pair(da, &tma_a, fb, kb * kBK, row_a);
-          } else {
+          if (is_a) {
+            if (rank == 0) mbar_expect_tx(full_bar + stage, 2 * kAStage2);
+            uint8_t* da = sA + stage * kAStage2;
+            if (!a.a_mn_major) {
+              tma_load_2d_pair(da, &tma_a, fb, kb * kBK, row_a);
+            } else if (a.a_map3d) {
+              tma_load_3d_pair(da, &tma_a, fb, 0, kb * kBK, row_a >> 6);
+            } else {
 #pragma unroll
-            for (int j = 0; j < kBM / 64; ++j)
-              tma_load_2d_pair(da + j * (kBK * 128), &tma_a, fb, row_a + j * 64, kb * kBK);
-          }
-          if (!a.b_mn_major) {
-            tma_load_2d_pair(db, &tma_b, fb, kb * kBK, col_b);
+              for (int j = 0; j < kBM / 64; ++j)
+                tma_load_2d_pair(da + j * (kBK * 128), &tma_a, fb, row_a + j * 64, kb * kBK);
+            }
           } else {
+            if (rank == 0) mbar_expect_tx(full_bar + stage, 2 * kBStage2);
+            uint8_t* db = sB + stage * kBStage2;
+            if (!a.b_mn_major) {
+              tma_load_2d_pair(db, &tma_b, fb, kb * kBK, col_b);
+            } else if (a.b_map3d) {
+              tma_load_3d_pair(db, &tma_b, fb, 0, kb * kBK, col_b >> 6);
+            } else {
 #pragma unroll
-            for (int j = 0; j < kBN / 128; ++j)
-              tma_load_2d_pair(db + j * (kBK * 128), &tma_b, fb, col_b + j * 64, kb * kBK);
+              for (int j = 0; j < kBN / 128; ++j)
+                tma_load_2d_pair(db + j * (kBK * 128), &tma_b, fb, col_b + j * 64, kb * kBK);
+            }
           }
           if (++stage == kStages2) { stage = 0; phase ^= 1; }
         }
@@ -323,6 +348,7 @@ sm100_gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_const
 #pragma unroll
           for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
           if (bias != nullptr) {
+#pragma unroll
             for (int i = 0; i < 32; ++i)
               if (i < nvalid) v[i] += __bfloat162float(bias[col0 + i]);
           }
@@ -345,22 +371,30 @@ sm100_gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_const
     asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
 }
 
-cudaError_t launch_sm100_gemm2(const CUtensorMap& tma_a, const CUtensorMap& tma_b, const GemmArgs& args,
-                               int grid, cudaStream_t stream) {
+template <int kSt>
+static cudaError_t launch2(const CUtensorMap& tma_a, const CUtensorMap& tma_b, const GemmArgs& args, int grid,
+                           cudaStream_t stream) {
   static bool configured[64] = {false};
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return e;
+  constexpr int smem = (int)smem_alloc2(kSt);
   if (dev < 64 && !configured[dev]) {
-    e = cudaFuncSetAttribute(sm100_gemm2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemAlloc2);
+    e = cudaFuncSetAttribute(sm100_gemm2_kernel<kSt>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return e;
     configured[dev] = true;
   }
+  // the cluster shape (2,1,1) is part of the kernel's definition
+  sm100_gemm2_kernel<kSt><<<grid, kThreads2, smem, stream>>>(tma_a, tma_b, args);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_sm100_gemm2(const CUtensorMap& tma_a, const CUtensorMap& tma_b, const GemmArgs& args,
+                               int grid, cudaStream_t stream) {
   grid &= ~1;
   if (grid < 2) grid = 2;
-  // the cluster shape (2,1,1) is part of the kernel's definition
-  sm100_gemm2_kernel<<<grid, kThreads2, kSmemAlloc2, stream>>>(tma_a, tma_b, args);
-  return cudaGetLastError();
+  if (args.stages == 6) return launch2<6>(tma_a, tma_b, args, grid, stream);
+  return launch2<7>(tma_a, tma_b, args, grid, stream);
 }
 
 }  // namespace msb

@@ -4,12 +4,74 @@
 #include "ops.h"
 
 #include <cuda_bf16.h>
+#include <string.h>
 
 namespace msb {
 
 namespace {
 
 constexpr int kLnThreads = 256;
+
+// ---- cross-GPU row exchange (see RowExchange in ops.h) ----
+__device__ __forceinline__ void ex_red_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ex_ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint64_t ex_timer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+// Thread 0 of the CTA publishes "this CTA's rows are written" on every peer.
+__device__ __forceinline__ void ex_signal(const RowExchange& ex) {
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    for (int p = 0; p < ex.n; ++p)
+      if (p != ex.me) ex_red_release_sys(ex.counter[p], 1u);
+  }
+}
+// All threads return true once every CTA of every peer has published; false after the deadline
+// (the status word then says which kernel gave up: code 20 + kind).
+__device__ __forceinline__ bool ex_wait(const RowExchange& ex, uint32_t kind) {
+  int ok = 1;
+  if (threadIdx.x == 0) {
+    const uint64_t t0 = ex_timer_ns();
+    uint32_t it = 0;
+    while ((int32_t)(ex_ld_acquire_sys(ex.my_counter) - ex.target) < 0) {
+      if ((++it & 0xf) == 0) {
+        if (ex_timer_ns() - t0 > ex.timeout_ns) {
+          ok = 0;
+          if (atomicCAS(ex.status, 0u, 20u + kind) == 0u) {
+            ex.status[1] = blockIdx.x;
+            ex.status[2] = ex_ld_acquire_sys(ex.my_counter);
+            ex.status[3] = ex.target;
+          }
+          break;
+        }
+        __nanosleep(128);
+      }
+    }
+  }
+  return __syncthreads_and(ok) != 0;
+}
+// Writes this GPU's W-float contribution of one row into its slot on every GPU of the group.
+template <int W>
+__device__ __forceinline__ void ex_put(const RowExchange& ex, int row, const float (&v)[W]) {
+  for (int p = 0; p < ex.n; ++p) {
+    float* d = ex.dst[p] + (int64_t)row * W;
+#pragma unroll
+    for (int i = 0; i < W; ++i) d[i] = v[i];
+  }
+}
+// Source q's contribution of one row (L1 bypassed: peers wrote it).
+__device__ __forceinline__ float ex_get(const RowExchange& ex, int q, int row, int width, int i) {
+  return __ldcg(ex.slots + q * ex.stride + (int64_t)row * width + i);
+}
 
 __device__ __forceinline__ float bf_lo(uint32_t v) { return __uint_as_float(v << 16); }
 __device__ __forceinline__ float bf_hi(uint32_t v) { return __uint_as_float(v & 0xffff0000u); }
@@ -80,9 +142,15 @@ __global__ void __launch_bounds__(kLnThreads)
 ln_fwd_kernel(int mode, const uint4* __restrict__ x, const uint4* __restrict__ res,
               uint4* __restrict__ h_out, uint4* __restrict__ y, const uint4* __restrict__ gamma,
               const uint4* __restrict__ beta, float* __restrict__ stats,
-              float* __restrict__ mean_rstd, int rows, int cols, int total_cols, float eps) {
+              float* __restrict__ mean_rstd, int rows, int cols, int total_cols, float eps,
+              const __grid_constant__ RowExchange ex) {
   __shared__ float red[64];
   const int nvec = cols >> 3;
+  // With an exchange (ex.n > 0) mode 1 writes the partial statistics of its rows to every GPU of
+  // the mesh row and counts one arrival per CTA on every peer; mode 2 first waits (bounded) for
+  // the arrivals of all peers' CTAs and then sums the sources' statistics in fixed order.
+  const bool exchange = ex.n > 0;
+  if (exchange && mode == 2 && !ex_wait(ex, 0u)) return;
   for (int row = blockIdx.x; row < rows; row += gridDim.x) {
     float vals[MAXV][8];
     float s = 0.f, ss = 0.f;
@@ -109,12 +177,26 @@ ln_fwd_kernel(int mode, const uint4* __restrict__ x, const uint4* __restrict__ r
     }
     float mean, rstd;
     if (mode == 2) {
-      s = stats[2 * row];
-      ss = stats[2 * row + 1];
+      if (exchange) {
+        s = 0.f;
+        ss = 0.f;
+        for (int q = 0; q < ex.n; ++q) { s += ex_get(ex, q, row, 2, 0); ss += ex_get(ex, q, row, 2, 1); }
+      } else {
+        s = stats[2 * row];
+        ss = stats[2 * row + 1];
+      }
     } else {
       block_sum2(s, ss, red);
       if (mode == 1) {
-        if (threadIdx.x == 0) { stats[2 * row] = s; stats[2 * row + 1] = ss; }
+        if (threadIdx.x == 0) {
+          if (exchange) {
+            const float v2[2] = {s, ss};
+            ex_put<2>(ex, row, v2);
+          } else {
+            stats[2 * row] = s;
+            stats[2 * row + 1] = ss;
+          }
+        }
         continue;
       }
     }
@@ -142,6 +224,7 @@ ln_fwd_kernel(int mode, const uint4* __restrict__ x, const uint4* __restrict__ r
       }
     }
   }
+  if (exchange && mode == 1) ex_signal(ex);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -153,7 +236,7 @@ ln_bwd_kernel(int mode, const uint4* __restrict__ dy, const uint4* __restrict__ 
               const uint4* __restrict__ gamma, const float* __restrict__ mean_rstd,
               const uint4* __restrict__ dres, uint4* __restrict__ dx, float* __restrict__ stats,
               float* __restrict__ dgamma, float* __restrict__ dbeta, int rows, int cols,
-              int total_cols) {
+              int total_cols, const __grid_constant__ RowExchange ex) {
   __shared__ float red[64];
   const int nvec = cols >> 3;
   float accg[MAXV][8], accb[MAXV][8];
@@ -161,6 +244,9 @@ ln_bwd_kernel(int mode, const uint4* __restrict__ dy, const uint4* __restrict__ 
   for (int k = 0; k < MAXV; ++k)
 #pragma unroll
     for (int i = 0; i < 8; ++i) { accg[k][i] = 0.f; accb[k][i] = 0.f; }
+  // exchange of the partial sums with the GPUs of the mesh row: see ln_fwd_kernel
+  const bool exchange = ex.n > 0;
+  if (exchange && mode == 2 && !ex_wait(ex, 1u)) return;
   const bool want_param_grads = mode != 2 && dgamma != nullptr;
 
   for (int row = blockIdx.x; row < rows; row += gridDim.x) {
@@ -187,12 +273,26 @@ ln_bwd_kernel(int mode, const uint4* __restrict__ dy, const uint4* __restrict__ 
       }
     }
     if (mode == 2) {
-      s1 = stats[2 * row];
-      s2 = stats[2 * row + 1];
+      if (exchange) {
+        s1 = 0.f;
+        s2 = 0.f;
+        for (int q = 0; q < ex.n; ++q) { s1 += ex_get(ex, q, row, 2, 0); s2 += ex_get(ex, q, row, 2, 1); }
+      } else {
+        s1 = stats[2 * row];
+        s2 = stats[2 * row + 1];
+      }
     } else {
       block_sum2(s1, s2, red);
       if (mode == 1) {
-        if (threadIdx.x == 0) { stats[2 * row] = s1; stats[2 * row + 1] = s2; }
+        if (threadIdx.x == 0) {
+          if (exchange) {
+            const float v2[2] = {s1, s2};
+            ex_put<2>(ex, row, v2);
+          } else {
+            stats[2 * row] = s1;
+            stats[2 * row + 1] = s2;
+          }
+        }
         continue;
       }
     }
@@ -214,6 +314,7 @@ ln_bwd_kernel(int mode, const uint4* __restrict__ dy, const uint4* __restrict__ 
       }
     }
   }
+  if (exchange && mode == 1) ex_signal(ex);
   if (want_param_grads) {
 #pragma unroll
     for (int k = 0; k < MAXV; ++k) {
@@ -349,7 +450,7 @@ __global__ void __launch_bounds__(256)
 ce_partial_kernel(const __nv_bfloat16* __restrict__ logits, int64_t ld,
                   const int64_t* __restrict__ targets, int rows, int cols, int col_offset,
                   int vocab, float* __restrict__ row_max, float* __restrict__ row_sumexp,
-                  float* __restrict__ tgt_logit) {
+                  float* __restrict__ tgt_logit, const __grid_constant__ RowExchange ex) {
   __shared__ float red[64];
   const int valid = max(0, min(cols, vocab - col_offset));
   const int nvec = valid >> 3;
@@ -379,23 +480,50 @@ ce_partial_kernel(const __nv_bfloat16* __restrict__ logits, int64_t ld,
     }
     block_sum2(s, dummy, red);
     if (threadIdx.x == 0) {
-      row_max[row] = mx;
-      row_sumexp[row] = s;
       const int64_t t = targets[row] - col_offset;
-      tgt_logit[row] = (t >= 0 && t < valid) ? __bfloat162float(p[t]) : 0.f;
+      const float tl = (t >= 0 && t < valid) ? __bfloat162float(p[t]) : 0.f;
+      if (ex.n > 0) {        // publish (max, sum-exp relative to it, target logit) to the mesh row
+        const float v3[3] = {mx, s, tl};
+        ex_put<3>(ex, row, v3);
+      } else {
+        row_max[row] = mx;
+        row_sumexp[row] = s;
+        tgt_logit[row] = tl;
+      }
     }
   }
+  if (ex.n > 0) ex_signal(ex);
 }
 
 __global__ void __launch_bounds__(256)
 ce_grad_kernel(__nv_bfloat16* __restrict__ logits, int64_t ld, const int64_t* __restrict__ targets,
                int rows, int cols, int col_offset, int vocab, const float* __restrict__ gmax,
-               const float* __restrict__ gsumexp, float scale) {
+               const float* __restrict__ gsumexp, float scale, float* __restrict__ row_loss,
+               const __grid_constant__ RowExchange ex) {
   const int nvec = cols >> 3;
+  if (ex.n > 0 && !ex_wait(ex, 2u)) return;
   for (int row = blockIdx.x; row < rows; row += gridDim.x) {
     __nv_bfloat16* p = logits + (int64_t)row * ld;
     uint4* pv = reinterpret_cast<uint4*>(p);
-    const float mx = gmax[row], inv = scale / gsumexp[row];
+    float mx, se;
+    if (ex.n > 0) {
+      // combine the vocabulary slices of the mesh row in fixed order: global max, sum of the
+      // rescaled partial sums, the one non-zero target logit; every GPU of the row gets the same
+      mx = -INFINITY;
+      for (int q = 0; q < ex.n; ++q) mx = fmaxf(mx, ex_get(ex, q, row, 3, 0));
+      se = 0.f;
+      float tl = 0.f;
+      for (int q = 0; q < ex.n; ++q) {
+        const float sq = ex_get(ex, q, row, 3, 1);
+        if (sq > 0.f) se += sq * __expf(ex_get(ex, q, row, 3, 0) - mx);
+        tl += ex_get(ex, q, row, 3, 2);
+      }
+      if (threadIdx.x == 0 && row_loss != nullptr) row_loss[row] = __logf(se) + mx - tl;
+    } else {
+      mx = gmax[row];
+      se = gsumexp[row];
+    }
+    const float inv = scale / se;
     const int64_t t = targets[row] - col_offset;
     for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
       float f[8];
@@ -489,11 +617,21 @@ inline int grid_for(int64_t n, int threads, int cap = 148 * 16) {
 // ------------------------------------------------------------------------------------------
 // launchers
 // ------------------------------------------------------------------------------------------
+int ce_grid(int rows) { return rows < 148 * 8 ? rows : 148 * 8; }
+
+int ln_grid(int backward, int rows) {
+  const int cap = backward ? 148 * 8 : 148 * 16;
+  return rows < cap ? rows : cap;
+}
+
 cudaError_t ln_fwd(int mode, const void* x, const void* res, void* h_out, void* y,
                    const void* gamma, const void* beta, float* stats, float* mean_rstd, int rows,
-                   int cols, int total_cols, float eps, cudaStream_t stream) {
+                   int cols, int total_cols, float eps, cudaStream_t stream, const RowExchange* exch) {
   if (cols % 8 != 0 || cols > 8 * kLnThreads * 8) return cudaErrorInvalidValue;
-  const int grid = rows < 148 * 16 ? rows : 148 * 16;
+  if (exch != nullptr && mode != 1 && mode != 2) return cudaErrorInvalidValue;
+  const int grid = ln_grid(0, rows);
+  RowExchange ex;
+  if (exch != nullptr) ex = *exch; else memset(&ex, 0, sizeof(ex));
   auto X = reinterpret_cast<const uint4*>(x);
   auto R = reinterpret_cast<const uint4*>(res);
   auto H = reinterpret_cast<uint4*>(h_out);
@@ -503,21 +641,25 @@ cudaError_t ln_fwd(int mode, const void* x, const void* res, void* h_out, void* 
   const int threads = ln_threads(cols);
   const int nvec_per_thread = (cols / 8 + threads - 1) / threads;
   if (nvec_per_thread <= 1)
-    ln_fwd_kernel<1><<<grid, threads, 0, stream>>>(mode, X, R, H, Y, G, B, stats, mean_rstd, rows, cols, total_cols, eps);
+    ln_fwd_kernel<1><<<grid, threads, 0, stream>>>(mode, X, R, H, Y, G, B, stats, mean_rstd, rows, cols, total_cols, eps, ex);
   else if (nvec_per_thread <= 2)
-    ln_fwd_kernel<2><<<grid, threads, 0, stream>>>(mode, X, R, H, Y, G, B, stats, mean_rstd, rows, cols, total_cols, eps);
+    ln_fwd_kernel<2><<<grid, threads, 0, stream>>>(mode, X, R, H, Y, G, B, stats, mean_rstd, rows, cols, total_cols, eps, ex);
   else if (nvec_per_thread <= 4)
-    ln_fwd_kernel<4><<<grid, threads, 0, stream>>>(mode, X, R, H, Y, G, B, stats, mean_rstd, rows, cols, total_cols, eps);
+    ln_fwd_kernel<4><<<grid, threads, 0, stream>>>(mode, X, R, H, Y, G, B, stats, mean_rstd, rows, cols, total_cols, eps, ex);
   else
-    ln_fwd_kernel<8><<<grid, threads, 0, stream>>>(mode, X, R, H, Y, G, B, stats, mean_rstd, rows, cols, total_cols, eps);
+    ln_fwd_kernel<8><<<grid, threads, 0, stream>>>(mode, X, R, H, Y, G, B, stats, mean_rstd, rows, cols, total_cols, eps, ex);
   return cudaGetLastError();
 }
 
 cudaError_t ln_bwd(int mode, const void* dy, const void* h, const void* gamma,
                    const float* mean_rstd, const void* dres, void* dx, float* stats, float* dgamma,
-                   float* dbeta, int rows, int cols, int total_cols, cudaStream_t stream) {
+                   float* dbeta, int rows, int cols, int total_cols, cudaStream_t stream,
+                   const RowExchange* exch) {
   if (cols % 8 != 0 || cols > 8 * kLnThreads * 8) return cudaErrorInvalidValue;
-  const int grid = rows < 148 * 8 ? rows : 148 * 8;
+  if (exch != nullptr && mode != 1 && mode != 2) return cudaErrorInvalidValue;
+  const int grid = ln_grid(1, rows);
+  RowExchange ex;
+  if (exch != nullptr) ex = *exch; else memset(&ex, 0, sizeof(ex));
   auto DY = reinterpret_cast<const uint4*>(dy);
   auto H = reinterpret_cast<const uint4*>(h);
   auto G = reinterpret_cast<const uint4*>(gamma);
@@ -526,13 +668,13 @@ cudaError_t ln_bwd(int mode, const void* dy, const void* h, const void* gamma,
   const int threads = ln_threads(cols);
   const int nvec_per_thread = (cols / 8 + threads - 1) / threads;
   if (nvec_per_thread <= 1)
-    ln_bwd_kernel<1><<<grid, threads, 0, stream>>>(mode, DY, H, G, mean_rstd, DR, DX, stats, dgamma, dbeta, rows, cols, total_cols);
+    ln_bwd_kernel<1><<<grid, threads, 0, stream>>>(mode, DY, H, G, mean_rstd, DR, DX, stats, dgamma, dbeta, rows, cols, total_cols, ex);
   else if (nvec_per_thread <= 2)
-    ln_bwd_kernel<2><<<grid, threads, 0, stream>>>(mode, DY, H, G, mean_rstd, DR, DX, stats, dgamma, dbeta, rows, cols, total_cols);
+    ln_bwd_kernel<2><<<grid, threads, 0, stream>>>(mode, DY, H, G, mean_rstd, DR, DX, stats, dgamma, dbeta, rows, cols, total_cols, ex);
   else if (nvec_per_thread <= 4)
-    ln_bwd_kernel<4><<<grid, threads, 0, stream>>>(mode, DY, H, G, mean_rstd, DR, DX, stats, dgamma, dbeta, rows, cols, total_cols);
+    ln_bwd_kernel<4><<<grid, threads, 0, stream>>>(mode, DY, H, G, mean_rstd, DR, DX, stats, dgamma, dbeta, rows, cols, total_cols, ex);
   else
-    ln_bwd_kernel<8><<<grid, threads, 0, stream>>>(mode, DY, H, G, mean_rstd, DR, DX, stats, dgamma, dbeta, rows, cols, total_cols);
+    ln_bwd_kernel<8><<<grid, threads, 0, stream>>>(mode, DY, H, G, mean_rstd, DR, DX, stats, dgamma, dbeta, rows, cols, total_cols, ex);
   return cudaGetLastError();
 }
 
@@ -577,18 +719,22 @@ cudaError_t sumsq(const void* x, int is_fp32, int64_t n, float* out, cudaStream_
 
 cudaError_t ce_partial(const void* logits, int64_t ld, const int64_t* targets, int rows, int cols,
                        int col_offset, int vocab, float* row_max, float* row_sumexp,
-                       float* tgt_logit, cudaStream_t stream) {
+                       float* tgt_logit, cudaStream_t stream, const RowExchange* exch) {
+  RowExchange ex;
+  if (exch != nullptr) ex = *exch; else memset(&ex, 0, sizeof(ex));
   if (ld % 8) return cudaErrorInvalidValue;
-  const int grid = rows < 148 * 8 ? rows : 148 * 8;
-  ce_partial_kernel<<<grid, 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(logits), ld, targets, rows, cols, col_offset, vocab, row_max, row_sumexp, tgt_logit);
+  const int grid = ce_grid(rows);
+  ce_partial_kernel<<<grid, 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(logits), ld, targets, rows, cols, col_offset, vocab, row_max, row_sumexp, tgt_logit, ex);
   return cudaGetLastError();
 }
 cudaError_t ce_grad(void* logits, int64_t ld, const int64_t* targets, int rows, int cols,
                     int col_offset, int vocab, const float* gmax, const float* gsumexp, float scale,
-                    cudaStream_t stream) {
+                    cudaStream_t stream, float* row_loss, const RowExchange* exch) {
+  RowExchange ex;
+  if (exch != nullptr) ex = *exch; else memset(&ex, 0, sizeof(ex));
   if (ld % 8 || cols % 8) return cudaErrorInvalidValue;
-  const int grid = rows < 148 * 8 ? rows : 148 * 8;
-  ce_grad_kernel<<<grid, 256, 0, stream>>>(reinterpret_cast<__nv_bfloat16*>(logits), ld, targets, rows, cols, col_offset, vocab, gmax, gsumexp, scale);
+  const int grid = ce_grid(rows);
+  ce_grad_kernel<<<grid, 256, 0, stream>>>(reinterpret_cast<__nv_bfloat16*>(logits), ld, targets, rows, cols, col_offset, vocab, gmax, gsumexp, scale, row_loss, ex);
   return cudaGetLastError();
 }
 

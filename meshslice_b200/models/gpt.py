@@ -177,17 +177,29 @@ class GPTModel:
         y = self.ln_f.forward(x, delta)
         logits = self.head.forward(y)                                    # [T/R, Vp/C]
         vc = cfg.vocab_padded // m.C
-        parts = {k: F.ce_partial(logits.shards[k], targets.shards[k], k[1] * vc, cfg.vocab) for k in m.coords()}
-        mx = ShardedTensor(m, {k: v[0] for k, v in parts.items()})
-        gmax = m.all_reduce(mx, "col", op="max")
-        se = ShardedTensor(m, {k: parts[k][1] * torch.exp(parts[k][0] - gmax.shards[k]) for k in m.coords()})
-        packed = m.all_reduce(ShardedTensor(m, {k: torch.stack([se.shards[k], parts[k][2]]) for k in m.coords()}), "col")
-        loss = ShardedTensor(m, {k: (torch.log(packed.shards[k][0]) + gmax.shards[k] - packed.shards[k][1]).sum()
-                                 / n_tokens_global for k in m.coords()})
-        # backward
-        for k in m.coords():
-            F.ce_grad_(logits.shards[k], targets.shards[k], k[1] * vc, cfg.vocab, gmax.shards[k],
-                       packed.shards[k][0].contiguous(), 1.0 / n_tokens_global)
+        ex = getattr(getattr(m, "engine", None), "row_exchange", None)
+        k0 = l0 = None
+        if len(logits.shards) == 1:
+            (k0, l0), = logits.shards.items()
+        if ex is not None and l0 is not None and l0.is_cuda:
+            # max / sum-exp / target logit of the vocabulary slices travel inside the two kernels
+            from .. import _native
+            prod, cons = ex.next(l0.shape[0], _native.load().ce_grid(l0.shape[0]))
+            F.ce_partial(l0, targets.shards[k0], k0[1] * vc, cfg.vocab, exch=prod)
+            row_loss = F.ce_grad_exchanged_(l0, targets.shards[k0], k0[1] * vc, cfg.vocab, 1.0 / n_tokens_global, cons)
+            loss = ShardedTensor(m, {k0: row_loss.sum() / n_tokens_global})
+        else:
+            parts = {k: F.ce_partial(logits.shards[k], targets.shards[k], k[1] * vc, cfg.vocab) for k in m.coords()}
+            mx = ShardedTensor(m, {k: v[0] for k, v in parts.items()})
+            gmax = m.all_reduce(mx, "col", op="max")
+            se = ShardedTensor(m, {k: parts[k][1] * torch.exp(parts[k][0] - gmax.shards[k]) for k in m.coords()})
+            packed = m.all_reduce(ShardedTensor(m, {k: torch.stack([se.shards[k], parts[k][2]]) for k in m.coords()}), "col")
+            loss = ShardedTensor(m, {k: (torch.log(packed.shards[k][0]) + gmax.shards[k] - packed.shards[k][1]).sum()
+                                     / n_tokens_global for k in m.coords()})
+            # backward
+            for k in m.coords():
+                F.ce_grad_(logits.shards[k], targets.shards[k], k[1] * vc, cfg.vocab, gmax.shards[k],
+                           packed.shards[k][0].contiguous(), 1.0 / n_tokens_global)
         d = self.head.backward(logits)
         dx = self.ln_f.backward(d)                                       # gradient of x + delta
         dh, dm = dx, dx

@@ -144,6 +144,15 @@ class ShardedLayerNorm:
             h = ShardedTensor(m, {k: v[0] for k, v in outs.items()})
             y = ShardedTensor(m, {k: v[1] for k, v in outs.items()})
             mr = ShardedTensor(m, {k: v[2] for k, v in outs.items()})
+        elif self._exchanger(x) is not None:
+            # statistics travel inside the two kernels (peer stores + arrival counters): no collective
+            (k, xl), = x.shards.items()
+            prod, cons = self._exchange(xl.shape[0], backward=False)
+            hl, _ = F.ln_stats(xl, R(k), exch=prod)
+            h = ShardedTensor(m, {k: hl})
+            outs = {k: F.ln_apply(hl, None, G(k), Bt(k), self.in_dim, self.eps, exch=cons)}
+            y = ShardedTensor(m, {k: v[0] for k, v in outs.items()})
+            mr = ShardedTensor(m, {k: v[1] for k, v in outs.items()})
         else:
             hs = {k: F.ln_stats(x.shards[k], R(k)) for k in m.coords()}
             h = ShardedTensor(m, {k: v[0] for k, v in hs.items()})
@@ -155,6 +164,18 @@ class ShardedLayerNorm:
         self.h = h
         self._saved = (h, mr)
         return y
+
+    def _exchanger(self, t: ShardedTensor):
+        """The mesh's in-kernel row exchange, when it has one and the shard lives on its GPU."""
+        ex = getattr(getattr(self.mesh, "engine", None), "row_exchange", None)
+        if ex is None or len(t.shards) != 1 or not next(iter(t.shards.values())).is_cuda:
+            return None
+        return ex
+
+    def _exchange(self, rows: int, backward: bool):
+        from .. import _native
+        grid = _native.load().ln_grid(1 if backward else 0, rows)
+        return self.mesh.engine.row_exchange.next(rows, grid)
 
     def backward(self, dy: ShardedTensor, dres: Optional[ShardedTensor] = None) -> ShardedTensor:
         """Gradient w.r.t. h; ``dres`` is the gradient that reaches h through the residual path."""
@@ -168,6 +189,12 @@ class ShardedLayerNorm:
         if m.C == 1:
             return ShardedTensor(m, {k: F.ln_bwd_full(dy.shards[k], h.shards[k], G(k), mr.shards[k], DG(k),
                                                       DB(k), DR(k)) for k in m.coords()})
+        if self._exchanger(dy) is not None:
+            (k, dyl), = dy.shards.items()
+            prod, cons = self._exchange(dyl.shape[0], backward=True)
+            F.ln_bwd_stats(dyl, h.shards[k], G(k), mr.shards[k], DG(k), DB(k), exch=prod)
+            return ShardedTensor(m, {k: F.ln_bwd_apply(dyl, h.shards[k], G(k), mr.shards[k], None, self.in_dim,
+                                                       DR(k), exch=cons)})
         stats = ShardedTensor(m, {k: F.ln_bwd_stats(dy.shards[k], h.shards[k], G(k), mr.shards[k], DG(k), DB(k))
                                   for k in m.coords()})
         stats = m.all_reduce(stats, "col")
@@ -190,10 +217,12 @@ class ShardedAttention:
     communication (ShardedLayers.py:141-159).  The reference is non-causal; ``causal=True`` adds
     the decoder mask.  The score matrix is never written to HBM on the GPU path."""
 
-    def __init__(self, mesh: Mesh, n_heads: int, seqlen: int, causal: bool = False):
+    def __init__(self, mesh: Mesh, n_heads: int, seqlen: int, causal: bool = False, allow_fallback: bool = False):
+        """``allow_fallback``: shapes the attention kernel does not cover (head_dim != 128 or
+        seq % 128 != 0) run the eager formulation on the GPU instead of raising."""
         if n_heads % mesh.C:
             raise ValueError("heads must divide over the mesh columns")
-        self.mesh, self.seqlen, self.causal = mesh, seqlen, causal
+        self.mesh, self.seqlen, self.causal, self.allow_fallback = mesh, seqlen, causal, allow_fallback
         self.heads_per_shard = n_heads // mesh.C
         self._saved = None
 
@@ -202,7 +231,8 @@ class ShardedAttention:
         for k, t in x.shards.items():
             if t.shape[0] % self.seqlen:
                 raise ValueError("local tokens must be whole sequences (batch divisible by mesh rows)")
-            outs[k] = F.attention_fwd(t, t.shape[0] // self.seqlen, self.seqlen, self.heads_per_shard, self.causal)
+            outs[k] = F.attention_fwd(t, t.shape[0] // self.seqlen, self.seqlen, self.heads_per_shard, self.causal,
+                                      allow_fallback=self.allow_fallback)
         self._saved = (x, {k: v for k, v in outs.items()})
         return ShardedTensor(self.mesh, {k: v[0] for k, v in outs.items()})
 
@@ -211,7 +241,8 @@ class ShardedAttention:
         self._saved = None
         return ShardedTensor(self.mesh, {
             k: F.attention_bwd(dy.shards[k], t, outs[k][0], outs[k][1], t.shape[0] // self.seqlen, self.seqlen,
-                               self.heads_per_shard, self.causal) for k, t in x.shards.items()})
+                               self.heads_per_shard, self.causal, allow_fallback=self.allow_fallback)
+            for k, t in x.shards.items()})
 
     def parameters(self):
         return []

@@ -30,28 +30,31 @@ def _p(t: Optional[torch.Tensor]) -> int:
 # ----------------------------------------------------------------------------------------------
 # LayerNorm over a possibly column-sharded feature dimension
 # ----------------------------------------------------------------------------------------------
-def ln_stats(x, res) -> Tuple[torch.Tensor, torch.Tensor]:
-    """h = x (+ res); stats[row] = (sum h, sum h^2) over the local columns."""
+def ln_stats(x, res, exch=None) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
+    """h = x (+ res); stats[row] = (sum h, sum h^2) over the local columns.  With ``exch`` (the
+    producer descriptor of a ``RowExchanger``) the kernel publishes the statistics to the GPUs of
+    the mesh row instead of returning them."""
     rows, cols = x.shape
     if x.is_cuda:
         h = torch.empty_like(x) if res is not None else x
-        stats = torch.empty(rows, 2, device=x.device, dtype=torch.float32)
+        stats = None if exch is not None else torch.empty(rows, 2, device=x.device, dtype=torch.float32)
         _C().ln_fwd(1, x.data_ptr(), _p(res), h.data_ptr() if res is not None else 0, 0, 0, 0,
-                    stats.data_ptr(), 0, rows, cols, cols, 0.0, _st())
+                    _p(stats), 0, rows, cols, cols, 0.0, _st(), exch)
         return h, stats
     h = x if res is None else (x.float() + res.float()).to(x.dtype)
     hf = h.float()
     return h, torch.stack([hf.sum(1), (hf * hf).sum(1)], 1)
 
 
-def ln_apply(h, stats, gamma, beta, total_cols: int, eps: float):
-    """y = (h - mean) * rstd * gamma + beta from (all-reduced) statistics."""
+def ln_apply(h, stats, gamma, beta, total_cols: int, eps: float, exch=None):
+    """y = (h - mean) * rstd * gamma + beta from (all-reduced) statistics, or, with ``exch`` (the
+    consumer descriptor), from the statistics the GPUs of the mesh row published."""
     rows, cols = h.shape
     if h.is_cuda:
         y = torch.empty_like(h)
         mr = torch.empty(rows, 2, device=h.device, dtype=torch.float32)
-        _C().ln_fwd(2, h.data_ptr(), 0, 0, y.data_ptr(), _p(gamma), _p(beta), stats.data_ptr(),
-                    mr.data_ptr(), rows, cols, total_cols, eps, _st())
+        _C().ln_fwd(2, h.data_ptr(), 0, 0, y.data_ptr(), _p(gamma), _p(beta), _p(stats),
+                    mr.data_ptr(), rows, cols, total_cols, eps, _st(), exch)
         return y, mr
     mean = stats[:, 0] / total_cols
     var = (stats[:, 1] / total_cols - mean * mean).clamp_min(0)
@@ -79,13 +82,14 @@ def ln_full(x, res, gamma, beta, eps: float):
     return h, y, mr
 
 
-def ln_bwd_stats(dy, h, gamma, mean_rstd, dgamma, dbeta):
-    """stats[row] = (sum g, sum g * xhat), g = dy * gamma; accumulates dgamma / dbeta (fp32)."""
+def ln_bwd_stats(dy, h, gamma, mean_rstd, dgamma, dbeta, exch=None):
+    """stats[row] = (sum g, sum g * xhat), g = dy * gamma; accumulates dgamma / dbeta (fp32).
+    With ``exch`` the sums are published to the mesh row (nothing is returned)."""
     rows, cols = dy.shape
     if dy.is_cuda:
-        stats = torch.empty(rows, 2, device=dy.device, dtype=torch.float32)
+        stats = None if exch is not None else torch.empty(rows, 2, device=dy.device, dtype=torch.float32)
         _C().ln_bwd(1, dy.data_ptr(), h.data_ptr(), _p(gamma), mean_rstd.data_ptr(), 0, 0,
-                    stats.data_ptr(), _p(dgamma), _p(dbeta), rows, cols, cols, _st())
+                    _p(stats), _p(dgamma), _p(dbeta), rows, cols, cols, _st(), exch)
         return stats
     xh = (h.float() - mean_rstd[:, :1]) * mean_rstd[:, 1:]
     d = dy.float()
@@ -97,13 +101,13 @@ def ln_bwd_stats(dy, h, gamma, mean_rstd, dgamma, dbeta):
     return torch.stack([g.sum(1), (g * xh).sum(1)], 1)
 
 
-def ln_bwd_apply(dy, h, gamma, mean_rstd, stats, total_cols: int, dres=None):
+def ln_bwd_apply(dy, h, gamma, mean_rstd, stats, total_cols: int, dres=None, exch=None):
     """dx = rstd * (g - mean(g) - xhat * mean(g * xhat)) (+ dres)."""
     rows, cols = dy.shape
     if dy.is_cuda:
         dx = torch.empty_like(dy)
         _C().ln_bwd(2, dy.data_ptr(), h.data_ptr(), _p(gamma), mean_rstd.data_ptr(), _p(dres),
-                    dx.data_ptr(), stats.data_ptr(), 0, 0, rows, cols, total_cols, _st())
+                    dx.data_ptr(), _p(stats), 0, 0, rows, cols, total_cols, _st(), exch)
         return dx
     rstd = mean_rstd[:, 1:]
     xh = (h.float() - mean_rstd[:, :1]) * rstd
@@ -166,10 +170,24 @@ def _split_qkv(qkv, batch, seq, heads):
     return t[:, :, :, 0], t[:, :, :, 1], t[:, :, :, 2], D  # each [b, s, h, D]
 
 
-def attention_fwd(qkv, batch: int, seq: int, heads: int, causal: bool = False):
+FALLBACKS = {"attention": 0}      # eager-PyTorch runs of an op on CUDA tensors (only with allow_fallback)
+
+
+def _check_attention_shape(qkv, D: int, seq: int, allow_fallback: bool):
+    """The tcgen05 attention kernels need head_dim 128 and seq % 128 == 0.  Any other shape on a GPU
+    would mean a materialised S x S score matrix in eager PyTorch: refuse unless asked for."""
+    if qkv.is_cuda and not (D == 128 and seq % 128 == 0):
+        if not allow_fallback:
+            raise ValueError(f"attention kernel needs head_dim 128 and seq % 128 == 0 (got head_dim {D}, seq {seq}); "
+                             f"pass allow_fallback=True to run the eager PyTorch formulation instead")
+        FALLBACKS["attention"] += 1
+
+
+def attention_fwd(qkv, batch: int, seq: int, heads: int, causal: bool = False, allow_fallback: bool = False):
     """softmax(Q K^T / sqrt(D)) V per (sequence, head).  Returns (out [b*s, heads*D], lse)."""
     q, k, v, D = _split_qkv(qkv, batch, seq, heads)
-    if qkv.is_cuda and hasattr(_C(), "attention_fwd") and D == 128 and seq % 128 == 0:
+    _check_attention_shape(qkv, D, seq, allow_fallback)
+    if qkv.is_cuda and D == 128 and seq % 128 == 0:
         out = torch.empty(batch * seq, heads * D, dtype=qkv.dtype, device=qkv.device)
         lse = torch.empty(batch, heads, seq, dtype=torch.float32, device=qkv.device)
         _C().attention_fwd(qkv.data_ptr(), out.data_ptr(), lse.data_ptr(), batch, seq, heads,
@@ -184,10 +202,12 @@ def attention_fwd(qkv, batch: int, seq: int, heads: int, causal: bool = False):
     return o.permute(0, 2, 1, 3).reshape(batch * seq, heads * D).to(qkv.dtype), lse
 
 
-def attention_bwd(dout, qkv, out, lse, batch: int, seq: int, heads: int, causal: bool = False):
+def attention_bwd(dout, qkv, out, lse, batch: int, seq: int, heads: int, causal: bool = False,
+                  allow_fallback: bool = False):
     """Gradient w.r.t. qkv in the same interleaved layout."""
     q, k, v, D = _split_qkv(qkv, batch, seq, heads)
-    if qkv.is_cuda and hasattr(_C(), "attention_bwd") and D == 128 and seq % 128 == 0:
+    _check_attention_shape(qkv, D, seq, allow_fallback)
+    if qkv.is_cuda and D == 128 and seq % 128 == 0:
         dqkv = torch.empty_like(qkv)
         delta = torch.empty(batch, heads, seq, dtype=torch.float32, device=qkv.device)
         dq_acc = torch.empty(batch * seq, heads * D, dtype=torch.float32, device=qkv.device)
@@ -218,10 +238,15 @@ def attention_bwd(dout, qkv, out, lse, batch: int, seq: int, heads: int, causal:
 # ----------------------------------------------------------------------------------------------
 # vocabulary-parallel cross-entropy
 # ----------------------------------------------------------------------------------------------
-def ce_partial(logits, targets, col_offset: int, vocab: int):
-    """Per row: (max, sum exp(x - max), target logit or 0) over this shard's valid columns."""
+def ce_partial(logits, targets, col_offset: int, vocab: int, exch=None):
+    """Per row: (max, sum exp(x - max), target logit or 0) over this shard's valid columns.  With
+    ``exch`` the three values are published to the GPUs of the mesh row and None is returned."""
     rows, cols = logits.shape
     if logits.is_cuda:
+        if exch is not None:
+            _C().ce_partial(logits.data_ptr(), logits.stride(0), targets.data_ptr(), rows, cols, col_offset,
+                            vocab, 0, 0, 0, _st(), exch)
+            return None
         mx, se, tl = (torch.empty(rows, device=logits.device, dtype=torch.float32) for _ in range(3))
         _C().ce_partial(logits.data_ptr(), logits.stride(0), targets.data_ptr(), rows, cols, col_offset,
                         vocab, mx.data_ptr(), se.data_ptr(), tl.data_ptr(), _st())
@@ -237,6 +262,17 @@ def ce_partial(logits, targets, col_offset: int, vocab: int):
     inside = (t >= 0) & (t < valid)
     tl = torch.where(inside, lf.gather(1, t.clamp(0, valid - 1)[:, None])[:, 0], torch.zeros(rows))
     return mx, se, tl
+
+
+def ce_grad_exchanged_(logits, targets, col_offset: int, vocab: int, scale: float, exch):
+    """In place: logits <- (softmax - onehot) * scale with the global max / sum-exp combined inside
+    the kernel from what the mesh row's GPUs published (``exch``: consumer descriptor).  Returns the
+    per-row loss log(sum exp) - target logit [rows] (identical on every GPU of the mesh row)."""
+    rows, cols = logits.shape
+    row_loss = torch.empty(rows, device=logits.device, dtype=torch.float32)
+    _C().ce_grad(logits.data_ptr(), logits.stride(0), targets.data_ptr(), rows, cols, col_offset, vocab,
+                 0, 0, scale, _st(), row_loss.data_ptr(), exch)
+    return row_loss
 
 
 def ce_grad_(logits, targets, col_offset: int, vocab: int, gmax, gsum, scale: float):

@@ -56,6 +56,9 @@ def gemm_args(a, b, layout, out, *, accumulate=False, bias=None, act=None, pre_a
     if two_cta is None:
         two_cta = os.environ.get("MSB_TWO_CTA", "1") != "0"
     d["two_cta"] = 1 if two_cta else 0
+    for key, env in (("stages", "MSB_G2_STAGES"), ("group", "MSB_G2_GROUP"), ("map3d", "MSB_G2_MAP3D")):
+        if env in os.environ:
+            d[key] = int(os.environ[env])
     if bias is not None:
         d["bias"] = bias.data_ptr()
     if act is not None:

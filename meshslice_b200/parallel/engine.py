@@ -26,14 +26,26 @@ def _local(t):
 
 class FusedEngine:
     def __init__(self, mesh: DistMesh, stage_a_bytes: int, stage_b_bytes: int, slot_bytes: int,
-                 send_bytes: int, extra_heap_bytes: int = 0, timeout_ns: int = 20_000_000_000):
+                 extra_heap_bytes: int = 0, timeout_ns: int = 20_000_000_000, exchange_rows: int = 0,
+                 allow_fallback: bool = False):
+        """``exchange_rows`` > 0 also sets up the in-kernel row exchange among the GPUs of this
+        rank's mesh row (LayerNorm statistics, cross-entropy partials) for up to that many rows.
+        ``allow_fallback``: a product whose shape breaks the fused kernel's divisibility rules runs
+        as NCCL collectives + local GEMM instead of raising (counted in ``fallbacks``)."""
         self.mesh = mesh
-        total = stage_a_bytes + stage_b_bytes + slot_bytes + extra_heap_bytes + (8 << 20)   # send_bytes: unused
+        ex_bytes = 2 * mesh.C * exchange_rows * rt.RowExchanger.WIDTH * 4 + 4096 if exchange_rows and mesh.C > 1 else 0
+        total = stage_a_bytes + stage_b_bytes + slot_bytes + extra_heap_bytes + ex_bytes + (8 << 20)
         self.heap = rt.SymmHeap(total, group=mesh.group)
-        self.ws = rt.Workspace(self.heap, stage_a_bytes, stage_b_bytes, slot_bytes, send_bytes)
+        self.ws = rt.Workspace(self.heap, stage_a_bytes, stage_b_bytes, slot_bytes)
         self.world = rt.World.real(self.ws)
         self.coord = MeshCoord(mesh.R, mesh.C, mesh.r, mesh.c)
         self.fg = FusedGemm(self.coord, self.world, sm_count(), timeout_ns=timeout_ns)
+        self.row_exchange = None
+        if ex_bytes:
+            self.row_exchange = rt.RowExchanger(self.heap, self.coord.row_peers(), mesh.c, exchange_rows,
+                                                timeout_ns=timeout_ns)
+        self.allow_fallback = allow_fallback
+        self.fallbacks = 0
         self._warned = set()
         mesh.engine = self
 
@@ -43,12 +55,19 @@ class FusedEngine:
         """Pointer list indexed by the position along the gathering axis; only this rank's own
         shard is read by its kernel (it is pushed to the peers), so only that entry is set."""
         if t.data_ptr() % 16:
-            raise FusedPlanError("gathered operand must be 16-byte aligned")
+            # every rank must take the same path: copy into an aligned temporary instead of
+            # refusing the plan on this rank only
+            t = t.clone(memory_format=torch.contiguous_format)
         lst = [0] * n
         lst[idx] = t.data_ptr()
         return lst
 
     def _fallback(self, which, err, X, W, n_slices):
+        if not self.allow_fallback:
+            raise FusedPlanError(f"fused {which} not applicable to X {tuple(X.shape)}, W {tuple(W.shape)} on mesh "
+                                 f"{self.mesh.R}x{self.mesh.C}: {err} (FusedEngine(allow_fallback=True) runs such "
+                                 f"products as NCCL collectives + local GEMM)") from err
+        self.fallbacks += 1
         if which not in self._warned:
             warnings.warn(f"fused {which} not applicable ({err}); using NCCL collectives + local GEMM")
             self._warned.add(which)

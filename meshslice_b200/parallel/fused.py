@@ -135,6 +135,8 @@ class FusedGemm:
         self.timeout_ns = timeout_ns
         self.use_barriers = use_barriers
         self.C = _native.load()
+        # every communication warp of every CTA bumps a chunk's flag once per contributing GPU
+        self.signals = grid * int(getattr(self.C, "AUX_WARPS", 1))
         self._cache = {}
         # staging buffers per epilogue warp of the push kernels (3 costs one pipeline stage)
         self.push_bufs = int(os.environ.get("MSB_PUSH_BUFS", "1"))
@@ -266,22 +268,46 @@ class FusedGemm:
         x_mine, w_mine = x_ptrs[mc.c], w_ptrs[mc.r]
 
         gather_w, gather_x = mc.R > 1, mc.C > 1     # a group of one needs no copy at all
-        xbase = 1 if gather_w else 0                # index of the first X chunk
+        # W travels in chunks of whole 256-column blocks, in the order in which the tile raster
+        # reaches them, so the first tiles start after 1/nW of W (both operands are sliced and
+        # pipelined, as in TensorParallel.py:159-172)
+        tiles_n = (n + BN - 1) // BN
+        nW = max(1, min(n_slices, tiles_n)) if gather_w else 0
+        per = (tiles_n + nW - 1) // nW if gather_w else 1
+        nW = (tiles_n + per - 1) // per if gather_w else 0
+        xbase = nW                                  # index of the first X chunk
 
         def build():
-            jobs, chunks = [], []
-            if gather_w:   # chunk 0: this rank's W shard goes to every GPU of its mesh column
-                jobs.append((1, 0, kr, n * 2, n * 2, n * 2,
-                             [self.world.ptr(q, ws.stage_b) + mc.r * kr * n * 2 for q in colp]))
-                chunks.append((0, 1, [self._chunk_flag(q, 0) for q in colp], self.grid * mc.R))
+            wjobs, xjobs = [], []
+            for wc in range(nW):   # column block group wc of this rank's W shard -> every GPU of its mesh column
+                col0 = wc * per * BN
+                cols = min(n, col0 + per * BN) - col0
+                wjobs.append([(1, col0 * 2, kr, cols * 2, n * 2, n * 2,
+                               [self.world.ptr(q, ws.stage_b) + (mc.r * kr * n + col0) * 2 for q in colp])])
             for s in range(S if gather_x else 0):   # row blocks of this rank's X shard, block-cyclic
-                jb = len(jobs)
+                js = []
                 for blk in range(s, tiles_m, S):
                     row0 = blk * BM
                     rows = min(BM, m - row0)
-                    jobs.append((0, row0 * kl * 2, rows, kl * 2, kl * 2, Kd * 2,
-                                 [self.world.ptr(q, ws.stage_a) + row0 * Kd * 2 + mc.c * kl * 2 for q in rowp]))
-                chunks.append((jb, len(jobs), [self._chunk_flag(q, xbase + s) for q in rowp], self.grid * mc.C))
+                    js.append((0, row0 * kl * 2, rows, kl * 2, kl * 2, Kd * 2,
+                               [self.world.ptr(q, ws.stage_a) + row0 * Kd * 2 + mc.c * kl * 2 for q in rowp]))
+                xjobs.append(js)
+            # order of travel = order of need: the first tiles want W chunk 0 and X slice 0, the first
+            # sweep over the columns wants the rest of W, later slices of X are wanted last
+            order = []
+            if wjobs:
+                order.append(("w", 0))
+            if xjobs:
+                order.append(("x", 0))
+            order += [("w", i) for i in range(1, len(wjobs))] + [("x", i) for i in range(1, len(xjobs))]
+            jobs, chunks = [], []
+            for kind, i in order:
+                jb = len(jobs)
+                jobs += wjobs[i] if kind == "w" else xjobs[i]
+                if kind == "w":
+                    chunks.append((jb, len(jobs), [self._chunk_flag(q, i) for q in colp], self.signals * mc.R))
+                else:
+                    chunks.append((jb, len(jobs), [self._chunk_flag(q, xbase + i) for q in rowp], self.signals * mc.C))
             return jobs, chunks
 
         d = self._common(out, accumulate, stream)
@@ -289,13 +315,13 @@ class FusedGemm:
                  a_mn_major=0, b_mn_major=1, slice_dim=0, n_slices=S, cyc=1, group=8,
                  gather_src0=x_mine, gather_src1=w_mine)
         if gather_w or gather_x:
-            jt, ct, n_chunks = self._jobs(("os", m, kl, kr, n, S), build)
+            jt, ct, n_chunks = self._jobs(("os", m, kl, kr, n, S, nW), build)
             d.update(jobs=jt.data_ptr(), chunks=ct.data_ptr(), n_chunks=n_chunks,
                      chunk_flags=ws.local(ws.flags + 4 * rt.CHUNK0))
             if gather_x:
                 d.update(a_flag_mode=1, a_flag_base=xbase)
             if gather_w:
-                d.update(b_flag_mode=2, b_flag_base=0, b_flag_count=1)
+                d.update(b_flag_mode=4, b_flag_base=0, b_flag_count=nW, b_nchunk=per)
         if bias is not None:
             d["bias"] = bias.data_ptr()
         if act == "gelu":
@@ -369,14 +395,14 @@ class FusedGemm:
                         recs.append((t + s_ * pb, job, [self._chunk_flag(q, nA + mc.r * sub + s_) for q in dests]))
             recs.sort(key=lambda rec: rec[0])
             jobs = [rec[1] for rec in recs]
-            chunks = [(i, i + 1, rec[2], self.grid) for i, rec in enumerate(recs)]
+            chunks = [(i, i + 1, rec[2], self.signals) for i, rec in enumerate(recs)]
             return jobs, chunks
 
         d = self._common(out, accumulate, stream)
         d.update(M=m, N=n, K=Kd, A=xg if gather_x else x_mine, B=wg if gather_w else w_mine, lda=Kd, ldb=n,
                  a_mn_major=0, b_mn_major=1, slice_dim=0, n_slices=1, cyc=1, group=8,
                  gather_src0=x_mine, gather_src1=w_mine, k_rot=start(mc.r, mc.c) // 64,
-                 kp_target=self.grid)
+                 kp_target=self.signals)
         if gather_w or gather_x:
             jt, ct, n_chunks = self._jobs(("os_kpanel", order, m, kl, kr, n, sub), build)
             d.update(jobs=jt.data_ptr(), chunks=ct.data_ptr(), n_chunks=n_chunks,
@@ -421,7 +447,7 @@ class FusedGemm:
                         continue
                     jobs.append((1, (row0 - mc.r * nr) * kl * 2, BN, kl * 2, kl * 2, kl * 2,
                                  [self.world.ptr(q, ws.stage_b) + row0 * kl * 2 for q in colp]))
-                chunks.append((jb, len(jobs), [self._chunk_flag(q, s) for q in colp], self.grid * mc.R))
+                chunks.append((jb, len(jobs), [self._chunk_flag(q, s) for q in colp], self.signals * mc.R))
             return jobs, chunks
 
         peers = mc.row_peers()  # owners of the output column blocks, indexed by column
@@ -481,7 +507,7 @@ class FusedGemm:
                         continue
                     jobs.append((0, (col0 - mc.c * ml) * 2, kr, cyc * BM * 2, ml * 2, M * 2,
                                  [self.world.ptr(q, ws.stage_a) + col0 * 2 for q in rowp]))
-                chunks.append((jb, len(jobs), [self._chunk_flag(q, s) for q in rowp], self.grid * mc.C))
+                chunks.append((jb, len(jobs), [self._chunk_flag(q, s) for q in rowp], self.signals * mc.C))
             return jobs, chunks
 
         peers = mc.col_peers()  # owners of the output row blocks, indexed by row

@@ -97,7 +97,6 @@ class Workspace:
     stage_a_bytes: int
     stage_b_bytes: int
     slot_bytes: int
-    send_bytes: int = 0            # unused since the gathers read their operands in place; kept for callers
     flags: int = 0
     stage_a: int = 0
     stage_b: int = 0
@@ -156,6 +155,52 @@ class World:
 
     def flag_ptr(self, rank: int, word: int) -> int:
         return self.ptr(rank, self.mine.flags + 4 * word)
+
+
+class RowExchanger:
+    """Host side of the in-kernel exchange of a few floats per row among the GPUs of one mesh row
+    (LayerNorm statistics, cross-entropy max / sum-exp / target logit): the counterpart of the
+    ``psum`` over the mesh columns at ShardedLayers.py:129-131, without a collective call.
+
+    The producing kernel writes its rows' partial values into this GPU's slot on every GPU of the
+    group and counts one arrival per CTA on every peer; the consuming kernel waits for the arrivals
+    of all peers' CTAs and sums the slots.  Two slot / counter sets alternate from call to call: a
+    peer can be at most one call ahead (its consumer of call k needs this GPU's producer of call
+    k), so what it writes for call k + 1 never lands in the set this GPU still reads for call k.
+    Every rank of the group must issue the same sequence of exchanges."""
+
+    WIDTH = 4        # floats reserved per row and source (LayerNorm uses 2, cross-entropy 3)
+
+    def __init__(self, heap: SymmHeap, group_ranks: List[int], my_index: int, max_rows: int,
+                 timeout_ns: int = 20_000_000_000):
+        self.heap, self.ranks, self.me, self.max_rows = heap, list(group_ranks), my_index, max_rows
+        self.n = len(self.ranks)
+        self.timeout_ns = timeout_ns
+        self.stride = max_rows * self.WIDTH                       # floats per source
+        self.set_bytes = self.n * self.stride * 4
+        self.slots = heap.alloc(2 * self.set_bytes)
+        self.counters = heap.alloc(64)
+        heap.bytes_view(self.counters, 64).zero_()
+        self.calls = 0
+        self.arrived = [0, 0]                                     # cumulative targets per set
+        torch.cuda.synchronize()
+
+    def next(self, rows: int, producer_grid: int):
+        """Descriptors (producer, consumer) of the next exchange of ``rows`` rows; the producing
+        kernel runs ``producer_grid`` CTAs on every GPU of the group."""
+        if rows > self.max_rows:
+            raise ValueError(f"row exchange sized for {self.max_rows} rows, got {rows}")
+        k = self.calls & 1
+        self.calls += 1
+        self.arrived[k] = (self.arrived[k] + (self.n - 1) * producer_grid) & 0xffffffff
+        base = self.slots + k * self.set_bytes
+        d = dict(n=self.n, me=self.me,
+                 dst=[self.heap.ptr(q, base + self.me * self.stride * 4) for q in self.ranks],
+                 slots=self.heap.base + base, stride=self.stride,
+                 counter=[self.heap.ptr(q, self.counters + 4 * k) for q in self.ranks],
+                 my_counter=self.heap.base + self.counters + 4 * k, target=self.arrived[k],
+                 timeout_ns=self.timeout_ns, status=_native.status().dev)
+        return d, d
 
 
 JOB_DTYPE = np.dtype([("src", "<u8"), ("dst", "<u8"), ("rows", "<u4"), ("row_bytes", "<u4"),

@@ -140,8 +140,16 @@ def meshslice_rs(mesh: Mesh, X, W, K=4, B=8):
 # ----------------------------------------------------------------------------------------------
 # Wang et al. collective matmul: bidirectional ring along the mesh row
 # ----------------------------------------------------------------------------------------------
+def _even_halves(t, dim: int, what: str):
+    """The bidirectional ring moves two halves of a shard in opposite directions."""
+    for s in t.shards.values():
+        if s.shape[dim] % 2:
+            raise ValueError(f"wang: the {what} of a shard ({s.shape[dim]}) must be even (two half blocks)")
+
+
 def wang_os(mesh: Mesh, X, W, K=1, B=8):
     n = mesh.C
+    _even_halves(X, 1, "contraction length")
     Wj = mesh.all_gather(W, "row", 0)
     def blk(w, i, hi):
         h = w.shape[0] // n // 2

@@ -89,9 +89,9 @@ class Trainer:
         if tcfg.backend == "fused" and self.device.type == "cuda":
             from .parallel.engine import FusedEngine, LocalGemmEngine
             if self.world > 1:
-                sa, sb, sl, se = self._workspace_bytes()
-                self.engine = FusedEngine(self.mesh, sa, sb, sl, se, extra_heap_bytes=n_sh * 2 + (1 << 20),
-                                          timeout_ns=tcfg.timeout_ns)
+                sa, sb, sl = self._workspace_bytes()
+                self.engine = FusedEngine(self.mesh, sa, sb, sl, extra_heap_bytes=n_sh * 2 + (1 << 20),
+                                          timeout_ns=tcfg.timeout_ns, exchange_rows=tcfg.micro_batch * cfg.seq)
                 sharded_buf = self.engine.heap.empty((n_sh,), torch.bfloat16)
             else:
                 self.engine = LocalGemmEngine(self.mesh)
@@ -124,8 +124,7 @@ class Trainer:
         stage_a = m * gath * 2
         stage_b = max(i * o // C for i, o, _ in lin) * 2
         slots = max(m * max((i if df == "os" else o) for i, o, df in lin), max(i * o // C for i, o, _ in lin)) * 2
-        send = 0      # gathers read the operands in place (push based): no send buffers
-        return stage_a, stage_b, slots, send
+        return stage_a, stage_b, slots
 
     # ------------------------------------------------------------------ data
     def rows_of_global_batch(self, ids_global: torch.Tensor) -> torch.Tensor:

@@ -33,7 +33,7 @@ class Heartbeat:
                 return ""
             return self.store.get(key).decode()
         except Exception:
-            return ""
+            return "unreachable"      # the store's host process is gone
 
     def beat(self, step: int):
         self.store.set(self._key(self.rank), f"step:{step}")
@@ -56,6 +56,9 @@ class Heartbeat:
                 if v.startswith("step:") and int(v[5:]) >= step:
                     break
                 if time.time() > deadline:
+                    if v == "unreachable":
+                        raise PeerLostError(f"the job's key-value store stopped answering before step {step}: "
+                                            f"the rank that hosts it has left")
                     raise PeerLostError(f"rank {r} did not reach step {step} within {timeout_s}s (last: {v or 'nothing'})")
                 time.sleep(0.02)
 

@@ -1,6 +1,7 @@
 """Worker for the multi-process CPU tests (Gloo): algorithms on a DistMesh, a model step, and
 host-side failure detection.  Started by torch.distributed.run."""
 import os
+import time
 import sys
 from datetime import timedelta
 
@@ -78,6 +79,10 @@ def main():
             guarded_step(hb, 1, work)
         except ValueError:
             print("rank 0 RAISED", flush=True)
+            time.sleep(2.0)       # a failing rank takes a moment to tear down; it hosts the store
+            os._exit(0)
+        except PeerLostError as e:    # rank 0 was already gone when this rank looked before step 1
+            print(f"rank {rank} PEER_LOST: {e}", flush=True)
             os._exit(0)
         try:
             guarded_step(hb, 2, lambda: 1, timeout_s=5.0)

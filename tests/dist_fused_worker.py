@@ -21,7 +21,7 @@ def main():
     R, C = [int(v) for v in os.environ.get("MESH", f"1x{world}").split("x")]
     slices = int(os.environ.get("SLICES", "2"))
     mesh = DistMesh(R, C)
-    eng = FusedEngine(mesh, 64 << 20, 64 << 20, 64 << 20, 32 << 20, timeout_ns=2_000_000_000)
+    eng = FusedEngine(mesh, 64 << 20, 64 << 20, 64 << 20, timeout_ns=2_000_000_000, exchange_rows=4096)
     dev = torch.device("cuda")
     r, c = mesh.r, mesh.c
     g = torch.Generator(device="cpu").manual_seed(7)

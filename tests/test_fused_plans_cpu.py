@@ -49,6 +49,7 @@ def _capture(R, C, call):
             fg = fz.FusedGemm.__new__(fz.FusedGemm)
             fg.mesh, fg.world, fg.grid, fg.timeout_ns, fg.use_barriers = mc, FakeWorld(R * C, mc.rank), 148, 1, False
             fg._cache = {}
+            fg.signals = 148 * 2      # two communication warps per CTA bump every chunk flag
             cap = {}
             fg._jobs = lambda key, builder, cap=cap: (cap.setdefault("plan", builder()),
                                                       type("T", (), {"data_ptr": lambda s: 1})(),
@@ -113,11 +114,18 @@ def test_os_plans_fill_both_staging_buffers_once(mesh):
             assert d["A"] == 10 ** 9 and "a_flag_mode" not in d
         if R == 1:
             assert d["B"] == 2 * 10 ** 9 and "b_flag_mode" not in d
-    # flag targets: every CTA of every contributing GPU bumps each chunk once
+    # flag targets: every communication warp of every contributing GPU bumps each chunk once;
+    # W travels in column chunks (flags 0 .. nW-1), X in row slices (flags nW ..), first wanted first
     if R > 1 and C > 1:
         _, chunks = caps[0]["plan"]
-        assert chunks[0][3] == 148 * R and all(ch[3] == 148 * C for ch in chunks[1:])
-        assert len(chunks) == 1 + caps[0]["d"]["n_slices"]
+        d = caps[0]["d"]
+        nW = d["b_flag_count"]
+        assert d["b_flag_mode"] == 4 and d["a_flag_base"] == nW and nW == 2 and d["b_nchunk"] == 1
+        flag0 = ((0 + 1) << 40) + 4 * rt.CHUNK0
+        order = [(ch[2][0] - flag0) // 4 for ch in chunks]        # flag index of each chunk, in travel order
+        assert order == [0, nW] + list(range(1, nW)) + list(range(nW + 1, nW + d["n_slices"]))
+        for ch, idx in zip(chunks, order):
+            assert ch[3] == 296 * (R if idx < nW else C)
 
 
 @pytest.mark.parametrize("mesh", [(2, 4), (4, 2), (2, 2)])
@@ -179,10 +187,10 @@ def test_k_panel_plans(mesh, order, sub):
             assert d["b_flag_mode"] == 3 and d["b_kpanel"] * 64 * sub == kr and d["b_flag_base"] == C * sub
         r, c = divmod(rank, C)
         start = {"summa": 0, "wang": c * kl, "cannon": ((r + c) % C) * kl}[order]
-        assert d["k_rot"] == start // 64 and d["kp_target"] == 148
+        assert d["k_rot"] == start // 64 and d["kp_target"] == 296
         if "plan" in cap:
             jobs, chunks = cap["plan"]
-            assert len(jobs) == len(chunks) and all(ch[1] - ch[0] == 1 and ch[3] == 148 for ch in chunks)
+            assert len(jobs) == len(chunks) and all(ch[1] - ch[0] == 1 and ch[3] == 296 for ch in chunks)
             for ch in chunks:
                 for f in ch[2]:
                     flag_hits[f] = flag_hits.get(f, 0) + 1
@@ -295,7 +303,8 @@ def test_tile_order_matches_the_gather_chunks_and_the_arrival_targets(mesh, slic
         jobs, chunks = plan
         lo = (1 << 40) + stage_off
         out = {}
-        for ci, (jb, je, _sigs, _t) in enumerate(chunks):
+        for (jb, je, sigs, _t) in chunks:
+            ci = (sigs[0] & ((1 << 40) - 1)) // 4 - rt.CHUNK0      # the chunk's flag index
             got = set()
             for sel, src, rows, rb, sp, dp, dsts in jobs[jb:je]:
                 for dptr in dsts:
@@ -308,15 +317,24 @@ def test_tile_order_matches_the_gather_chunks_and_the_arrival_targets(mesh, slic
             out[ci] = got
         return out
 
-    # ---- OS: X row blocks, sliced along M; chunk 0 carries W when it is gathered
+    # ---- OS: X row blocks, sliced along M (flags xbase + s); W column blocks in chunks (flags 0 .. nW-1)
     m, Kd, n = 2048, 1024, 512
     caps = _capture(R, C, lambda fg, mc: fg.os([10 ** 9] * C, [2 * 10 ** 9] * R, m, Kd // C, Kd // R, n, None,
                                                n_slices=slices))
     d = caps[0]["d"]
     sched = fz.tile_schedule(d)
     assert sorted((a, b) for a, b, _ in sched) == [(i, j) for i in range(m // BMc) for j in range(-(-n // BNc))]
+    if R > 1:
+        per_chunk = {}
+        for cap in caps.values():
+            for ci, blks in blocks_of_chunks(cap["plan"], 1 << 34, 0, "cols").items():
+                if ci < d["b_flag_count"]:
+                    per_chunk.setdefault(ci, set()).update(blks)
+        assert d["b_flag_mode"] == 4
+        for mb, nb_, s_ in sched:
+            assert nb_ in per_chunk[nb_ // d["b_nchunk"]]
     if C > 1:
-        xbase = 1 if R > 1 else 0
+        xbase = d["a_flag_base"]
         # union over all source ranks of the row blocks that chunk xbase + s delivers to rank 0
         per_chunk = {}
         for cap in caps.values():

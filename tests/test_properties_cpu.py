@@ -21,6 +21,8 @@ MESHES = [(1, 2), (2, 1), (2, 2), (2, 3), (3, 2), (4, 2), (1, 4)]
 def test_every_dataflow_equals_the_dense_product(mesh, K, B, mi, ki, ni, seed, alg):
     R, C = mesh
     unit = K * B * R * C                      # divisible by every slicing the algorithms apply
+    if alg == "wang":
+        unit *= 2                             # the ring moves two half blocks per shard
     M, Kd, N = unit * mi, unit * ki, unit * ni
     g = torch.Generator().manual_seed(seed)
     X, W = torch.randn(M, Kd, generator=g, dtype=torch.float64), torch.randn(Kd, N, generator=g, dtype=torch.float64)
