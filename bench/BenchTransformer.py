@@ -6,6 +6,13 @@ GeLU).  Unlike the reference, which only writes a profiler trace, this prints de
 forward / backward milliseconds (max over ranks) and achieved TFLOP/s per GPU.
 
     torchrun --nproc-per-node 8 bench/BenchTransformer.py --alg meshflow --nrows 2 --ncols 4
+
+``--nrows x --ncols`` is the LOGICAL mesh of the study.  When fewer GPUs are launched than it has
+devices, the physical mesh (``--phys RxC``, default: the most square split of the launched ranks
+that divides the logical one) runs the per-device problem of the logical mesh, the reference's
+weak-scaling emulation (BenchTransformer.py:45-56,78-79): batch * phys_rows / nrows sequences and
+heads * phys_cols / ncols heads, so every GPU holds the shards and does the FLOPs it would in the
+large run; only the collective group sizes are those of the physical mesh.
 """
 import argparse
 import json
@@ -16,6 +23,24 @@ import torch
 import torch.distributed as dist
 
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+
+def physical_mesh(nrows: int, ncols: int, world: int, phys: str = ""):
+    """Physical mesh for a logical nrows x ncols study on ``world`` ranks: the logical mesh itself
+    when the ranks suffice, else ``phys`` or the most square split whose sides divide the logical ones."""
+    if phys:
+        pr, pc = (int(v) for v in phys.lower().split("x"))
+    elif nrows * ncols == world:
+        return nrows, ncols
+    else:
+        cands = [(r, world // r) for r in range(1, world + 1)
+                 if world % r == 0 and nrows % r == 0 and ncols % (world // r) == 0]
+        if not cands:
+            raise SystemExit(f"no split of {world} ranks divides the logical mesh {nrows}x{ncols}")
+        pr, pc = min(cands, key=lambda rc: abs(rc[0] - rc[1]))
+    if pr * pc != world or nrows % pr or ncols % pc:
+        raise SystemExit(f"physical mesh {pr}x{pc} does not match {world} ranks / logical mesh {nrows}x{ncols}")
+    return pr, pc
 
 
 def main():
@@ -29,6 +54,7 @@ def main():
     p.add_argument("--ncols", type=int, default=4)
     p.add_argument("--alg", type=str, default="noff", choices=["noff", "collective", "cannon", "wang", "meshflow", "summa"])
     p.add_argument("--iters", type=int, default=3)
+    p.add_argument("--phys", default="", help="physical mesh RxC when it is smaller than --nrows x --ncols")
     a = p.parse_args()
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
     torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", rank)))
@@ -39,17 +65,20 @@ def main():
     from meshslice_b200.parallel.mesh import DistMesh, EmuMesh
     from meshslice_b200.parallel.tensor_parallel import createMultihostMatrix
 
-    if a.nrows * a.ncols != world:
-        raise SystemExit(f"--nrows x --ncols = {a.nrows * a.ncols} but {world} ranks were launched")
-    B = world if a.batchsize <= 0 else a.batchsize
-    S, H, D = a.seqlen, a.nheads, a.headdim
-    mesh = DistMesh(a.nrows, a.ncols) if world > 1 else EmuMesh(1, 1)
+    pr, pc = physical_mesh(a.nrows, a.ncols, world, a.phys)
+    B_log = a.nrows * a.ncols if a.batchsize <= 0 else a.batchsize
+    if (B_log * pr) % a.nrows or (a.nheads * pc) % a.ncols:
+        raise SystemExit("batch / heads of the logical mesh do not scale to the physical one")
+    # per-device problem of the logical mesh on the physical one
+    B, H = B_log * pr // a.nrows, a.nheads * pc // a.ncols
+    S, D = a.seqlen, a.headdim
+    mesh = DistMesh(pr, pc) if world > 1 else EmuMesh(1, 1)
     dev = torch.device("cuda")
     T, d = B * S, H * D
-    if a.alg == "meshflow":
+    if a.alg != "noff" and a.alg != "collective":
         if world > 1:
-            m = T // a.nrows
-            FusedEngine(mesh, m * 4 * d * 2, 4 * d * d // a.ncols * 2 + (1 << 20), m * 4 * d * 2 + (1 << 20),
+            m = T // pr
+            FusedEngine(mesh, m * 4 * d * 2, 4 * d * d // pc * 2 + (1 << 20), m * 4 * d * 2 + (1 << 20),
                         exchange_rows=m)
         else:
             LocalGemmEngine(mesh)
@@ -70,7 +99,7 @@ def main():
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return t.item()
 
-    tag = "{}_{}x{}_{}_{}_{}".format(a.alg, a.nrows, a.ncols, B, H, D)
+    tag = "{}_{}x{}_{}_{}_{}".format(a.alg, a.nrows, a.ncols, B_log, a.nheads, D)
     if a.alg == "noff":
         x0 = createMultihostMatrix(mesh, (T, 3 * d), device=dev)
         norm, attn, gelu = ShardedLayerNorm(mesh, d, device=dev), ShardedAttention(mesh, H, S), GeLU()
@@ -114,7 +143,8 @@ def main():
         flops = 2.0 * T * (d * d + 4 * d * d + 4 * d * d + 3 * d * d)
     if rank == 0:
         tb_only = tb - tf
-        out = {"benchtag": tag, "forward_ms": tf, "backward_ms": tb_only, "fwd_bwd_ms": tb}
+        out = {"benchtag": tag, "logical_mesh": [a.nrows, a.ncols], "physical_mesh": [pr, pc],
+               "batch_run": B, "heads_run": H, "forward_ms": tf, "backward_ms": tb_only, "fwd_bwd_ms": tb}
         if flops:
             out["tflops_per_gpu_fwd"] = flops / world / (tf * 1e-3) / 1e12
             out["tflops_per_gpu_fwd_bwd"] = 3 * flops / world / (tb * 1e-3) / 1e12

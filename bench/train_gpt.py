@@ -59,7 +59,7 @@ def main():
         if tuned.get("mesh") and not a.mesh:
             R, C = tuned["mesh"]
         if len(tuned.get("layers", [])) == 4:
-            dataflows = tuple(l["dataflow"] if l["dataflow"] != "rs" else "os" for l in tuned["layers"])
+            dataflows = tuple(l["dataflow"] for l in tuned["layers"])
             ksplits = tuple(int(l["ksplit"] or 1) for l in tuned["layers"])
     cfg = GPTConfig(n_layers=a.layers, d_model=a.d_model, n_heads=a.nheads, ffn=a.ffn, vocab=a.vocab, seq=a.seqlen,
                     dataflows=dataflows, ksplits=ksplits)

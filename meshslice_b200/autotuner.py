@@ -34,8 +34,8 @@ TPUV4 = dict(
     base_overheads={"allgather": 13e-6, "reducescatter": 26e-6, "sendrecv": 13e-6},
     fabric="ring", shared_port=False, flops_per_chip=242 * 1024 ** 4)
 
-# NVLink 5 / NVSwitch defaults for one 8 x B200 box (per-direction port bandwidth measured on the
-# pool: 770 GB/s peer copy; refined by BenchCollectives2D --fabric-json)
+# NVLink 5 / NVSwitch defaults for one 8 x B200 box (measured per-direction peer-copy bandwidth of a
+# port: 770 GB/s; refined by BenchCollectives2D --fabric-json)
 B200_NVSWITCH = dict(
     latencies={"allgather": 3e-6, "reducescatter": 3e-6, "sendrecv": 3e-6},
     bws={"allgather": (700e9, 700e9), "reducescatter": (600e9, 600e9), "sendrecv": (700e9, 700e9)},

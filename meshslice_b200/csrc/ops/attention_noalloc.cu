@@ -1,6 +1,8 @@
 // Attention backward with library-owned scratch (see attention_noalloc.h for who needs it).
 #include "attention_noalloc.h"
 
+#include <mutex>
+
 #include "attention.h"
 
 namespace {
@@ -18,6 +20,7 @@ struct PerDevice {
   float* base = nullptr;
 };
 PerDevice g_dev[64];
+std::mutex g_setup_lock;   // first calls from several host threads
 
 }  // namespace
 
@@ -32,6 +35,7 @@ extern "C" cudaError_t msb_attention_bwd_noalloc(const void* qkv, const void* ou
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return e;
   if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+  std::unique_lock<std::mutex> lock(g_setup_lock);
   if (g_dev[dev].base == nullptr) {
     // set-up, once per device, with that device current
     float* p = nullptr;
@@ -41,11 +45,13 @@ extern "C" cudaError_t msb_attention_bwd_noalloc(const void* qkv, const void* ou
     if (e != cudaSuccess) return e;
     g_dev[dev].base = p;
   }
+  lock.unlock();
   float* acc = g_dev[dev].base;
   float* delta = acc + kAccFloats;
   uint32_t* status = reinterpret_cast<uint32_t*>(delta + kDeltaFloats);
   if (kernel_status != nullptr) {
-    // status of earlier calls; a plain async copy into caller memory, no allocation
+    // status of earlier calls (sticky: never cleared); an async copy into the caller's pinned
+    // memory, no allocation
     e = cudaMemcpyAsync(kernel_status, status, sizeof(uint32_t), cudaMemcpyDeviceToHost, stream);
     if (e != cudaSuccess) return e;
   }

@@ -26,10 +26,16 @@ extern "C" {
 //   * All calls share one scratch array per device.  Each call clears what it needs, so calls
 //     may follow each other on one stream, but two calls that overlap on the GPU (different
 //     streams) race on it.
+//   * The set-up is serialised by a lock, so first calls from several host threads are safe;
+//     the device is the one current in the calling thread.
 // Returns cudaErrorInvalidValue when the problem exceeds MSB_NOALLOC_MAX_ROWS or seq is not a
-// multiple of 128; otherwise the launch status.  *kernel_status (host pointer, may be null)
-// receives the kernels' bounded-wait status code of the PREVIOUS call on this device
-// (0 = ok), read without synchronising.
+// multiple of 128; otherwise the launch status.
+// kernel_status (may be null) must point to PINNED host memory (cudaHostAlloc / cudaHostRegister):
+// the bounded-wait status word of the kernels is copied there asynchronously on `stream`, ordered
+// before this call's kernels, so after the stream has run it holds what EARLIER calls on this
+// device reported (0 = ok).  The word is sticky: the first error code stays until the process
+// exits, later calls report it again.  With pageable memory the copy would block the host, and a
+// copy to host memory is not allowed while `stream` is being captured: pass null in both cases.
 cudaError_t msb_attention_bwd_noalloc(const void* qkv, const void* out, const void* dout,
                                       const float* lse, void* dqkv, int batch, int seq, int heads,
                                       int causal, float scale, cudaStream_t stream,

@@ -70,6 +70,7 @@ class GPTBlock:
     def __init__(self, mesh: Mesh, cfg: GPTConfig, idx: int, device, alloc_sharded, alloc_rep, grad_sharded,
                  grad_rep=None):
         d, df, ks = cfg.d_model, cfg.dataflows, cfg.ksplits
+        self.mesh = mesh
         kw = dict(dtype=cfg.dtype, device=device, std=cfg.init_std, alloc=alloc_sharded,
                   grad_alloc=grad_sharded)
         s = idx * 16
@@ -84,28 +85,39 @@ class GPTBlock:
         self.gelu = GeLU()
         self.ff2 = ShardedFFLayer(mesh, cfg.algorithm, df[3], ks[3], cfg.ffn, d, seed=s + 4, **kw)
 
+    # A right-stationary ('rs') layer computes x^T w and therefore wants its input transposed,
+    # [in, tokens] with the features over the mesh rows; its output and the gradient it returns are
+    # in the usual / the transposed orientation respectively (ShardedLayers.py:69-81).  The block keeps
+    # activations [tokens, features] and re-orients around such a layer.
+    def _lin(self, layer, x: ShardedTensor) -> ShardedTensor:
+        return layer.forward(self.mesh.transpose(x) if layer.dataflow == "rs" else x)
+
+    def _lin_bwd(self, layer, dy: ShardedTensor) -> ShardedTensor:
+        d = layer.backward(dy)
+        return self.mesh.transpose(d) if layer.dataflow == "rs" else d
+
     def forward(self, x: ShardedTensor, delta: Optional[ShardedTensor]):
         """Input: residual stream x and a pending branch output ``delta`` (added inside LN1).
         Returns (h, mlp_out): the caller's next LayerNorm adds them."""
         y = self.ln1.forward(x, delta)            # residual stream becomes x + delta
         x = self.ln1.h
-        a = self.out_proj.forward(self.attn.forward(self.in_proj.forward(y)))
+        a = self._lin(self.out_proj, self.attn.forward(self._lin(self.in_proj, y)))
         y = self.ln2.forward(a, x)                # h = x + a
         h = self.ln2.h
         if self.ff1._fused and self.ff1.dataflow == "os" and _FUSE_GELU:
             g, pre = self.ff1.forward_gelu(y)          # GeLU in the GEMM epilogue
             self.gelu.remember(pre)
         else:
-            g = self.gelu.forward(self.ff1.forward(y))
-        m = self.ff2.forward(g)
+            g = self.gelu.forward(self._lin(self.ff1, y))
+        m = self._lin(self.ff2, g)
         return h, m
 
     def backward(self, dh: ShardedTensor, dm: ShardedTensor):
         """dh: gradient of the residual stream after this block, dm: gradient of the MLP output.
         Returns (dx, ddelta) for the block below."""
-        d = self.ff1.backward(self.gelu.backward(self.ff2.backward(dm)))
+        d = self._lin_bwd(self.ff1, self.gelu.backward(self._lin_bwd(self.ff2, dm)))
         dh2 = self.ln2.backward(d, dh)            # gradient of h = x + a
-        d = self.in_proj.backward(self.attn.backward(self.out_proj.backward(dh2)))
+        d = self._lin_bwd(self.in_proj, self.attn.backward(self._lin_bwd(self.out_proj, dh2)))
         dx = self.ln1.backward(d, dh2)            # gradient of x + delta
         return dx, dx
 

@@ -38,7 +38,9 @@ class ShardedFFLayer:
     def __init__(self, mesh: Mesh, algorithm: str, dataflow: str, ksplit: int, in_dim: int, out_dim: int,
                  blocksize: int = 8, dtype=torch.bfloat16, device=None, seed: int = 0, std: float = 1.0,
                  alloc: Optional[Callable] = None, grad_alloc: Optional[Callable] = None,
-                 backend: str = "auto"):
+                 backend: str = "auto", grad_dtype=None):
+        """``grad_dtype``: dtype of the weight-gradient buffer that micro-batches accumulate into;
+        default fp32 for 16-bit weights (summing many micro-batches in bf16 loses the small ones)."""
         if dataflow not in ("os", "ls", "rs"):
             raise ValueError(f"unknown dataflow {dataflow!r}")
         self.mesh, self.algorithm, self.dataflow = mesh, algorithm, dataflow
@@ -55,7 +57,9 @@ class ShardedFFLayer:
             init = ShardedTensor(mesh, placed)
         self.weight = init
         galloc = grad_alloc or _default_alloc
-        self.grad = ShardedTensor(mesh, {k: galloc(v.shape, dtype, v.device).zero_() for k, v in init.shards.items()})
+        if grad_dtype is None:
+            grad_dtype = torch.float32 if dtype in (torch.bfloat16, torch.float16) else dtype
+        self.grad = ShardedTensor(mesh, {k: galloc(v.shape, grad_dtype, v.device).zero_() for k, v in init.shards.items()})
         b = SPMD(mesh, algorithm, blocksize, backend=backend)
         self._OS, self._LS, self._RS = b.OS(ksplit), b.LS(ksplit), b.RS(ksplit)
         self._fused = b._fused() is not None

@@ -120,7 +120,7 @@ class FusedEngine:
             out.copy_(y) if not accumulate else out.add_(y)
             return out
 
-    def ls(self, X, W, n_slices: int = 4, out: Optional[torch.Tensor] = None, accumulate=False):
+    def ls(self, X, W, n_slices: int = 4, out: Optional[torch.Tensor] = None, accumulate=False, rot_index=None):
         """Y[m, N/C] = RS_col( X[m, kl] @ AG_row(W)[N, kl]^T )."""
         X, W = _local(X), _local(W)
         m, kl = X.shape
@@ -131,13 +131,14 @@ class FusedEngine:
         try:
             W = W.contiguous()
             wp = self._own(W, self.mesh.R, self.mesh.r)
-            return self.fg.ls(X.contiguous(), wp, m, kl, nr, out, n_slices=n_slices, accumulate=accumulate)
+            return self.fg.ls(X.contiguous(), wp, m, kl, nr, out, n_slices=n_slices, accumulate=accumulate,
+                              rot_index=rot_index)
         except FusedPlanError as e:
             y = self._fallback("ls", e, X, W, n_slices)
             out.copy_(y) if not accumulate else out.add_(y)
             return out
 
-    def rs(self, X, W, n_slices: int = 4, out: Optional[torch.Tensor] = None, accumulate=False):
+    def rs(self, X, W, n_slices: int = 4, out: Optional[torch.Tensor] = None, accumulate=False, rot_index=None):
         """Y[M/R, n] = RS_row( AG_col(X)[kr, M]^T @ W[kr, n] )."""
         X, W = _local(X), _local(W)
         kr, ml = X.shape
@@ -148,7 +149,8 @@ class FusedEngine:
         try:
             X = X.contiguous()
             xp = self._own(X, self.mesh.C, self.mesh.c)
-            return self.fg.rs(xp, W.contiguous(), kr, ml, n, out, n_slices=n_slices, accumulate=accumulate)
+            return self.fg.rs(xp, W.contiguous(), kr, ml, n, out, n_slices=n_slices, accumulate=accumulate,
+                              rot_index=rot_index)
         except FusedPlanError as e:
             y = self._fallback("rs", e, X, W, n_slices)
             out.copy_(y) if not accumulate else out.add_(y)
@@ -175,10 +177,13 @@ class LocalGemmEngine:
     def os(self, X, W, n_slices=1, out=None, accumulate=False, bias=None, act=None, pre_act=None):
         return self._run(X, W, "nn", out, accumulate, bias=bias, act=act, pre_act=pre_act)
 
-    def ls(self, X, W, n_slices=1, out=None, accumulate=False):
+    def os_kpanel(self, X, W, order="summa", sub=1, out=None, accumulate=False):
+        return self._run(X, W, "nn", out, accumulate)
+
+    def ls(self, X, W, n_slices=1, out=None, accumulate=False, rot_index=None):
         return self._run(X, W, "nt", out, accumulate)
 
-    def rs(self, X, W, n_slices=1, out=None, accumulate=False):
+    def rs(self, X, W, n_slices=1, out=None, accumulate=False, rot_index=None):
         return self._run(X, W, "tn", out, accumulate)
 
     def check(self):

@@ -416,8 +416,14 @@ class FusedGemm:
 
     # ------------------------------------------------------------------ LS
     def ls(self, x, w_ptrs: List[int], m: int, kl: int, nr: int, out, n_slices: int = 4,
-           accumulate: bool = False, phase: str = "all", reset: bool = True):
-        """Y[m, N/C] = reduce-scatter over the mesh row of  X[m, kl] @ concat_r(W_r)[R*nr, kl]^T."""
+           accumulate: bool = False, phase: str = "all", reset: bool = True, rot_index: Optional[int] = None):
+        """Y[m, N/C] = reduce-scatter over the mesh row of  X[m, kl] @ concat_r(W_r)[R*nr, kl]^T.
+
+        ``rot_index`` selects at which owner's blocks this rank starts every slice: None = the rank
+        after this one in its push group (MeshSlice; also the order in which Wang's rotating output
+        accumulators visit the ranks), an explicit index i = the rank after i (Cannon's skew uses
+        r + c), a negative value = no rotation (every rank walks the owners in the same order, the
+        step order of SUMMA's reduce)."""
         mc, ws = self.mesh, self.world.mine
         N = mc.R * nr
         if N % mc.C:
@@ -467,14 +473,17 @@ class FusedGemm:
                  red_n=mc.C, red_slots=ws.local(ws.slots), red_rows=m, red_cols=nc, red_ld=nc,
                  red_counter=ws.local(ws.flags + 4 * rt.COUNTER0),
                  red_target=mc.C * (blocks_own // S) * (m // CTA_M) * 4, red_slice_dim=1,
-                 rot=_push_rotation(mc.c, mc.C, tiles_n // S))
+                 rot=0 if (rot_index is not None and rot_index < 0) else
+                 _push_rotation((mc.c if rot_index is None else rot_index) % mc.C, mc.C, tiles_n // S))
         self._launch(d, exit_barrier=False, phase=phase, reset=reset)
         return out
 
     # ------------------------------------------------------------------ RS
     def rs(self, x_ptrs: List[int], w, kr: int, ml: int, n: int, out, n_slices: int = 4,
-           accumulate: bool = False, cyc: int = 2, phase: str = "all", reset: bool = True):
-        """Y[M/R, n] = reduce-scatter over the mesh column of  concat_c(X_c)[kr, C*ml]^T @ W[kr, n]."""
+           accumulate: bool = False, cyc: int = 2, phase: str = "all", reset: bool = True,
+           rot_index: Optional[int] = None):
+        """Y[M/R, n] = reduce-scatter over the mesh column of  concat_c(X_c)[kr, C*ml]^T @ W[kr, n].
+        ``rot_index``: as in ``ls`` (along the mesh column)."""
         mc, ws = self.mesh, self.world.mine
         M = mc.C * ml
         if M % mc.R:
@@ -527,6 +536,7 @@ class FusedGemm:
                  red_n=mc.R, red_slots=ws.local(ws.slots), red_rows=mr, red_cols=n, red_ld=n,
                  red_counter=ws.local(ws.flags + 4 * rt.COUNTER0),
                  red_target=mc.R * ((mr // BM) // S) * 2 * tiles_n * 4, red_slice_dim=0,
-                 rot=_push_rotation(mc.r, mc.R, tiles_m // S))
+                 rot=0 if (rot_index is not None and rot_index < 0) else
+                 _push_rotation((mc.r if rot_index is None else rot_index) % mc.R, mc.R, tiles_m // S))
         self._launch(d, exit_barrier=False, phase=phase, reset=reset)
         return out

@@ -109,6 +109,22 @@ class Mesh:
         g = self.all_gather(st.map(lambda t: t.unsqueeze(0)), axis, 0)
         return g.map(lambda t: t[src])
 
+    def transpose(self, st: ShardedTensor) -> ShardedTensor:
+        """Global transpose of a P(row, col) matrix: [A, B] sharded (A/R, B/C) becomes [B, A] sharded
+        (B/R, A/C).  This is the re-orientation of activations that an 'rs' layer asks for (the
+        ``Transpose`` node of the reference's compute graph, Autotuner.py:304-337).  Generic form:
+        gather the matrix along both axes and cut the own block; a mesh may do better."""
+        rows = self.all_gather(st, "col", 1)
+        full = self.all_gather(rows, "row", 0)
+        out = {}
+        for (r, c), f in full.shards.items():
+            A, B = f.shape
+            if B % self.R or A % self.C:
+                raise ValueError(f"cannot transpose a {A} x {B} matrix on mesh {self.shape}")
+            b0, a0 = B // self.R, A // self.C
+            out[(r, c)] = f[c * a0:(c + 1) * a0, r * b0:(r + 1) * b0].t().contiguous()
+        return ShardedTensor(self, out)
+
     def reduce_to(self, st: ShardedTensor, axis: str, dst: int) -> ShardedTensor:
         """Sum along ``axis``; only the device with index ``dst`` is required to use the result."""
         return self.all_reduce(st, axis)

@@ -385,6 +385,28 @@ class SPMD:
                 y = ring_eng.os_kpanel(X, W, order=order, sub=max(1, K), **kw)
                 return ShardedTensor(mesh, {mesh.coords()[0]: y}) if isinstance(X, ShardedTensor) else y
             return run_panels
+        if (eng is None and self.backend != "collective" and which in ("ls", "rs") and hasattr(ring_eng, "os_kpanel")
+                and self.algorithm in ("summa", "wang", "cannon")):
+            # LS / RS of the baseline algorithms as schedules of the fused kernel.  What travels in
+            # their rings is the OUTPUT: Wang's two accumulators visit the ranks one after the other
+            # and end at their owner, Cannon does the same from a skewed start, SUMMA reduces one
+            # panel per step to its owner.  On a switch a ring hop is a direct store to the owner, so
+            # each is the push epilogue with the algorithm's own order of owners and granularity:
+            #   wang    one monolithic gather, owners visited from the next rank on (rotation by rank)
+            #   cannon  the same from the skewed start (r + c)
+            #   summa   lcm(R, C) * K panels, every rank walks the owners in the same step order
+            mesh, alg = self.mesh, self.algorithm
+            fn = getattr(ring_eng, which)
+            if alg == "summa":
+                sched = dict(n_slices=math.lcm(mesh.R, mesh.C) * max(1, K), rot_index=-1)
+            elif alg == "wang":
+                sched = dict(n_slices=1, rot_index=None)
+            else:
+                sched = dict(n_slices=1, rot_index=getattr(mesh, "r", 0) + getattr(mesh, "c", 0))
+            def run_ring(X, W, **kw):
+                y = fn(X, W, **sched, **kw)
+                return ShardedTensor(mesh, {mesh.coords()[0]: y}) if isinstance(X, ShardedTensor) else y
+            return run_ring
         if eng is not None:
             fn, mesh = getattr(eng, which), self.mesh
             def run(X, W, **kw):

@@ -99,7 +99,9 @@ class Trainer:
         if sharded_buf is None:
             sharded_buf = torch.empty(n_sh, dtype=dt, device=self.device)
         self.p_sh = sharded_buf.zero_()
-        self.g_sh = torch.zeros(n_sh, dtype=dt, device=self.device)
+        # gradients of 16-bit weights accumulate over the micro-batches in fp32
+        gdt = torch.float32 if dt in (torch.bfloat16, torch.float16) else dt
+        self.g_sh = torch.zeros(n_sh, dtype=gdt, device=self.device)
         self.p_rep = torch.zeros(n_rep, dtype=dt, device=self.device)
         self.g_rep = torch.zeros(n_rep, dtype=torch.float32, device=self.device)
         a_sh, a_gsh, a_rep, a_grep = Arena(self.p_sh), Arena(self.g_sh), Arena(self.p_rep), Arena(self.g_rep)
@@ -115,16 +117,24 @@ class Trainer:
 
     # ------------------------------------------------------------------ sizing
     def _workspace_bytes(self):
+        """Staging (gathered A / B operands) and slot (pushed partial tiles) bytes that the fused
+        kernels of one micro-batch need, over the forward, dX and dW products of every linear layer
+        under its dataflow (m = tokens per mesh row and micro-batch)."""
         cfg, R, C = self.cfg, self.R, self.C
         m = self.tcfg.micro_batch * cfg.seq
         d, f, V = cfg.d_model, cfg.ffn, cfg.vocab_padded
         lin = [(d, 3 * d, cfg.dataflows[0]), (d, d, cfg.dataflows[1]), (d, f, cfg.dataflows[2]),
                (f, d, cfg.dataflows[3]), (d, V, "os")]
-        gath = max((i if df == "os" else o) for i, o, df in lin)       # widest gathered activation
-        stage_a = m * gath * 2
-        stage_b = max(i * o // C for i, o, _ in lin) * 2
-        slots = max(m * max((i if df == "os" else o) for i, o, df in lin), max(i * o // C for i, o, _ in lin)) * 2
-        return stage_a, stage_b, slots
+        sa = sb = sl = 0
+        for i, o, df in lin:
+            if df == "os":      # OS(x, w), LS(dy, w), RS(x, dy)
+                a, b, s_ = m * i, i * o // C, max(m * i, i * o // C)
+            elif df == "ls":    # LS(x, w), OS(dy, w), RS(dy, x)
+                a, b, s_ = m * o, o * i // C, max(m * o, o * i // C)
+            else:               # RS(x^T, w), LS(w, dy), OS(x^T, dy): the token dimension is gathered whole
+                a, b, s_ = m * i, max(i * o // C, m * R * o // C), max(m * i, m * R * o // C)
+            sa, sb, sl = max(sa, a), max(sb, b), max(sl, s_)
+        return 2 * sa, 2 * sb, 2 * sl
 
     # ------------------------------------------------------------------ data
     def rows_of_global_batch(self, ids_global: torch.Tensor) -> torch.Tensor:

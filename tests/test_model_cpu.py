@@ -173,3 +173,59 @@ def test_loss_curve_is_the_same_on_every_mesh_shape():
     assert ref[2] < ref[0] and ref[3] < ref[1]      # the two batches repeat: the model learns them
     for shape, c in curves.items():
         assert all(abs(x - y) < 2e-4 for x, y in zip(c, ref)), (shape, c, ref)
+
+
+@pytest.mark.parametrize("dataflow", ["os", "is", "fsdp"])
+def test_1d_layers_forward_backward_match_dense(dataflow):
+    """BenchTransformer1D.py:21-38: the 1-D linear layers (Wang ring schedule on a 1 x n mesh, FSDP on
+    an n x 1 mesh) against dense autograd."""
+    from meshslice_b200.models.sharded_layers_1d import ShardedFFLayer1D
+    n, T, I, O = 4, 32, 64, 96
+    mesh = EmuMesh(n, 1) if dataflow == "fsdp" else EmuMesh(1, n)
+    layer = ShardedFFLayer1D(mesh, dataflow, I, O, dtype=torch.float32)
+    W = _full(mesh, layer.weight).clone().requires_grad_(True)
+    g = torch.Generator().manual_seed(5)
+    X = torch.randn(T, I, generator=g, requires_grad=True)
+    Yd = X @ (W if dataflow == "os" else W.t())
+    dY = torch.randn(T, O, generator=g)
+    Yd.backward(dY)
+    y = layer.forward(mesh.shard(X.detach()))
+    assert torch.allclose(_full(mesh, y), Yd.detach(), atol=1e-4, rtol=1e-4)
+    dx = layer.backward(mesh.shard(dY))
+    assert torch.allclose(_full(mesh, dx), X.grad, atol=1e-4, rtol=1e-4)
+    assert torch.allclose(_full(mesh, layer.grad), W.grad, atol=1e-4, rtol=1e-4)
+    with pytest.raises(ValueError):
+        ShardedFFLayer1D(EmuMesh(2, 2), dataflow, I, O, dtype=torch.float32)
+
+
+@pytest.mark.parametrize("dataflows", [("rs", "os", "os", "ls"), ("os", "rs", "rs", "rs"), ("ls", "ls", "rs", "os")])
+def test_gpt_block_runs_every_dataflow_the_tuner_can_pick(dataflows):
+    """Right-stationary layers want transposed activations (Autotuner.py:304-337); the block
+    re-orients around them, so any per-layer choice of os / ls / rs gives the dense model's loss
+    and gradients."""
+    import dataclasses
+    cfg = dataclasses.replace(CFG, dataflows=dataflows, n_layers=1)
+    mesh = EmuMesh(2, 4)
+    model = GPTModel(mesh, cfg)
+    B = 4
+    ids = torch.randint(0, cfg.vocab, (B, cfg.seq + 1), generator=torch.Generator().manual_seed(2))
+    per = B // mesh.R
+    tok = ShardedTensor(mesh, {(r, c): ids[r * per:(r + 1) * per, :-1].reshape(-1) for (r, c) in mesh.coords()})
+    tgt = ShardedTensor(mesh, {(r, c): ids[r * per:(r + 1) * per, 1:].reshape(-1) for (r, c) in mesh.coords()})
+    loss = model.forward_backward(tok, tgt, B * cfg.seq)
+    total = sum(loss.shards[(r, 0)] for r in range(mesh.R))
+
+    class View:                                    # the dense oracle multiplies by W or W^T by dataflow
+        pass
+    ref, P = _dense_loss(model, mesh, cfg, ids)
+    assert abs(total.item() - ref.item()) < 1e-4
+    b0 = model.blocks[0]
+    for layer, tag in ((b0.in_proj, "0.in"), (b0.out_proj, "0.out"), (b0.ff1, "0.ff1"), (b0.ff2, "0.ff2")):
+        assert torch.allclose(_full(mesh, layer.grad), P[tag].grad, atol=2e-5, rtol=1e-3), tag
+
+
+def test_mesh_transpose_is_the_global_transpose():
+    for shape in ((2, 4), (4, 2), (3, 2), (1, 4)):
+        mesh = EmuMesh(*shape)
+        X = torch.arange(24 * 48, dtype=torch.float32).reshape(24, 48)
+        assert torch.equal(mesh.unshard(mesh.transpose(mesh.shard(X))), X.t())

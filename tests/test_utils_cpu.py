@@ -71,3 +71,22 @@ def test_p2p_copy_jobs_are_checked_before_launch():
         validate_reduce([4096, 8192], 64, 16384, 30, 8, 30)
     with pytest.raises(ValueError):
         validate_reduce([4096, 8194], 64, 16384, 32, 8, 32)
+
+
+def test_logical_mesh_of_the_transformer_bench_maps_to_a_physical_one():
+    import importlib.util
+    import os
+    path = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "bench", "BenchTransformer.py")
+    spec = importlib.util.spec_from_file_location("bench_transformer", path)
+    bt = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bt)
+    assert bt.physical_mesh(2, 4, 8) == (2, 4)
+    assert bt.physical_mesh(4, 4, 8) == (2, 4)          # most square split that divides 4 x 4
+    assert bt.physical_mesh(4, 4, 4) == (2, 2)
+    assert bt.physical_mesh(8, 16, 8, "2x4") == (2, 4)
+    assert bt.physical_mesh(4, 4, 1) == (1, 1)
+    import pytest
+    with pytest.raises(SystemExit):
+        bt.physical_mesh(3, 3, 8)
+    with pytest.raises(SystemExit):
+        bt.physical_mesh(4, 4, 8, "8x1")
