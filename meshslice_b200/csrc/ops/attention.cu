@@ -1,22 +1,17 @@
-// Flash-style attention forward / backward for head_dim 128 on tcgen05 (sm_100a).
+// Flash-style attention forward / backward for head_dim 128 on tcgen05 (sm_100a): the score matrix
+// lives in tensor memory only.
 //
-// Forward, one CTA per (sequence, head, 128 query rows), 192 threads:
-//   warp 0     TMA producer: Q once, then K_j / V_j tiles into a two-stage ring
-//   warp 1     MMA issuer:   S_j = Q K_j^T into one of two TMEM score buffers, O += P_j V_j
-//   warps 2-5  softmax: one thread per query row (TMEM lane); online softmax in the log2 domain
-//              with lazy rescaling of O (only when the running maximum grows by more than 2^8),
-//              P_j written to shared memory as bf16 in the swizzled operand layout
-// Backward, one CTA per (sequence, head, 128 key rows), loop over query blocks:
-//   S = Q K^T, dP = dO V^T  ->  P = exp2(S - lse), dS = P (dP - delta) scale  ->
-//   dV += P^T dO, dK += dS^T Q (TMEM accumulators), dQ = dS K (added to an fp32 buffer with
-//   vector reductions).  All five products read the same shared-memory tiles; only the
-//   descriptors (K-major or MN-major view) differ.
+// Forward (attn_fwd2_kernel): one CTA per (sequence, head, 128 query rows), two CTAs per SM; S = Q K^T
+//   into TMEM, online softmax in the log2 domain with lazy rescaling of O (only when the running
+//   maximum grows by more than 2^8), P written back over S as packed bf16 and read by O += P V as
+//   the TMEM operand.
+// Backward (attn_bwd2_kernel<key-major>, <query-major>): dK / dV are accumulated by the CTA that owns
+//   128 keys, dQ by the CTA that owns 128 queries; both recompute S and dP, keep P and dS in TMEM,
+//   and never add to global memory: the gradients are bit-identical from run to run.
 // All waits are bounded; a timeout records a code in `status` and the CTA leaves.
 #include "attention.h"
 
 #include <cuda_bf16.h>
-
-#include <cstdlib>
 
 #include "../common/ptx.cuh"
 #include "../gemm/sm100_gemm.h"  // make_tensor_map_2d
@@ -34,7 +29,6 @@ constexpr int kHalf = kTile / 2;
 // two threads per row, each owning 64 of the 128 columns: the exponentials and the TMEM traffic
 // of a block, which sit in series with the MMAs, take half as long.  A warp may touch the TMEM
 // lanes 32 * (warp % 4) ... + 31, so warps 2-5 and 6-9 both cover all four lane quarters.
-constexpr int attn_threads(int ew_warps) { return 64 + 32 * ew_warps; }
 constexpr uint32_t kErrAttn = 20;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
@@ -81,22 +75,6 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
-// Writes 32 consecutive columns [c0, c0+32) of row `row` of a [128 x 128] bf16 tile stored as
-// two 128-byte-swizzled halves of 64 columns (the layout TMA produces and tcgen05 consumes).
-__device__ __forceinline__ void store_tile_row32(uint8_t* tile, int row, int c0, const float (&v)[32]) {
-  uint8_t* half = tile + (c0 >> 6) * kHalf + row * 128;
-  const int chunk0 = (c0 & 63) >> 3;  // 16-byte chunk index inside the 128-byte row
-#pragma unroll
-  for (int q = 0; q < 4; ++q) {
-    uint4 u;
-    u.x = pack_bf16(v[q * 8 + 0], v[q * 8 + 1]);
-    u.y = pack_bf16(v[q * 8 + 2], v[q * 8 + 3]);
-    u.z = pack_bf16(v[q * 8 + 4], v[q * 8 + 5]);
-    u.w = pack_bf16(v[q * 8 + 6], v[q * 8 + 7]);
-    *reinterpret_cast<uint4*>(half + (((chunk0 + q) ^ (row & 7)) << 4)) = u;
-  }
-}
-
 // K-major view of a tile: rows = M or N index, contraction along the 128 columns.
 __device__ __forceinline__ uint64_t desc_kmajor(uint32_t tile, int kstep) {
   return make_smem_desc(tile + (kstep >> 2) * kHalf + (kstep & 3) * 32, 16, 1024);
@@ -113,33 +91,60 @@ __device__ __forceinline__ void load_tile(uint8_t* dst, const CUtensorMap* map, 
 }
 
 // ==========================================================================================
-// forward
+// forward: P stays in tensor memory, two CTAs per SM
 // ==========================================================================================
-template <int kEwWarps>
-__global__ void __launch_bounds__(attn_threads(kEwWarps), 1)
-attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant__ AttnArgs a) {
-  static_assert(kEwWarps == 4 || kEwWarps == 8, "four or eight element-wise warps");
-  constexpr int kHalves = kEwWarps / 4;
-  constexpr int kColsPer = kBlk / kHalves;   // columns per thread
-  constexpr int kChunks = kColsPer / 32;     // 32-column TMEM loads per thread and block
-  constexpr int kEwThreads = 32 * kEwWarps;
+// One CTA per (sequence, head, 128 query rows), sized so that TWO CTAs share an SM
+// (96 KiB of shared memory, 256 TMEM columns, 192 threads each): while one CTA's softmax runs on the
+// SIMT pipes the other's products keep the tensor pipe busy, without any hand-written ping-pong.
+//   warp 0     TMA producer: Q once; K_j and V_j into one buffer each (K_{j+1} travels under
+//              softmax(j) and P V(j), V_{j+1} under S(j+1) and softmax(j+1))
+//   warp 1     MMA issuer: S_j = Q K_j^T into TMEM columns [0,128); O += P_j V_j with P_j read from
+//              TMEM (the A operand of tcgen05.mma may live in tensor memory), V_j from shared memory
+//   warps 2-5  softmax: one thread per query row; two passes over S in TMEM (row maximum, then
+//              exponentials); P_j is written back over S as packed bf16 (64 columns), so it never
+//              touches shared memory and needs no proxy fence
+// The tensor pipe runs the MMAs of a CTA in issue order, so S_{j+1} may be issued right behind
+// P_j V_j although it overwrites P_j, and a completed S_{j+1} implies a completed P_j V_j (O is safe
+// to rescale).
+constexpr size_t kFwd2Smem = 3 * kTile + 256 + 1024;
+
+__device__ __forceinline__ void umma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc,
+                                            uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// 32 lanes x 16 consecutive 32-bit columns: thread t of the warp writes row (lane base + t).
+__device__ __forceinline__ void tmem_st_32x16(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+        "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
+
+__global__ void __launch_bounds__(192, 2)
+attn_fwd2_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant__ AttnArgs a) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
   uint8_t* sQ = smem;
-  uint8_t* sK = smem + kTile;            // 2 stages
-  uint8_t* sV = smem + 3 * kTile;        // 2 stages
-  uint8_t* sP = smem + 5 * kTile;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 6 * kTile);
+  uint8_t* sK = smem + kTile;
+  uint8_t* sV = smem + 2 * kTile;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 3 * kTile);
   uint64_t* q_full = bars;
-  uint64_t* kv_full = bars + 1;   // [2]
-  uint64_t* kv_empty = bars + 3;  // [2]
-  uint64_t* s_full = bars + 5;    // [2]
-  uint64_t* p_ready = bars + 7;
-  uint64_t* pv_done = bars + 8;
-  uint64_t* xchg = bars + 9;      // the two threads of a row exchange their partial maximum / sum
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
-  float* sX = reinterpret_cast<float*>(smem + 6 * kTile + 256);   // [2 phases][2 halves][128 rows]
+  uint64_t* k_full = bars + 1;
+  uint64_t* k_empty = bars + 2;
+  uint64_t* v_full = bars + 3;
+  uint64_t* v_empty = bars + 4;
+  uint64_t* s_full = bars + 5;
+  uint64_t* p_ready = bars + 6;
+  uint64_t* o_done = bars + 7;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nblk = a.seq / kBlk;
@@ -153,148 +158,145 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constan
   if (threadIdx.x == 0) {
     tma_prefetch_desc(&tm_qkv);
     mbar_init(q_full, 1);
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(kv_full + i, 1);
-      mbar_init(kv_empty + i, 1);
-      mbar_init(s_full + i, 1);
-    }
-    mbar_init(p_ready, kEwThreads);
-    mbar_init(pv_done, 1);
-    mbar_init(xchg, kEwThreads);
+    mbar_init(k_full, 1);
+    mbar_init(k_empty, 1);
+    mbar_init(v_full, 1);
+    mbar_init(v_empty, 1);
+    mbar_init(s_full, 1);
+    mbar_init(p_ready, 128);
+    mbar_init(o_done, 1);
     mbar_fence_init();
   }
   if (warp == 1) {
-    tmem_alloc(tmem_slot, 512);
+    tmem_alloc(tmem_slot, 256);
     tmem_relinquish();
   }
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem = *tmem_slot;
-  const uint32_t tmem_o = tmem + 256;
+  const uint32_t tmem_o = tmem + 128;
 
   if (warp == 0) {
     if (lane == 0) {
       mbar_expect_tx(q_full, kTile);
       load_tile(sQ, &tm_qkv, q_full, colq, row0);
       for (int j = 0; j < n_kv; ++j) {
-        const int st = j & 1;
-        if (!mbar_wait(kv_empty + st, ((j >> 1) & 1) ^ 1, 4 * tmo)) {
+        const int krow = b * a.seq + j * kBlk;
+        if (!mbar_wait(k_empty, (j & 1) ^ 1, 4 * tmo)) {
           report(a.status, kErrAttn + 1, j, 0);
           break;
         }
-        mbar_expect_tx(kv_full + st, 2 * kTile);
-        const int krow = b * a.seq + j * kBlk;
-        load_tile(sK + st * kTile, &tm_qkv, kv_full + st, colq + kD, krow);
-        load_tile(sV + st * kTile, &tm_qkv, kv_full + st, colq + 2 * kD, krow);
+        mbar_expect_tx(k_full, kTile);
+        load_tile(sK, &tm_qkv, k_full, colq + kD, krow);
+        if (!mbar_wait(v_empty, (j & 1) ^ 1, 4 * tmo)) {
+          report(a.status, kErrAttn + 1, j, 1);
+          break;
+        }
+        mbar_expect_tx(v_full, kTile);
+        load_tile(sV, &tm_qkv, v_full, colq + 2 * kD, krow);
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
       const uint32_t idesc_s = make_idesc_bf16(128, 128, 0, 0);
       const uint32_t idesc_pv = make_idesc_bf16(128, 128, 0, 1);
-      const uint32_t q_addr = smem_u32(sQ), p_addr = smem_u32(sP);
-      bool ok = mbar_wait(q_full, 0, 2 * tmo) && mbar_wait(kv_full, 0, 2 * tmo);
+      const uint32_t q_addr = smem_u32(sQ), k_addr = smem_u32(sK), v_addr = smem_u32(sV);
+      // Every product of this CTA reads the same three buffers: all 24 operand descriptors are
+      // built once.  One thread issues every MMA, and an MMA of this size occupies the tensor pipe
+      // for about 64 cycles: building descriptors in the loop would make the issue the bottleneck.
+      uint64_t dq[8], dkk[8], dv[8];
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        dq[k] = desc_kmajor(q_addr, k);
+        dkk[k] = desc_kmajor(k_addr, k);
+        dv[k] = desc_mnmajor(v_addr, k);
+      }
+      bool ok = mbar_wait(q_full, 0, 2 * tmo) && mbar_wait(k_full, 0, 2 * tmo);
       if (!ok) report(a.status, kErrAttn + 2, 0, 0);
       if (ok) {
         tc_fence_after_sync();
-        const uint32_t k_addr = smem_u32(sK);
 #pragma unroll
-        for (int k = 0; k < 8; ++k)
-          umma_f16(tmem, desc_kmajor(q_addr, k), desc_kmajor(k_addr, k), idesc_s, k != 0);
+        for (int k = 0; k < 8; ++k) umma_f16(tmem, dq[k], dkk[k], idesc_s, k != 0);
         umma_commit(s_full);
+        umma_commit(k_empty);
       }
       for (int j = 0; j < n_kv && ok; ++j) {
-        if (j + 1 < n_kv) {
-          const int st = (j + 1) & 1;
-          if (!mbar_wait(kv_full + st, ((j + 1) >> 1) & 1, 2 * tmo)) {
-            report(a.status, kErrAttn + 3, j, 0);
-            ok = false;
-            break;
-          }
-          tc_fence_after_sync();
-          const uint32_t k_addr = smem_u32(sK + st * kTile);
-#pragma unroll
-          for (int k = 0; k < 8; ++k)
-            umma_f16(tmem + st * 128, desc_kmajor(q_addr, k), desc_kmajor(k_addr, k), idesc_s, k != 0);
-          umma_commit(s_full + st);
-        }
-        if (!mbar_wait(p_ready, j & 1, 4 * tmo)) {
+        if (!mbar_wait(p_ready, j & 1, 6 * tmo) || !mbar_wait(v_full, j & 1, 2 * tmo)) {
           report(a.status, kErrAttn + 4, j, 0);
           ok = false;
           break;
         }
         tc_fence_after_sync();
-        const uint32_t v_addr = smem_u32(sV + (j & 1) * kTile);
 #pragma unroll
-        for (int k = 0; k < 8; ++k)
-          umma_f16(tmem_o, desc_kmajor(p_addr, k), desc_mnmajor(v_addr, k), idesc_pv, (j | k) != 0);
-        umma_commit(pv_done);
-        umma_commit(kv_empty + (j & 1));
+        for (int k = 0; k < 8; ++k)   // 16 bf16 of a row of P = 8 TMEM columns per step
+          umma_f16_ts(tmem_o, tmem + k * 8, dv[k], idesc_pv, (j | k) != 0);
+        umma_commit(v_empty);
+        if (j + 1 == n_kv) {
+          umma_commit(o_done);
+        } else {
+          if (!mbar_wait(k_full, (j + 1) & 1, 2 * tmo)) {
+            report(a.status, kErrAttn + 3, j, 0);
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+#pragma unroll
+          for (int k = 0; k < 8; ++k) umma_f16(tmem, dq[k], dkk[k], idesc_s, k != 0);
+          umma_commit(s_full);
+          umma_commit(k_empty);
+        }
       }
     }
   } else {
-    // ---------------- softmax / epilogue: kHalves threads per query row ----------------
+    // ---------------- softmax / epilogue: one thread per query row ----------------
     const int q4 = warp & 3;
-    const int half = (warp - 2) >> 2;         // which kColsPer columns of the row this thread owns
-    const int col0 = half * kColsPer;
     const int row = q4 * 32 + lane;           // row inside the tile == TMEM lane
     const uint32_t lane_off = static_cast<uint32_t>(q4 * 32) << 16;
+    const uint32_t ts = tmem + lane_off, to = tmem_o + lane_off;
     const float sl2 = a.scale * kLog2e;
     float m_used = -INFINITY, l = 0.f;
     bool ok = true;
-    int xphase = 0;
-    // both threads of a row leave this with the combined value (maximum or sum)
-    auto exchange = [&](float v, bool is_max, bool& good) -> float {
-      if (kHalves == 1) return v;
-      sX[(xphase * 2 + half) * kBlk + row] = v;
-      mbar_arrive(xchg);
-      if (!warp_wait(xchg, xphase, 6 * tmo)) {
-        good = false;
-        return v;
-      }
-      const float o = sX[(xphase * 2 + (half ^ 1)) * kBlk + row];
-      xphase ^= 1;
-      return is_max ? fmaxf(v, o) : v + o;
-    };
     for (int j = 0; j < n_kv; ++j) {
-      const int sb = j & 1;
-      if (!warp_wait(s_full + sb, (j >> 1) & 1, 6 * tmo)) {
+      if (!warp_wait(s_full, j & 1, 6 * tmo)) {
         if (lane == 0) report(a.status, kErrAttn + 5, j, 0);
         ok = false;
         break;
       }
       tc_fence_after_sync();
-      const uint32_t ts = tmem + lane_off + sb * 128 + col0;
       const bool diag = a.causal && j == i_blk;
       float mx = -INFINITY;
+      // the masked forms run for the diagonal block only: the other blocks carry no mask arithmetic
+      if (!diag) {
 #pragma unroll 1
-      for (int c = 0; c < kChunks; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(ts + c * 32, r);
-        tmem_ld_wait();
+        for (int c = 0; c < 4; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32(ts + c * 32, r);
+          tmem_ld_wait();
+          float m0 = __uint_as_float(r[0]), m1 = __uint_as_float(r[1]);
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const float v = __uint_as_float(r[i]);
-          if (!diag || col0 + c * 32 + i <= row) mx = fmaxf(mx, v);
+          for (int i = 2; i < 32; i += 2) {
+            m0 = fmaxf(m0, __uint_as_float(r[i]));
+            m1 = fmaxf(m1, __uint_as_float(r[i + 1]));
+          }
+          mx = fmaxf(mx, fmaxf(m0, m1));
         }
-      }
-      mx = exchange(mx, true, ok);
-      if (!ok) {
-        if (lane == 0) report(a.status, kErrAttn + 8, j, 0);
-        break;
+      } else {
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32(ts + c * 32, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (c * 32 + i <= row) mx = fmaxf(mx, __uint_as_float(r[i]));
+        }
       }
       const float m_blk = mx * sl2;
       if (j == 0) {
         m_used = m_blk;
       } else {
-        // P of the previous block has been consumed and O is up to date after this wait
-        if (!warp_wait(pv_done, (j - 1) & 1, 6 * tmo)) {
-          if (lane == 0) report(a.status, kErrAttn + 6, j, 0);
-          ok = false;
-          break;
-        }
-        tc_fence_after_sync();
+        // S_j is complete, hence P_{j-1} V_{j-1} is too: O may be rescaled in place
         const float m_new = fmaxf(m_used, m_blk);
         const bool need = (m_new - m_used) > 8.0f;
         if (__any_sync(0xffffffffu, need)) {
@@ -303,9 +305,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constan
             l *= alpha;
             m_used = m_new;
           }
-          const uint32_t to = tmem_o + lane_off + col0;
 #pragma unroll 1
-          for (int c = 0; c < kChunks; ++c) {
+          for (int c = 0; c < 4; ++c) {
             uint32_t r[32];
             tmem_ld_32x32(to + c * 32, r);
             tmem_ld_wait();
@@ -313,36 +314,54 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constan
             for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
             tmem_st_32x32(to + c * 32, r);
           }
-          tmem_st_wait();
         }
       }
       float rowsum = 0.f;
+      const float neg_m = -m_used;
+      if (!diag) {
 #pragma unroll 1
-      for (int c = 0; c < kChunks; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(ts + c * 32, r);
-        tmem_ld_wait();
-        float p[32];
+        for (int c = 0; c < 4; ++c) {
+          uint32_t r[32], pk[16];
+          tmem_ld_32x32(ts + c * 32, r);
+          tmem_ld_wait();
+          float s0 = 0.f, s1 = 0.f;
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float e = fast_exp2(__uint_as_float(r[i]) * sl2 - m_used);
-          if (diag && col0 + c * 32 + i > row) e = 0.f;
-          p[i] = e;
-          rowsum += e;
+          for (int i = 0; i < 32; i += 2) {
+            const float e0 = fast_exp2(fmaf(__uint_as_float(r[i]), sl2, neg_m));
+            const float e1 = fast_exp2(fmaf(__uint_as_float(r[i + 1]), sl2, neg_m));
+            s0 += e0;
+            s1 += e1;
+            pk[i >> 1] = pack_bf16(e0, e1);
+          }
+          rowsum += s0 + s1;
+          // P columns [32c, 32c+32) as bf16 = TMEM columns [16c, 16c+16): over S columns already read
+          tmem_st_32x16(ts + c * 16, pk);
         }
-        store_tile_row32(sP, row, col0 + c * 32, p);
+      } else {
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t r[32], pk[16];
+          tmem_ld_32x32(ts + c * 32, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            float e0 = fast_exp2(fmaf(__uint_as_float(r[i]), sl2, neg_m));
+            float e1 = fast_exp2(fmaf(__uint_as_float(r[i + 1]), sl2, neg_m));
+            if (c * 32 + i > row) e0 = 0.f;
+            if (c * 32 + i + 1 > row) e1 = 0.f;
+            rowsum += e0 + e1;
+            pk[i >> 1] = pack_bf16(e0, e1);
+          }
+          tmem_st_32x16(ts + c * 16, pk);
+        }
       }
       l += rowsum;
-      fence_proxy_async_smem();
+      tmem_st_wait();
       tc_fence_before_sync();
       mbar_arrive(p_ready);
     }
     if (ok) {
-      l = exchange(l, false, ok);   // the row's denominator: both halves
-      if (!ok && lane == 0) report(a.status, kErrAttn + 9, 0, 0);
-    }
-    if (ok) {
-      if (!warp_wait(pv_done, (n_kv - 1) & 1, 6 * tmo)) {
+      if (!warp_wait(o_done, 0, 6 * tmo)) {
         if (lane == 0) report(a.status, kErrAttn + 7, 0, 0);
         ok = false;
       }
@@ -351,10 +370,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constan
       tc_fence_after_sync();
       const float inv = 1.0f / l;
       __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(a.out) +
-                            (int64_t)(row0 + row) * (a.heads * kD) + h * kD + col0;
-      const uint32_t to = tmem_o + lane_off + col0;
+                            (int64_t)(row0 + row) * (a.heads * kD) + h * kD;
 #pragma unroll 1
-      for (int c = 0; c < kChunks; ++c) {
+      for (int c = 0; c < 4; ++c) {
         uint32_t r[32];
         tmem_ld_32x32(to + c * 32, r);
         tmem_ld_wait();
@@ -368,20 +386,24 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constan
           *reinterpret_cast<uint4*>(orow + c * 32 + q * 8) = u;
         }
       }
-      if (half == 0) a.lse[((int64_t)b * a.heads + h) * a.seq + i_blk * kBlk + row] = m_used * kLn2 + logf(l);
+      a.lse[((int64_t)b * a.heads + h) * a.seq + i_blk * kBlk + row] = m_used * kLn2 + logf(l);
     }
   }
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
-  if (warp == 1) tmem_dealloc(tmem, 512);
+  if (warp == 1) tmem_dealloc(tmem, 256);
 }
 
 // ==========================================================================================
 // backward
 // ==========================================================================================
+// delta[b, h, s] = rowsum(dO * O) * scale and lse2[b, h, s] = lse * log2(e): pre-scaled so that the
+// element-wise passes of the backward kernels need one fused multiply-add each for the exponent and
+// for dP * scale - delta.
 __global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ dout,
-                                  float* __restrict__ delta, int batch, int seq, int heads) {
+                                  float* __restrict__ delta, int batch, int seq, int heads,
+                                  const float* __restrict__ lse, float* __restrict__ lse2, float scale) {
   // one warp per (token, head): delta = sum_d out * dout
   const int64_t w = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
@@ -399,73 +421,98 @@ __global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ out, const _
   for (int off = 16; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
   if (lane == 0) {
     const int64_t bq = t / seq, sq = t - bq * seq;
-    delta[(bq * heads + h) * seq + sq] = s;
+    const int64_t idx = (bq * heads + h) * seq + sq;
+    delta[idx] = s * scale;
+    lse2[idx] = lse[idx] * kLog2e;
   }
 }
 
-__global__ void attn_dq_store_kernel(const float4* __restrict__ dq_acc, __nv_bfloat16* __restrict__ dqkv,
-                                     int64_t tokens, int heads) {
-  const int64_t nvec = tokens * heads * (kD / 4);
-  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < nvec;
-       i += (int64_t)gridDim.x * blockDim.x) {
-    const int64_t th = i / (kD / 4);
-    const int v = (int)(i - th * (kD / 4));
-    const int64_t t = th / heads;
-    const int h = (int)(th - t * heads);
-    const float4 f = dq_acc[i];
-    uint2 o;
-    o.x = pack_bf16(f.x, f.y);
-    o.y = pack_bf16(f.z, f.w);
-    *reinterpret_cast<uint2*>(dqkv + t * heads * 3 * kD + h * 3 * kD + v * 4) = o;
-  }
-}
+// ==========================================================================================
+// backward: two deterministic kernels, P / dS stay in tensor memory
+// ==========================================================================================
+// The gradient is split by who accumulates it:
+//   attn_bwd2_kernel<true>   one CTA per 128 KEYS walks the query blocks and accumulates dV, dK in TMEM
+//   attn_bwd2_kernel<false>  one CTA per 128 QUERIES walks the key blocks and accumulates dQ in TMEM
+// Both recompute S and dP (7 products per block pair instead of 5), but nothing is ever added to
+// global memory: no fp32 dQ buffer, no memset, no atomics, and the result is bit-identical from run
+// to run.  P and dS are written back over S and dP as packed bf16 and feed the gradient products
+// as the TMEM (A) operand: they never touch shared memory.
+//
+// An MMA of M = 128 occupies the tensor pipe for about 92-105 cycles whatever its N up to 128, so
+// the products use full 128-wide blocks (eight instructions each) and the kernels are organised
+// around keeping that one pipe fed: the element-wise work is split in two phases (P from S; dS from
+// dP and P) and the MMA warp issues the next block's S (and dP) between the gradient products of the
+// current block, so each phase runs under products that do not depend on it:
+//   key-major    S(i) dP(i) | P(i)? dV(i) S(i+1) | dS(i)? dK(i) dP(i+1) | P(i+1)? ...
+//   query-major  S(j) dP(j) S(j+1) | dS(j)? dQ(j) dP(j+1) S(j+2) | ...          (two S buffers)
+//
+//   warp 0      TMA: the two resident 128-row tiles once, then a two-stage ring of 128-row tile pairs
+//   warp 1      MMA issuer (all operand descriptors are built once, outside the loops)
+//   warps 2-9   element-wise: two threads per TMEM lane, 64 of the 128 columns each
+constexpr int kRing = 2;
+constexpr size_t kBwd2Smem = 2 * kTile + kRing * 2 * kTile + 256 + 1024;
+constexpr int kBwd2Threads = 64 + 32 * 8;
 
-template <int kEwWarps>
-__global__ void __launch_bounds__(attn_threads(kEwWarps), 1)
-attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant__ CUtensorMap tm_do,
-                const __grid_constant__ AttnArgs a) {
-  static_assert(kEwWarps == 4 || kEwWarps == 8, "four or eight element-wise warps");
-  constexpr int kColsPer = kBlk / (kEwWarps / 4);
-  constexpr int kChunks = kColsPer / 32;
-  constexpr int kEwThreads = 32 * kEwWarps;
+struct Bwd2Args {
+  void* dqkv;
+  const float* lse2;    // lse * log2(e)          (written by attn_delta_kernel)
+  const float* delta;   // rowsum(dO * O) * scale (written by attn_delta_kernel)
+  int batch, seq, heads, causal;
+  float scale;
+  uint32_t* status;
+  uint64_t timeout_ns;
+};
+
+// kKeyMajor = true:  resident tiles K, V (this CTA's 128 keys), streamed Q, dO; accumulators dV, dK.
+//                    TMEM lanes = keys, columns = queries: lse / delta vary along the columns.
+// kKeyMajor = false: resident tiles Q, dO (this CTA's 128 queries), streamed K, V; accumulator dQ.
+//                    TMEM lanes = queries, columns = keys: lse / delta are per thread.
+template <bool kKeyMajor>
+__global__ void __launch_bounds__(kBwd2Threads, 1)
+attn_bwd2_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant__ CUtensorMap tm_do,
+                 const __grid_constant__ Bwd2Args a) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
-  uint8_t* sK = smem;
-  uint8_t* sV = smem + kTile;
-  uint8_t* sQ = smem + 2 * kTile;
-  uint8_t* sdO = smem + 3 * kTile;
-  uint8_t* sP = smem + 4 * kTile;
-  uint8_t* sdS = smem + 5 * kTile;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 6 * kTile);
-  uint64_t* kv_full = bars;
-  uint64_t* qdo_full = bars + 1;
-  uint64_t* qdo_empty = bars + 2;
-  uint64_t* sdp_full = bars + 3;
-  uint64_t* pds_ready = bars + 4;
-  uint64_t* mma_done = bars + 5;
-  uint64_t* dq_drained = bars + 6;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 7);
+  uint8_t* sR0 = smem;                      // resident: K (key-major) or Q
+  uint8_t* sR1 = smem + kTile;              // resident: V (key-major) or dO
+  uint8_t* sS0 = smem + 2 * kTile;          // ring of streamed tiles: Q or K
+  uint8_t* sS1 = sS0 + kRing * kTile;       //                          dO or V
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sS1 + kRing * kTile);
+  uint64_t* res_full = bars;
+  uint64_t* ring_full = bars + 1;           // [kRing]
+  uint64_t* ring_empty = bars + 3;          // [kRing]
+  uint64_t* s_full = bars + 5;              // [2] (key-major uses [0] only)
+  uint64_t* dp_full = bars + 7;
+  uint64_t* p_ready = bars + 8;             // key-major: P^T is in TMEM
+  uint64_t* ds_ready = bars + 9;            // dS is in TMEM
+  uint64_t* acc_done = bars + 10;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nblk = a.seq / kBlk;
-  const int j_blk = blockIdx.x;   // key block; with a causal mask low j means more work: first
+  const int blk = kKeyMajor ? (int)blockIdx.x : (a.causal ? nblk - 1 - (int)blockIdx.x : (int)blockIdx.x);
   const int h = blockIdx.y, b = blockIdx.z;
-  const int i0 = a.causal ? j_blk : 0;
-  const int n_it = nblk - i0;
+  // streamed blocks: queries i0 .. nblk-1 for a key block, keys 0 .. blk for a query block
+  const int i0 = kKeyMajor && a.causal ? blk : 0;
+  const int n_it = kKeyMajor ? nblk - i0 : (a.causal ? blk + 1 : nblk);
   const int colq = h * 3 * kD;
   const uint64_t tmo = a.timeout_ns;
 
   if (threadIdx.x == 0) {
     tma_prefetch_desc(&tm_qkv);
     tma_prefetch_desc(&tm_do);
-    mbar_init(kv_full, 1);
-    mbar_init(qdo_full, 1);
-    mbar_init(qdo_empty, 1);
-    mbar_init(sdp_full, 1);
-    mbar_init(pds_ready, kEwThreads);
-    mbar_init(mma_done, 1);
-    mbar_init(dq_drained, kEwThreads);
+    mbar_init(res_full, 1);
+    for (int i = 0; i < kRing; ++i) {
+      mbar_init(ring_full + i, 1);
+      mbar_init(ring_empty + i, 1);
+    }
+    mbar_init(s_full, 1);
+    mbar_init(s_full + 1, 1);
+    mbar_init(dp_full, 1);
+    mbar_init(p_ready, 256);
+    mbar_init(ds_ready, 256);
+    mbar_init(acc_done, 1);
     mbar_fence_init();
   }
   if (warp == 1) {
@@ -476,151 +523,275 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constan
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem = *tmem_slot;
-  const uint32_t t_s = tmem, t_dp = tmem + 128, t_dv = tmem + 256, t_dk = tmem + 384;
+  // key-major:   S^T [0,128)  dP^T [128,256)  dV [256,384)  dK [384,512)
+  // query-major: S buffers [0,128) [128,256)  dP [256,384)  dQ [384,512)
+  const uint32_t t_dp = tmem + (kKeyMajor ? 128 : 256);
+  const uint32_t t_acc0 = tmem + (kKeyMajor ? 256 : 384), t_acc1 = tmem + 384;
 
   if (warp == 0) {
     if (lane == 0) {
-      const int krow = b * a.seq + j_blk * kBlk;
-      mbar_expect_tx(kv_full, 2 * kTile);
-      load_tile(sK, &tm_qkv, kv_full, colq + kD, krow);
-      load_tile(sV, &tm_qkv, kv_full, colq + 2 * kD, krow);
+      const int rrow = b * a.seq + blk * kBlk;
+      mbar_expect_tx(res_full, 2 * kTile);
+      if (kKeyMajor) {
+        load_tile(sR0, &tm_qkv, res_full, colq + kD, rrow);        // K
+        load_tile(sR1, &tm_qkv, res_full, colq + 2 * kD, rrow);    // V
+      } else {
+        load_tile(sR0, &tm_qkv, res_full, colq, rrow);             // Q
+        load_tile(sR1, &tm_do, res_full, h * kD, rrow);            // dO
+      }
       for (int it = 0; it < n_it; ++it) {
-        if (!mbar_wait(qdo_empty, (it & 1) ^ 1, 6 * tmo)) {
+        const int st = it & 1;
+        if (!mbar_wait(ring_empty + st, ((it >> 1) & 1) ^ 1, 6 * tmo)) {
           report(a.status, kErrAttn + 11, it, 0);
           break;
         }
-        const int qrow = b * a.seq + (i0 + it) * kBlk;
-        mbar_expect_tx(qdo_full, 2 * kTile);
-        load_tile(sQ, &tm_qkv, qdo_full, colq, qrow);
-        load_tile(sdO, &tm_do, qdo_full, h * kD, qrow);
+        const int srow = b * a.seq + (i0 + it) * kBlk;
+        mbar_expect_tx(ring_full + st, 2 * kTile);
+        if (kKeyMajor) {
+          load_tile(sS0 + st * kTile, &tm_qkv, ring_full + st, colq, srow);            // Q
+          load_tile(sS1 + st * kTile, &tm_do, ring_full + st, h * kD, srow);           // dO
+        } else {
+          load_tile(sS0 + st * kTile, &tm_qkv, ring_full + st, colq + kD, srow);       // K
+          load_tile(sS1 + st * kTile, &tm_qkv, ring_full + st, colq + 2 * kD, srow);   // V
+        }
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      const uint32_t id_kk = make_idesc_bf16(128, 128, 0, 0);   // both operands K-major
-      const uint32_t id_mm = make_idesc_bf16(128, 128, 1, 1);   // both MN-major
-      const uint32_t id_km = make_idesc_bf16(128, 128, 0, 1);   // A K-major, B MN-major
-      const uint32_t k_a = smem_u32(sK), v_a = smem_u32(sV), q_a = smem_u32(sQ), do_a = smem_u32(sdO),
-                     p_a = smem_u32(sP), ds_a = smem_u32(sdS);
-      bool ok = mbar_wait(kv_full, 0, 2 * tmo);
-      if (!ok) report(a.status, kErrAttn + 12, 0, 0);
-      for (int it = 0; it < n_it && ok; ++it) {
-        if (!mbar_wait(qdo_full, it & 1, 2 * tmo) || !mbar_wait(dq_drained, (it & 1) ^ 1, 6 * tmo)) {
-          report(a.status, kErrAttn + 13, it, 0);
-          ok = false;
-          break;
+      const uint32_t id_s = make_idesc_bf16(128, 128, 0, 0);      // A K-major (smem) * B K-major
+      const uint32_t id_g = make_idesc_bf16(128, 128, 0, 1);      // A (TMEM) * B MN-major
+      // all operand descriptors, once: resident tiles; ring stage 0 (stage 1 = + kTile >> 4 in the
+      // start-address field)
+      uint64_t dr0[8], dr1[8], ds0k[8], ds1k[8], ds0m[8], ds1m[8];
+      {
+        const uint32_t r0 = smem_u32(sR0), r1 = smem_u32(sR1), b0 = smem_u32(sS0), b1 = smem_u32(sS1);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          dr0[k] = desc_kmajor(r0, k);
+          dr1[k] = desc_kmajor(r1, k);
+          ds0k[k] = desc_kmajor(b0, k);
+          ds1k[k] = desc_kmajor(b1, k);
+          ds0m[k] = desc_mnmajor(b0, k);
+          ds1m[k] = desc_mnmajor(b1, k);
         }
-        tc_fence_after_sync();
-#pragma unroll
-        for (int k = 0; k < 8; ++k)   // S = Q K^T
-          umma_f16(t_s, desc_kmajor(q_a, k), desc_kmajor(k_a, k), id_kk, k != 0);
-#pragma unroll
-        for (int k = 0; k < 8; ++k)   // dP = dO V^T
-          umma_f16(t_dp, desc_kmajor(do_a, k), desc_kmajor(v_a, k), id_kk, k != 0);
-        umma_commit(sdp_full);
-        if (!mbar_wait(pds_ready, it & 1, 6 * tmo)) {
-          report(a.status, kErrAttn + 14, it, 0);
-          ok = false;
-          break;
-        }
-        tc_fence_after_sync();
-#pragma unroll
-        for (int k = 0; k < 8; ++k)   // dV += P^T dO   (contraction over the query rows)
-          umma_f16(t_dv, desc_mnmajor(p_a, k), desc_mnmajor(do_a, k), id_mm, (it | k) != 0);
-#pragma unroll
-        for (int k = 0; k < 8; ++k)   // dK += dS^T Q
-          umma_f16(t_dk, desc_mnmajor(ds_a, k), desc_mnmajor(q_a, k), id_mm, (it | k) != 0);
-#pragma unroll
-        for (int k = 0; k < 8; ++k)   // dQ = dS K      (contraction over the key rows)
-          umma_f16(t_s, desc_kmajor(ds_a, k), desc_mnmajor(k_a, k), id_km, k != 0);
-        umma_commit(mma_done);
-        umma_commit(qdo_empty);
       }
+      constexpr uint64_t kStageOff = (uint64_t)(kTile >> 4);
+      bool ok = mbar_wait(res_full, 0, 2 * tmo);
+      if (!ok) report(a.status, kErrAttn + 12, 0, 0);
+      auto wait_ring = [&](int it) -> bool {
+        if (mbar_wait(ring_full + (it & 1), (it >> 1) & 1, 4 * tmo)) {
+          tc_fence_after_sync();
+          return true;
+        }
+        report(a.status, kErrAttn + 13, it, 0);
+        return false;
+      };
+      auto wait_ew = [&](uint64_t* bar, int it, uint32_t code) -> bool {
+        if (mbar_wait(bar, it & 1, 8 * tmo)) {
+          tc_fence_after_sync();
+          return true;
+        }
+        report(a.status, code, it, 0);
+        return false;
+      };
+      // S (or S^T) of block `it` into score buffer `buf`; dP (or dP^T) of block `it`
+      auto issue_s = [&](int it, int buf) {
+        const uint64_t so = (it & 1) ? kStageOff : 0;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) umma_f16(tmem + buf * 128, dr0[k], ds0k[k] + so, id_s, k != 0);
+        umma_commit(s_full + buf);
+      };
+      auto issue_dp = [&](int it) {
+        const uint64_t so = (it & 1) ? kStageOff : 0;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) umma_f16(t_dp, dr1[k], ds1k[k] + so, id_s, k != 0);
+        umma_commit(dp_full);
+      };
+      if (ok && n_it > 0) {
+        ok = wait_ring(0);
+        if (ok) {
+          issue_s(0, 0);
+          issue_dp(0);
+        }
+      }
+      for (int it = 0; it < n_it && ok; ++it) {
+        const uint64_t so = (it & 1) ? kStageOff : 0;
+        const bool more = it + 1 < n_it;
+        if (kKeyMajor) {
+          if (!(ok = wait_ew(p_ready, it, kErrAttn + 14))) break;
+#pragma unroll
+          for (int k = 0; k < 8; ++k)   // dV += P^T dO   (contraction over the 128 queries)
+            umma_f16_ts(t_acc0, tmem + (k >> 2) * 64 + (k & 3) * 8, ds1m[k] + so, id_g, (it | k) != 0);
+          if (more) {
+            if (!(ok = wait_ring(it + 1))) break;
+            issue_s(it + 1, 0);         // S^T region: P^T(it) was read by the products just issued
+          }
+          if (!(ok = wait_ew(ds_ready, it, kErrAttn + 14))) break;
+#pragma unroll
+          for (int k = 0; k < 8; ++k)   // dK += dS^T Q
+            umma_f16_ts(t_acc1, t_dp + (k >> 2) * 64 + (k & 3) * 8, ds0m[k] + so, id_g, (it | k) != 0);
+          umma_commit(ring_empty + (it & 1));
+          if (more) issue_dp(it + 1);
+        } else {
+          if (more) {
+            if (!(ok = wait_ring(it + 1))) break;
+            issue_s(it + 1, (it + 1) & 1);
+          }
+          if (!(ok = wait_ew(ds_ready, it, kErrAttn + 14))) break;
+#pragma unroll
+          for (int k = 0; k < 8; ++k)   // dQ += dS K     (contraction over the 128 keys)
+            umma_f16_ts(t_acc0, t_dp + (k >> 2) * 64 + (k & 3) * 8, ds0m[k] + so, id_g, (it | k) != 0);
+          umma_commit(ring_empty + (it & 1));
+          if (more) issue_dp(it + 1);
+        }
+      }
+      if (ok) umma_commit(acc_done);
     }
   } else {
     const int q4 = warp & 3;
-    const int col0 = ((warp - 2) >> 2) * kColsPer;   // this thread's columns of every 128-wide row
-    const int row = q4 * 32 + lane;
-    const uint32_t lane_off = (static_cast<uint32_t>(q4 * 32) << 16) + col0;
+    const int half = (warp - 2) >> 2;                     // which 64 of the 128 columns
+    const int row = q4 * 32 + lane;                       // TMEM lane: key (key-major) or query
+    const uint32_t lane_off = static_cast<uint32_t>(q4 * 32) << 16;
     const float sl2 = a.scale * kLog2e;
+    const int64_t stat0 = ((int64_t)b * a.heads + h) * a.seq;
+    float my_lse2 = 0.f, my_delta = 0.f;
+    if (!kKeyMajor) {
+      my_lse2 = a.lse2[stat0 + blk * kBlk + row];
+      my_delta = a.delta[stat0 + blk * kBlk + row];
+    }
+    const int me = blk * kBlk + row;                      // this lane's key (key-major) or query index
     bool ok = true;
     for (int it = 0; it < n_it; ++it) {
-      const int i_blk = i0 + it;
-      const int64_t qtok = (int64_t)b * a.seq + i_blk * kBlk + row;
-      const int64_t sidx = ((int64_t)b * a.heads + h) * a.seq + i_blk * kBlk + row;
-      const float lse2 = a.lse[sidx] * kLog2e;
-      const float dlt = a.delta[sidx];
-      if (!warp_wait(sdp_full, it & 1, 8 * tmo)) {
+      const int sb = kKeyMajor ? 0 : (it & 1);
+      const uint32_t ts = tmem + lane_off + sb * 128 + half * 64;
+      const uint32_t tdp = t_dp + lane_off + half * 64;
+      const int c0 = (i0 + it) * kBlk + half * 64;        // first streamed index of this thread's columns
+      // causal: a score survives when key <= query; only blocks that touch the diagonal pay for it
+      const bool masked = a.causal && (kKeyMajor ? (c0 < me) : (c0 + 63 > me));
+      uint32_t pk[32];                                    // P of this thread's 64 columns, packed bf16
+      // ---- phase 1: P = exp2(S * scale * log2(e) - lse2) ----
+      if (!warp_wait(s_full + sb, kKeyMajor ? (it & 1) : ((it >> 1) & 1), 8 * tmo)) {
         if (lane == 0) report(a.status, kErrAttn + 15, it, 0);
         ok = false;
         break;
       }
       tc_fence_after_sync();
-      const bool diag = a.causal && i_blk == j_blk;
-#pragma unroll 1
-      for (int c = 0; c < kChunks; ++c) {
-        uint32_t rs[32], rp[32];
-        tmem_ld_32x32(t_s + lane_off + c * 32, rs);
-        tmem_ld_32x32(t_dp + lane_off + c * 32, rp);
-        tmem_ld_wait();
-        float p[32], ds[32];
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float e = fast_exp2(__uint_as_float(rs[i]) * sl2 - lse2);
-          if (diag && col0 + c * 32 + i > row) e = 0.f;
-          p[i] = e;
-          ds[i] = e * (__uint_as_float(rp[i]) - dlt) * a.scale;
+      for (int c = 0; c < 2; ++c) {
+        uint32_t rs[32];
+        tmem_ld_32x32(ts + c * 32, rs);
+        float ls[32];
+        if (kKeyMajor) {   // one address per warp: broadcast loads of 16 bytes
+          const float4* lp = reinterpret_cast<const float4*>(a.lse2 + stat0 + c0 + c * 32);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const float4 x = __ldg(lp + i);
+            ls[4 * i] = x.x; ls[4 * i + 1] = x.y; ls[4 * i + 2] = x.z; ls[4 * i + 3] = x.w;
+          }
         }
-        store_tile_row32(sP, row, col0 + c * 32, p);
-        store_tile_row32(sdS, row, col0 + c * 32, ds);
+        tmem_ld_wait();
+        if (!masked) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            const float e0 = fast_exp2(fmaf(__uint_as_float(rs[i]), sl2, -(kKeyMajor ? ls[i] : my_lse2)));
+            const float e1 = fast_exp2(fmaf(__uint_as_float(rs[i + 1]), sl2, -(kKeyMajor ? ls[i + 1] : my_lse2)));
+            pk[c * 16 + (i >> 1)] = pack_bf16(e0, e1);
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            float e0 = fast_exp2(fmaf(__uint_as_float(rs[i]), sl2, -(kKeyMajor ? ls[i] : my_lse2)));
+            float e1 = fast_exp2(fmaf(__uint_as_float(rs[i + 1]), sl2, -(kKeyMajor ? ls[i + 1] : my_lse2)));
+            const int q0 = c0 + c * 32 + i;
+            if (!(kKeyMajor ? (me <= q0) : (q0 <= me))) e0 = 0.f;
+            if (!(kKeyMajor ? (me <= q0 + 1) : (q0 + 1 <= me))) e1 = 0.f;
+            pk[c * 16 + (i >> 1)] = pack_bf16(e0, e1);
+          }
+        }
       }
-      fence_proxy_async_smem();
-      tc_fence_before_sync();
-      mbar_arrive(pds_ready);
-      if (!warp_wait(mma_done, it & 1, 8 * tmo)) {
+      if (kKeyMajor) {
+        // P^T over this thread's own S^T columns: 64 bf16 = 32 TMEM columns from the half's first column
+        uint32_t lo[16], hi[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) { lo[i] = pk[i]; hi[i] = pk[16 + i]; }
+        tmem_st_32x16(ts, lo);
+        tmem_st_32x16(ts + 16, hi);
+        tmem_st_wait();
+        tc_fence_before_sync();
+        mbar_arrive(p_ready);
+      }
+      // ---- phase 2: dS = P * (dP * scale - delta * scale) ----
+      if (!warp_wait(dp_full, it & 1, 8 * tmo)) {
         if (lane == 0) report(a.status, kErrAttn + 16, it, 0);
         ok = false;
         break;
       }
       tc_fence_after_sync();
-      float* dq = a.dq_acc + qtok * (a.heads * kD) + h * kD + col0;
-#pragma unroll 1
-      for (int c = 0; c < kChunks; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(t_s + lane_off + c * 32, r);
+      uint32_t dk[32];
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        uint32_t rp[32];
+        tmem_ld_32x32(tdp + c * 32, rp);
+        float dl[32];
+        if (kKeyMajor) {
+          const float4* dp = reinterpret_cast<const float4*>(a.delta + stat0 + c0 + c * 32);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const float4 y = __ldg(dp + i);
+            dl[4 * i] = y.x; dl[4 * i + 1] = y.y; dl[4 * i + 2] = y.z; dl[4 * i + 3] = y.w;
+          }
+        }
         tmem_ld_wait();
 #pragma unroll
-        for (int q = 0; q < 8; ++q) {
-          asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dq + c * 32 + q * 4),
-                       "f"(__uint_as_float(r[q * 4 + 0])), "f"(__uint_as_float(r[q * 4 + 1])),
-                       "f"(__uint_as_float(r[q * 4 + 2])), "f"(__uint_as_float(r[q * 4 + 3]))
-                       : "memory");
+        for (int i = 0; i < 32; i += 2) {
+          const uint32_t pp = pk[c * 16 + (i >> 1)];
+          const float e0 = __uint_as_float(pp << 16), e1 = __uint_as_float(pp & 0xffff0000u);
+          const float g0 = e0 * fmaf(__uint_as_float(rp[i]), a.scale, -(kKeyMajor ? dl[i] : my_delta));
+          const float g1 = e1 * fmaf(__uint_as_float(rp[i + 1]), a.scale, -(kKeyMajor ? dl[i + 1] : my_delta));
+          dk[c * 16 + (i >> 1)] = pack_bf16(g0, g1);
         }
       }
-      tc_fence_before_sync();
-      mbar_arrive(dq_drained);
+      {
+        uint32_t lo[16], hi[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) { lo[i] = dk[i]; hi[i] = dk[16 + i]; }
+        tmem_st_32x16(tdp, lo);       // dS over this thread's own dP columns
+        tmem_st_32x16(tdp + 16, hi);
+        tmem_st_wait();
+        tc_fence_before_sync();
+        mbar_arrive(ds_ready);
+      }
     }
     if (ok) {
-      // dV and dK of this key block are complete (mma_done of the last iteration was awaited)
-      __nv_bfloat16* base = reinterpret_cast<__nv_bfloat16*>(a.out) +
-                            ((int64_t)b * a.seq + j_blk * kBlk + row) * (a.heads * 3 * kD) + colq;
+      if (!warp_wait(acc_done, 0, 8 * tmo)) {
+        if (lane == 0) report(a.status, kErrAttn + 17, 0, 0);
+        ok = false;
+      }
+    }
+    if (ok) {
+      tc_fence_after_sync();
+      // accumulators -> bf16 rows of dqkv; the two threads of a lane take 64 columns each
+      __nv_bfloat16* base = reinterpret_cast<__nv_bfloat16*>(a.dqkv) +
+                            ((int64_t)b * a.seq + blk * kBlk + row) * (a.heads * 3 * kD) + colq;
+      const int n_acc = kKeyMajor ? 2 : 1;
 #pragma unroll 1
-      for (int which = 0; which < 2; ++which) {
-        const uint32_t t = (which == 0 ? t_dk : t_dv) + lane_off;
-        __nv_bfloat16* dst = base + (which == 0 ? kD : 2 * kD) + col0;
+      for (int which = 0; which < n_acc; ++which) {
+        // key-major: acc0 = dV, acc1 = dK;  query-major: acc0 = dQ
+        const uint32_t t = (which == 0 ? t_acc0 : t_acc1) + lane_off + half * 64;
+        __nv_bfloat16* dst = base + (kKeyMajor ? (which == 0 ? 2 * kD : kD) : 0) + half * 64;
 #pragma unroll 1
-        for (int c = 0; c < kChunks; ++c) {
+        for (int c = 0; c < 2; ++c) {
           uint32_t r[32];
           tmem_ld_32x32(t + c * 32, r);
           tmem_ld_wait();
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
-            uint4 u;
-            u.x = pack_bf16(__uint_as_float(r[q * 8 + 0]), __uint_as_float(r[q * 8 + 1]));
-            u.y = pack_bf16(__uint_as_float(r[q * 8 + 2]), __uint_as_float(r[q * 8 + 3]));
-            u.z = pack_bf16(__uint_as_float(r[q * 8 + 4]), __uint_as_float(r[q * 8 + 5]));
-            u.w = pack_bf16(__uint_as_float(r[q * 8 + 6]), __uint_as_float(r[q * 8 + 7]));
-            *reinterpret_cast<uint4*>(dst + c * 32 + q * 8) = u;
+            uint4 v;
+            v.x = pack_bf16(__uint_as_float(r[q * 8 + 0]), __uint_as_float(r[q * 8 + 1]));
+            v.y = pack_bf16(__uint_as_float(r[q * 8 + 2]), __uint_as_float(r[q * 8 + 3]));
+            v.z = pack_bf16(__uint_as_float(r[q * 8 + 4]), __uint_as_float(r[q * 8 + 5]));
+            v.w = pack_bf16(__uint_as_float(r[q * 8 + 6]), __uint_as_float(r[q * 8 + 7]));
+            *reinterpret_cast<uint4*>(dst + c * 32 + q * 8) = v;
           }
         }
       }
@@ -632,17 +803,6 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constan
   if (warp == 1) tmem_dealloc(tmem, 512);
 }
 
-constexpr size_t kAttnSmem = 6 * kTile + 256 + 2 * 2 * kBlk * sizeof(float) + 1024;
-
-// Element-wise warps per CTA: 8 unless MSB_ATTN_EW_WARPS=4 is set in the environment.
-int ew_warps() {
-  static const int v = [] {
-    const char* e = std::getenv("MSB_ATTN_EW_WARPS");
-    return (e != nullptr && e[0] == '4' && e[1] == '\0') ? 4 : 8;
-  }();
-  return v;
-}
-
 // The shared-memory attribute is per device: set it once on every device that launches.
 cudaError_t configure_device() {
   static bool configured[64] = {false};
@@ -650,13 +810,11 @@ cudaError_t configure_device() {
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return e;
   if (dev >= 0 && dev < 64 && configured[dev]) return cudaSuccess;
-  e = cudaFuncSetAttribute(attn_fwd_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kAttnSmem);
+  e = cudaFuncSetAttribute(attn_fwd2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kFwd2Smem);
   if (e != cudaSuccess) return e;
-  e = cudaFuncSetAttribute(attn_fwd_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kAttnSmem);
+  e = cudaFuncSetAttribute(attn_bwd2_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kBwd2Smem);
   if (e != cudaSuccess) return e;
-  e = cudaFuncSetAttribute(attn_bwd_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kAttnSmem);
-  if (e != cudaSuccess) return e;
-  e = cudaFuncSetAttribute(attn_bwd_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kAttnSmem);
+  e = cudaFuncSetAttribute(attn_bwd2_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kBwd2Smem);
   if (e != cudaSuccess) return e;
   if (dev >= 0 && dev < 64) configured[dev] = true;
   return cudaSuccess;
@@ -683,8 +841,7 @@ cudaError_t attention_fwd(const void* qkv, void* out, float* lse, int batch, int
   a.status = status;
   a.timeout_ns = 2000000000ull;
   dim3 grid(seq / kBlk, heads, batch);
-  if (ew_warps() == 8) attn_fwd_kernel<8><<<grid, attn_threads(8), kAttnSmem, stream>>>(tm, a);
-  else attn_fwd_kernel<4><<<grid, attn_threads(4), kAttnSmem, stream>>>(tm, a);
+  attn_fwd2_kernel<<<grid, 192, kFwd2Smem, stream>>>(tm, a);
   return cudaGetLastError();
 }
 
@@ -697,35 +854,35 @@ cudaError_t attention_bwd(const void* qkv, const void* out, const void* dout, co
     if (e0 != cudaSuccess) return e0;
   }
   const int64_t tokens = (int64_t)batch * seq;
-  cudaError_t e = cudaMemsetAsync(dq_acc, 0, tokens * heads * kD * sizeof(float), stream);
-  if (e != cudaSuccess) return e;
   {
+    // delta * scale into `delta`, lse * log2(e) into the head of the `dq_acc` scratch
     const int64_t warps = tokens * heads;
     const int threads = 256;
     const int64_t blocks = (warps * 32 + threads - 1) / threads;
     attn_delta_kernel<<<(unsigned)blocks, threads, 0, stream>>>(
-        reinterpret_cast<const __nv_bfloat16*>(out), reinterpret_cast<const __nv_bfloat16*>(dout), delta, batch, seq, heads);
+        reinterpret_cast<const __nv_bfloat16*>(out), reinterpret_cast<const __nv_bfloat16*>(dout), delta, batch, seq, heads,
+        lse, dq_acc, scale);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
   }
   CUtensorMap tq, td;
   const uint64_t width = (uint64_t)heads * 3 * kD, wdo = (uint64_t)heads * kD;
   if (make_tensor_map_2d(&tq, qkv, width, (uint64_t)tokens, width * 2, 64, kBlk) != 0) return cudaErrorInvalidValue;
   if (make_tensor_map_2d(&td, dout, wdo, (uint64_t)tokens, wdo * 2, 64, kBlk) != 0) return cudaErrorInvalidValue;
-  AttnArgs a{};
-  a.out = dqkv;
-  a.lse = const_cast<float*>(lse);
-  a.dq_acc = dq_acc;
-  a.delta = delta;
-  a.batch = batch; a.seq = seq; a.heads = heads; a.causal = causal;
-  a.scale = scale;
-  a.status = status;
-  a.timeout_ns = 2000000000ull;
-  dim3 grid(seq / kBlk, heads, batch);
-  if (ew_warps() == 8) attn_bwd_kernel<8><<<grid, attn_threads(8), kAttnSmem, stream>>>(tq, td, a);
-  else attn_bwd_kernel<4><<<grid, attn_threads(4), kAttnSmem, stream>>>(tq, td, a);
-  e = cudaGetLastError();
+  // two deterministic kernels: dK / dV per key block, dQ per query block
+  Bwd2Args g{};
+  g.dqkv = dqkv;
+  g.lse2 = dq_acc;     // lse * log2(e)
+  g.delta = delta;     // delta * scale
+  g.batch = batch; g.seq = seq; g.heads = heads; g.causal = causal;
+  g.scale = scale;
+  g.status = status;
+  g.timeout_ns = 2000000000ull;
+  dim3 grid2(seq / kBlk, heads, batch);
+  attn_bwd2_kernel<true><<<grid2, kBwd2Threads, kBwd2Smem, stream>>>(tq, td, g);
+  cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return e;
-  attn_dq_store_kernel<<<148 * 8, 256, 0, stream>>>(reinterpret_cast<const float4*>(dq_acc),
-                                                   reinterpret_cast<__nv_bfloat16*>(dqkv), tokens, heads);
+  attn_bwd2_kernel<false><<<grid2, kBwd2Threads, kBwd2Smem, stream>>>(tq, td, g);
   return cudaGetLastError();
 }
 

@@ -12,8 +12,10 @@ namespace msb {
 cudaError_t attention_fwd(const void* qkv, void* out, float* lse, int batch, int seq, int heads,
                           int causal, float scale, uint32_t* status, cudaStream_t stream);
 
-// dqkv (same layout as qkv) from dout.  `dq_acc` is fp32 scratch [batch*seq, heads*128] and
-// `delta` fp32 scratch [batch, heads, seq]; both are overwritten.
+// dqkv (same layout as qkv) from dout.  `dq_acc` and `delta` are fp32 scratch of at least
+// batch * heads * seq elements each (they receive lse * log2(e) and rowsum(dO * O) * scale); both
+// are overwritten.  The gradients are accumulated in tensor memory by the CTA that owns them, so the
+// result is bit-identical from run to run.
 cudaError_t attention_bwd(const void* qkv, const void* out, const void* dout, const float* lse,
                           void* dqkv, float* dq_acc, float* delta, int batch, int seq, int heads,
                           int causal, float scale, uint32_t* status, cudaStream_t stream);

@@ -210,7 +210,7 @@ def attention_bwd(dout, qkv, out, lse, batch: int, seq: int, heads: int, causal:
     if qkv.is_cuda and D == 128 and seq % 128 == 0:
         dqkv = torch.empty_like(qkv)
         delta = torch.empty(batch, heads, seq, dtype=torch.float32, device=qkv.device)
-        dq_acc = torch.empty(batch * seq, heads * D, dtype=torch.float32, device=qkv.device)
+        dq_acc = torch.empty(batch, heads, seq, dtype=torch.float32, device=qkv.device)   # scratch: lse * log2(e)
         dout = dout.contiguous()
         _C().attention_bwd(qkv.data_ptr(), out.data_ptr(), dout.data_ptr(), lse.data_ptr(),
                            dqkv.data_ptr(), dq_acc.data_ptr(), delta.data_ptr(), batch, seq, heads,

@@ -56,3 +56,19 @@ def test_attention_large_scores_exercise_rescaling():
     o_ref, lse_ref, _ = _ref(qkv, batch, seq, heads, False, dout)
     assert (out.float() - o_ref).abs().max().item() < 0.05
     assert (lse - lse_ref).abs().max().item() < 0.05
+
+
+def test_attention_backward_is_bit_identical_from_run_to_run():
+    """dQ, dK and dV are accumulated in tensor memory by the CTA that owns them, never added to
+    global memory from several CTAs: the same inputs give the same bits."""
+    from meshslice_b200 import _native
+    from meshslice_b200.ops import functional as F
+    batch, seq, heads = 2, 1024, 4
+    g = torch.Generator(device="cuda").manual_seed(5)
+    qkv = torch.randn(batch * seq, heads * 3 * 128, device="cuda", generator=g).bfloat16()
+    dout = torch.randn(batch * seq, heads * 128, device="cuda", generator=g).bfloat16()
+    out, lse = F.attention_fwd(qkv, batch, seq, heads, True)
+    a = F.attention_bwd(dout, qkv, out, lse, batch, seq, heads, True).clone()
+    b = F.attention_bwd(dout, qkv, out, lse, batch, seq, heads, True)
+    _native.check_status()
+    assert torch.equal(a, b)
