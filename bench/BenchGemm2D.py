@@ -5,7 +5,8 @@ NCCL + library-GEMM formulation, for several global shapes and slice counts on o
     torchrun --nproc-per-node 8 bench/BenchGemm2D.py --mesh 2x4 --slices 1 2 4 8 --json out.json
 
 Per case it prints achieved TFLOP/s per GPU and the fraction of the roofline
-max(FLOPs / measured GEMM peak, NVLink bytes / measured link bandwidth).
+max(FLOPs / measured GEMM peak, NVLink bytes / measured link bandwidth).  L2 is flushed before every
+timed call; times are CUDA-event times on the launching stream, maximum over the ranks.
 """
 import argparse
 import json
@@ -20,18 +21,27 @@ sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 SHAPES = [(16384, 4096, 16384), (16384, 16384, 4096), (16384, 12288, 49152), (16384, 49152, 12288)]  # M, K, N
 
 
-def timeit(fn, iters=5, warm=2):
+_FLUSH = None
+
+
+def timeit(fn, iters=5, warm=3):
+    """Mean device time of one call (CUDA events around every call on the launching stream, L2 flushed
+    by a 256 MiB write before each, 3 warm-up calls), maximum over the ranks."""
+    global _FLUSH
+    if _FLUSH is None:
+        _FLUSH = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
     for _ in range(warm):
         fn()
     torch.cuda.synchronize()
     dist.barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(iters):
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(iters)]
+    for e0, e1 in evs:
+        _FLUSH.zero_()
+        e0.record()
         fn()
-    e1.record()
+        e1.record()
     torch.cuda.synchronize()
-    t = torch.tensor([e0.elapsed_time(e1) / iters], device="cuda")
+    t = torch.tensor([sum(e0.elapsed_time(e1) for e0, e1 in evs) / iters], device="cuda")
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     return t.item() * 1e-3
 

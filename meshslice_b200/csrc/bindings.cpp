@@ -154,6 +154,11 @@ void gemm_run(const py::dict& d) {
   a.b_flag_mode = (int)geti(d, "b_flag_mode");
   a.b_flag_base = (int)geti(d, "b_flag_base");
   a.b_flag_count = (int)geti(d, "b_flag_count");
+  a.a_flag_target = (uint32_t)geti(d, "a_flag_target", 0);
+  a.b_flag_target = (uint32_t)geti(d, "b_flag_target", 0);
+  if ((a.a_flag_mode != 0 && a.a_flag_mode != 3 && a.a_flag_target == 0) ||
+      (a.b_flag_mode != 0 && a.b_flag_mode != 3 && a.b_flag_target == 0))
+    throw std::runtime_error("gemm: a gathered operand needs its flag target");
   a.b_nchunk = (int)geti(d, "b_nchunk", 1);
   if (a.b_nchunk < 1) a.b_nchunk = 1;
   a.a_kpanel = (int)geti(d, "a_kpanel", 1);

@@ -147,13 +147,15 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 __device__ __forceinline__ float bf16_lo(uint32_t v) { return __uint_as_float(v << 16); }
 __device__ __forceinline__ float bf16_hi(uint32_t v) { return __uint_as_float(v & 0xffff0000u); }
 
-// Waits for the chunk flags of one operand (bumped by this GPU's and by peers' CTAs).
-__device__ __forceinline__ bool wait_chunk(const GemmArgs& a, int idx, uint64_t tmo) {
-  return wait_flag_geq_sys(a.chunk_flags + idx, a.chunks[idx].target, tmo);
+// Waits for one chunk flag of an operand (bumped by this GPU's and by peers' communication warps).
+// The value that means "complete" belongs to the operand (a_flag_target / b_flag_target), not to the
+// chunk's position in the travel order: the chunk list is ordered by need, the flags by operand.
+__device__ __forceinline__ bool wait_chunk(const GemmArgs& a, int idx, uint32_t target, uint64_t tmo) {
+  return wait_flag_geq_sys(a.chunk_flags + idx, target, tmo);
 }
 // `seen` remembers chunks already observed complete, so that only the first tile that needs a
 // chunk pays for the system-scope flag reads.
-__device__ __forceinline__ bool wait_operand(const GemmArgs& a, int mode, int base, int count,
+__device__ __forceinline__ bool wait_operand(const GemmArgs& a, int mode, int base, int count, uint32_t target,
                                              int slice, int col_chunk, uint64_t tmo, uint64_t& seen) {
   if (mode == 0 || mode == 3) return true;   // mode 3 is waited for inside the contraction loop
   const int lo = mode == 1 ? base + slice : (mode == 4 ? base + col_chunk : base);
@@ -161,7 +163,7 @@ __device__ __forceinline__ bool wait_operand(const GemmArgs& a, int mode, int ba
   for (int i = lo; i < hi; ++i) {
     const uint64_t bit = 1ull << (i & 63);
     if (i < 64 && (seen & bit)) continue;
-    if (!wait_chunk(a, i, tmo)) return false;
+    if (!wait_chunk(a, i, target, tmo)) return false;
     if (i < 64) seen |= bit;
   }
   return true;
@@ -574,8 +576,10 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
         if (a.a_flag_mode | a.b_flag_mode) {
           const uint64_t before = seen;
           const int cc = tc.n_blk / a.b_nchunk;   // column chunk of B (flag mode 4)
-          if (!wait_operand(a, a.a_flag_mode, a.a_flag_base, a.a_flag_count, tc.slice, 0, 3 * tmo, seen) ||
-              !wait_operand(a, a.b_flag_mode, a.b_flag_base, a.b_flag_count, tc.slice, cc, 3 * tmo, seen)) {
+          if (!wait_operand(a, a.a_flag_mode, a.a_flag_base, a.a_flag_count, a.a_flag_target, tc.slice, 0,
+                            3 * tmo, seen) ||
+              !wait_operand(a, a.b_flag_mode, a.b_flag_base, a.b_flag_count, a.b_flag_target, tc.slice, cc,
+                            3 * tmo, seen)) {
             report(a, kTimeoutChunk, t, tc.slice);
             ok = false;
             break;

@@ -120,6 +120,8 @@ struct GemmArgs {
   int b_flag_mode;
   int b_flag_base, b_flag_count;
   int b_nchunk;                // flag mode 4: 256-column blocks of B per chunk (>= 1)
+  uint32_t a_flag_target;      // flag value once a chunk of A / of B is complete (modes 1, 2, 4):
+  uint32_t b_flag_target;      // communication warps per GPU x GPUs contributing to the operand
   // flag mode 3 ("K panels", the SUMMA / ring schedules): the operand arrives in panels of the
   // contraction dimension; k-block kb needs flag base + kb / kpanel, which counts to kp_target
   int a_kpanel, b_kpanel;      // 64-wide k-blocks per panel

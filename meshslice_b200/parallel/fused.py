@@ -319,9 +319,9 @@ class FusedGemm:
             d.update(jobs=jt.data_ptr(), chunks=ct.data_ptr(), n_chunks=n_chunks,
                      chunk_flags=ws.local(ws.flags + 4 * rt.CHUNK0))
             if gather_x:
-                d.update(a_flag_mode=1, a_flag_base=xbase)
+                d.update(a_flag_mode=1, a_flag_base=xbase, a_flag_target=self.signals * mc.C)
             if gather_w:
-                d.update(b_flag_mode=4, b_flag_base=0, b_flag_count=nW, b_nchunk=per)
+                d.update(b_flag_mode=4, b_flag_base=0, b_flag_count=nW, b_nchunk=per, b_flag_target=self.signals * mc.R)
         if bias is not None:
             d["bias"] = bias.data_ptr()
         if act == "gelu":
@@ -464,7 +464,8 @@ class FusedGemm:
         if gather_w:
             jt, ct, n_chunks = self._jobs(("ls", m, kl, nr, S), build)
             d.update(jobs=jt.data_ptr(), chunks=ct.data_ptr(), n_chunks=n_chunks,
-                     chunk_flags=ws.local(ws.flags + 4 * rt.CHUNK0), b_flag_mode=1, b_flag_base=0)
+                     chunk_flags=ws.local(ws.flags + 4 * rt.CHUNK0), b_flag_mode=1, b_flag_base=0,
+                     b_flag_target=self.signals * mc.R)
         if mc.C > 1:   # a mesh row of one GPU keeps its product: plain epilogue into `out`
             d.update(
                  push_n=mc.C, push_dim=1, push_extent=nc, push_ld=nc, push_rows=m,
@@ -527,7 +528,8 @@ class FusedGemm:
         if gather_x:
             jt, ct, n_chunks = self._jobs(("rs", kr, ml, n, S, cyc), build)
             d.update(jobs=jt.data_ptr(), chunks=ct.data_ptr(), n_chunks=n_chunks,
-                     chunk_flags=ws.local(ws.flags + 4 * rt.CHUNK0), a_flag_mode=1, a_flag_base=0)
+                     chunk_flags=ws.local(ws.flags + 4 * rt.CHUNK0), a_flag_mode=1, a_flag_base=0,
+                     a_flag_target=self.signals * mc.C)
         if mc.R > 1:   # a mesh column of one GPU keeps its product: plain epilogue into `out`
             d.update(
                  push_n=mc.R, push_dim=0, push_extent=mr, push_ld=n, push_rows=mr,

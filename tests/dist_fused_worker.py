@@ -26,17 +26,15 @@ def main():
     mode = os.environ.get("MODE", "gemm")
     R, C = [int(v) for v in os.environ.get("MESH", f"1x{world}").split("x")]
     fails = []
-    if mode == "train":
-        train(R, C, rank, world)
-    else:
-        from meshslice_b200.parallel.engine import FusedEngine
-        from meshslice_b200.parallel.mesh import DistMesh
-        mesh = DistMesh(R, C)
-        big = os.environ.get("BIG", "0") == "1"
-        ws = (512 << 20) if big else (64 << 20)
-        eng = FusedEngine(mesh, ws, ws, ws, timeout_ns=4_000_000_000, exchange_rows=8192,
-                          extra_heap_bytes=(96 << 20) if mode == "p2p" else 0)
-        {"gemm": gemm, "ops": ops, "p2p": p2p}[mode](mesh, eng, fails, big)
+    try:
+        _run(mode, R, C, rank, world, fails)
+    except Exception as e:     # a kernel status error or a plan error: say which rank and what
+        import traceback
+        fails.append(f"{type(e).__name__}: {e}")
+        print(f"rank {rank} EXCEPTION {type(e).__name__}: {e}\n{traceback.format_exc(limit=6)}", flush=True)
+        # the other ranks may be inside kernels that wait for this one: they give up at their own
+        # bounded waits; nothing more can be agreed on
+        os._exit(1)
     t = torch.tensor([len(fails)], device="cuda")
     if world > 1:
         dist.all_reduce(t)
@@ -48,6 +46,20 @@ def main():
         dist.barrier()
         dist.destroy_process_group()
     sys.exit(0 if t.item() == 0 else 1)
+
+
+def _run(mode, R, C, rank, world, fails):
+    if mode == "train":
+        train(R, C, rank, world)
+    else:
+        from meshslice_b200.parallel.engine import FusedEngine
+        from meshslice_b200.parallel.mesh import DistMesh
+        mesh = DistMesh(R, C)
+        big = os.environ.get("BIG", "0") == "1"
+        ws = (512 << 20) if big else (64 << 20)
+        eng = FusedEngine(mesh, ws, ws, ws, timeout_ns=int(os.environ.get("TIMEOUT_NS", "2000000000")), exchange_rows=8192,
+                          extra_heap_bytes=(96 << 20) if mode == "p2p" else 0)
+        {"gemm": gemm, "ops": ops, "p2p": p2p}[mode](mesh, eng, fails, big)
 
 
 def _close(fails, name, out, ref, K):

@@ -126,6 +126,18 @@ def test_os_plans_fill_both_staging_buffers_once(mesh):
         assert order == [0, nW] + list(range(1, nW)) + list(range(nW + 1, nW + d["n_slices"]))
         for ch, idx in zip(chunks, order):
             assert ch[3] == 296 * (R if idx < nW else C)
+        # what a consumer waits for is per operand, whatever the chunk's place in the travel order:
+        # the arrivals at every flag of rank 0 (all sources, 296 warps each) equal that operand's target
+        arrivals = {}
+        for cap in caps.values():
+            for (_jb, _je, sigs, _t) in cap["plan"][1]:
+                for sp in sigs:
+                    if (sp >> 40) == 1:
+                        f = ((sp & ((1 << 40) - 1)) // 4) - rt.CHUNK0
+                        arrivals[f] = arrivals.get(f, 0) + 296
+        assert d["b_flag_target"] == 296 * R and d["a_flag_target"] == 296 * C
+        for f, got in arrivals.items():
+            assert got == (d["b_flag_target"] if f < nW else d["a_flag_target"]), (f, got)
 
 
 @pytest.mark.parametrize("mesh", [(2, 4), (4, 2), (2, 2)])

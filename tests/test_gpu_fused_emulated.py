@@ -34,11 +34,11 @@ def _close(out, ref, K):
     assert ((out.float() - ref).norm() / ref.norm()).item() < 1.5e-2
 
 
-@pytest.mark.parametrize("mesh,slices", [((2, 2), 2), ((1, 4), 1), ((4, 2), 4)])
+@pytest.mark.parametrize("mesh,slices", [((2, 2), 2), ((1, 4), 1), ((4, 2), 4), ((2, 4), 2)])
 def test_os_gathers_both_operands(mesh, slices):
     from meshslice_b200 import _native
     R, C = mesh
-    M, Kd, N = 512 * R, 1024, 256 * C
+    M, Kd, N = 512 * R, 1024, 768 * C      # several W column chunks and X row slices on non-square meshes
     X = torch.randn(M, Kd, device="cuda").bfloat16()
     W = torch.randn(Kd, N, device="cuda").bfloat16()
     m, kl, kr, n = M // R, Kd // C, Kd // R, N // C

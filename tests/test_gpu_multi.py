@@ -27,7 +27,10 @@ def _run_worker(mesh, mode="gemm", slices=2, extra=None, timeout=600):
         cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}",
                "--master-addr", "127.0.0.1", "--master-port", str(_PORT[0]), os.path.join(_HERE, "dist_fused_worker.py")]
     res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=timeout)
-    assert res.returncode == 0 and "FUSED_MULTI_GPU_OK" in res.stdout, (res.stdout[-2000:], res.stderr[-3000:])
+    if res.returncode != 0 or "FUSED_MULTI_GPU_OK" not in res.stdout:
+        noise = ("[W", "W1", "W0", "OMP_NUM", "*****", "  File", "    ", "Traceback")
+        err = "\n".join(l for l in res.stderr.splitlines() if l.strip() and not l.startswith(noise))
+        pytest.fail(f"worker {mesh} {mode}: rc {res.returncode}\n{res.stdout[-3000:]}\n{err[-3000:]}")
 
 
 def _meshes(n):
