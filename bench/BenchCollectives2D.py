@@ -57,9 +57,11 @@ def main():
     ap.add_argument("which", nargs="?", default="all", choices=["allgather", "reducescatter", "sendrecv", "all"])
     ap.add_argument("--mesh", default="")
     ap.add_argument("--min-bytes", type=int, default=1 << 10)
-    ap.add_argument("--max-bytes", type=int, default=1 << 28, help="largest per-device shard")
+    ap.add_argument("--max-bytes", type=int, default=1 << 30, help="largest per-device shard (default 1 GiB)")
     ap.add_argument("--fabric-json", default="")
     ap.add_argument("--impl", default="both", choices=["nccl", "p2p", "both"])
+    ap.add_argument("--p2p-mode", default="push", choices=["push", "pull"],
+                    help="all-gather / send-recv of the P2P twins: posted stores to the peers, or loads from them")
     args = ap.parse_args()
 
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
@@ -73,7 +75,7 @@ def main():
 
     R, C = [int(v) for v in args.mesh.split("x")] if args.mesh else choose_mesh(world)
     mesh = DistMesh(R, C)
-    heap = rt.SymmHeap(args.max_bytes + (16 << 20))
+    heap = rt.SymmHeap(args.max_bytes * (1 + (max(R, C) if args.p2p_mode == "push" else 0)) + (16 << 20))
     p2p = P2PCollectives(mesh, heap, args.max_bytes)
     sizes = []
     b = args.min_bytes
@@ -105,9 +107,10 @@ def main():
                                   "reducescatter": lambda: mesh.reduce_scatter(st, axis, dim),
                                   "sendrecv": lambda: mesh.permute(st, axis, 1)}[kind]
                         else:
-                            fn = {"allgather": lambda: p2p.all_gather(rows, cols, axis, dim),
+                            push = args.p2p_mode == "push"
+                            fn = {"allgather": lambda: p2p.all_gather(rows, cols, axis, dim, push=push),
                                   "reducescatter": lambda: p2p.reduce_scatter(rows, cols, axis, dim),
-                                  "sendrecv": lambda: p2p.send_recv(rows, cols, axis)}[kind]
+                                  "sendrecv": lambda: p2p.send_recv(rows, cols, axis, push=push)}[kind]
                         ts = repeat_bench(fn, repeat=3 if nbytes >= (1 << 26) else 5, inner=3 if nbytes >= (1 << 26) else 10)
                         _native.check_status()
                         actual = rows * cols * 2

@@ -24,10 +24,14 @@ SHAPES = [(16384, 4096, 16384), (16384, 16384, 4096), (16384, 12288, 49152), (16
 _FLUSH = None
 
 
-def timeit(fn, iters=5, warm=3):
+_ITERS, _WARM = 5, 3
+
+
+def timeit(fn, iters=None, warm=None):
     """Mean device time of one call (CUDA events around every call on the launching stream, L2 flushed
     by a 256 MiB write before each, 3 warm-up calls), maximum over the ranks."""
     global _FLUSH
+    iters, warm = iters or _ITERS, _WARM if warm is None else warm
     if _FLUSH is None:
         _FLUSH = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
     for _ in range(warm):
@@ -57,8 +61,12 @@ def main():
     ap.add_argument("--baselines", nargs="*", default=[], choices=["summa", "wang", "cannon"],
                     help="also time the OS product on these K-panel schedules")
     ap.add_argument("--sub", type=int, default=2, help="sub-panels per owner for --baselines")
+    ap.add_argument("--iters", type=int, default=5, help="timed calls per case")
+    ap.add_argument("--warm", type=int, default=3, help="warm-up calls per case (at least 3 for reported numbers)")
     ap.add_argument("--json", default="")
     args = ap.parse_args()
+    global _ITERS, _WARM
+    _ITERS, _WARM = args.iters, args.warm
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", rank)))
     dist.init_process_group("nccl", device_id=torch.device("cuda", torch.cuda.current_device()))

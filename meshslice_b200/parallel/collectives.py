@@ -2,8 +2,12 @@
 with NCCL twins for comparison.  They are the B200 counterparts of the collectives that
 BenchCollectives2D.py:16-26 times, along either mesh axis and on either tensor dimension.
 
-All three pull: a rank reads its peers' input buffers directly over NVLink, so the input must
-live in the symmetric heap (``P2PCollectives.input``); outputs are ordinary local tensors.
+All-gather and send-recv PUSH by default: a rank reads its own input once and writes it into the
+output buffer of every peer (posted stores over NVLink, which do not wait for a round trip the way
+peer loads do); the output then lives in the symmetric heap (a view of it is returned).  With
+``push=False`` they pull instead (the rank reads its peers' inputs; output is a local tensor).
+Reduce-scatter pulls: every rank reads its chunk of all peers' inputs and sums it.  Inputs live in
+the symmetric heap (``P2PCollectives.input``).
 """
 from __future__ import annotations
 
@@ -52,6 +56,8 @@ class P2PCollectives:
         heap.bytes_view(self.flags, rt.FLAG_WORDS * 4).zero_()
         self.inp_off = heap.alloc(max_bytes)
         self.max_bytes = max_bytes
+        self.out_off = None           # output region of the push variants, allocated on first use
+        self.out_bytes = 0
         self.epoch = 0
         self.done_total = 0
         torch.cuda.synchronize()
@@ -81,11 +87,39 @@ class P2PCollectives:
         self.C.p2p_copy(jt.data_ptr(), len(jobs), self._bar(self.grid), self.grid, _native.stream_ptr())
         return jt
 
-    def all_gather(self, rows: int, cols: int, axis: str, dim: int, out: torch.Tensor = None):
+    def _out_region(self, nbytes: int) -> int:
+        """Offset of the symmetric output region (same on every rank: every rank allocates it at the
+        same point of its call sequence with the same size)."""
+        if self.out_off is None:
+            n_max = max(self.mesh.R, self.mesh.C)
+            self.out_bytes = n_max * self.max_bytes
+            self.out_off = self.heap.alloc(self.out_bytes)
+            torch.cuda.synchronize()
+            self.mesh.dist.barrier()
+        if nbytes > self.out_bytes:
+            raise ValueError(f"gathered output of {nbytes} bytes exceeds the output region ({self.out_bytes})")
+        return self.out_off
+
+    def all_gather(self, rows: int, cols: int, axis: str, dim: int, out: torch.Tensor = None, push: bool = True):
         """Gathers every peer's [rows, cols] bf16 input along ``axis`` and concatenates on ``dim``."""
         peers = self._peers(axis)
         n = len(peers)
         shape = (rows * n, cols) if dim == 0 else (rows, cols * n)
+        if push and out is None:
+            rb = cols * 2
+            off = self._out_region(n * rows * rb)
+            me = peers.index(self.heap.rank)
+            src = self.heap.ptr(self.heap.rank, self.inp_off)
+            jobs = []
+            for k in range(n):           # every rank starts at a different destination
+                q = peers[(me + 1 + k) % n]
+                base = self.heap.ptr(q, off)
+                if dim == 0:
+                    jobs.append((src, base + me * rows * rb, rows, rb, rb, rb))
+                else:
+                    jobs.append((src, base + me * rb, rows, rb, rb, n * rb))
+            self._keep = self._copy(jobs)     # the kernel's exit barrier: every rank's block has landed
+            return self.heap.tensor(off, shape)
         if out is None:
             out = torch.empty(shape, dtype=torch.bfloat16, device="cuda")
         rb = cols * 2
@@ -103,10 +137,16 @@ class P2PCollectives:
         self._keep = self._copy(jobs)
         return out
 
-    def send_recv(self, rows: int, cols: int, axis: str, out: torch.Tensor = None):
+    def send_recv(self, rows: int, cols: int, axis: str, out: torch.Tensor = None, push: bool = True):
         """Ring shift by +1: every rank receives the input of its predecessor along ``axis``."""
         peers = self._peers(axis)
         i = peers.index(self.heap.rank)
+        if push and out is None:
+            rb = cols * 2
+            off = self._out_region(rows * rb)
+            dst = self.heap.ptr(peers[(i + 1) % len(peers)], off)
+            self._keep = self._copy([(self.heap.ptr(self.heap.rank, self.inp_off), dst, rows, rb, rb, rb)])
+            return self.heap.tensor(off, (rows, cols))
         src = self.heap.ptr(peers[(i - 1) % len(peers)], self.inp_off)
         if out is None:
             out = torch.empty(rows, cols, dtype=torch.bfloat16, device="cuda")

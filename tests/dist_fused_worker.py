@@ -58,7 +58,7 @@ def _run(mode, R, C, rank, world, fails):
         big = os.environ.get("BIG", "0") == "1"
         ws = (512 << 20) if big else (64 << 20)
         eng = FusedEngine(mesh, ws, ws, ws, timeout_ns=int(os.environ.get("TIMEOUT_NS", "2000000000")), exchange_rows=8192,
-                          extra_heap_bytes=(96 << 20) if mode == "p2p" else 0)
+                          extra_heap_bytes=(32 << 20) * (2 + max(R, C)) if mode == "p2p" else 0)
         {"gemm": gemm, "ops": ops, "p2p": p2p}[mode](mesh, eng, fails, big)
 
 
@@ -198,11 +198,12 @@ def p2p(mesh, eng, fails, big):
         for dim in (0, 1):
             coll.input((rows, cols)).copy_(full[me])
             coll.barrier()
-            out = coll.all_gather(rows, cols, axis, dim)
-            eng.check()
-            if not torch.equal(out, torch.cat(full, dim=dim)):
-                fails.append(f"all_gather {axis} dim {dim}")
-            coll.barrier()
+            for push in (True, False):
+                out = coll.all_gather(rows, cols, axis, dim, push=push)
+                eng.check()
+                if not torch.equal(out, torch.cat(full, dim=dim)):
+                    fails.append(f"all_gather {axis} dim {dim} push={push}")
+                coll.barrier()
             out = coll.reduce_scatter(rows, cols, axis, dim)
             eng.check()
             tot = sum(t.float() for t in full)
@@ -212,11 +213,12 @@ def p2p(mesh, eng, fails, big):
             coll.barrier()
         coll.input((rows, cols)).copy_(full[me])
         coll.barrier()
-        out = coll.send_recv(rows, cols, axis)
-        eng.check()
-        if not torch.equal(out, full[(me - 1) % n]):
-            fails.append(f"send_recv {axis}")
-        coll.barrier()
+        for push in (True, False):
+            out = coll.send_recv(rows, cols, axis, push=push)
+            eng.check()
+            if not torch.equal(out, full[(me - 1) % n]):
+                fails.append(f"send_recv {axis} push={push}")
+            coll.barrier()
 
 
 def train(R, C, rank, world):
