@@ -10,6 +10,7 @@ and compared with the plain GEMM of the same shape.
 
     python bench/fused_case.py ls 4 8192 1024 16384 [slices] [iters]   # LS over C=4: m, k_local, N
     python bench/fused_case.py rs 2 2048 16384 4096 [slices] [iters]   # RS over R=2: k_local, M, n
+    python bench/fused_case.py os 4 8192 1024 4096 [slices] [iters]    # OS over C=4: m, k_local, n (gather of X)
     ncu --set full --clock-control none -k regex:sm100_gemm_kernel -s 8 -c 2 -o prof python bench/fused_case.py ls 4 4096 1024 8192 4 1
 """
 import json
@@ -85,11 +86,31 @@ def main():
         plain = lambda: gemm(xs[k0], wsd[k0], "tn", out=y)
         ref = sum(xs[(r, 0)].float().t()[:mr] @ wsd[(r, 0)].float() for r in range(n))
         flops = 2.0 * kr * M * nn
+    elif which == "os":      # Y[m, n] = AG_col(X)[m, C * kl] @ W[C * kl, n], R = 1: the gather side
+        m, kl, nn = d0, d1, d2
+        Kd = n * kl
+        ops = setup(1, n, m * Kd * 2, 16, 16)
+        xs = {k: torch.randn(m, kl, device="cuda").bfloat16() for k in ops}
+        wsd = {k: torch.randn(Kd, nn, device="cuda").bfloat16() for k in ops}
+        outs = {k: torch.empty(m, nn, device="cuda", dtype=torch.bfloat16) for k in ops}
+        run = lambda phase: [op.os([xs[(0, c)].data_ptr() for c in range(n)], [wsd[k].data_ptr()], m, kl, Kd, nn, outs[k],
+                                   n_slices=slices, phase=phase, reset=False) for k, op in ops.items()]
+        k0 = (0, 0)
+        xg = torch.cat([xs[(0, c)] for c in range(n)], dim=1)
+        y = torch.empty(m, nn, device="cuda", dtype=torch.bfloat16)
+        plain = lambda: gemm(xg, wsd[k0], "nn", out=y)
+        ref = xg.float() @ wsd[k0].float()
+        flops = 2.0 * m * Kd * nn
     else:
-        raise SystemExit("first argument: ls or rs")
+        raise SystemExit("first argument: os, ls or rs")
     for op in ops.values():
         op._reset_flags(_native.stream_ptr())
-    for phase in ("gemm", "reduce"):
+    if which == "os":
+        # gather-only launches: every emulated rank writes its shard into all n staging buffers
+        res["comm_ms"] = timeit(lambda: run("comm"), iters) / len(ops)
+        res["gather_gbs_written"] = n * m * kl * 2 / (res["comm_ms"] * 1e-3) / 1e9
+        _native.check_status()
+    for phase in (("gemm",) if which == "os" else ("gemm", "reduce")):
         res[phase + "_ms"] = timeit(lambda: run(phase), iters) / len(ops)
         _native.check_status()
     res["plain_gemm_ms"] = timeit(plain, iters)

@@ -195,6 +195,8 @@ void gemm_run(const py::dict& d) {
   a.red_ld = geti(d, "red_ld");
   a.red_counter = P<const uint32_t>(getp(d, "red_counter"));
   a.red_target = (uint32_t)geti(d, "red_target");
+  a.red_work = P<uint32_t>(getp(d, "red_work"));
+  if (a.red_n > 0 && a.red_work == nullptr) throw std::runtime_error("gemm: the reduce phase needs its work counters");
   a.red_slice_dim = (int)geti(d, "red_slice_dim");
   if (a.red_n > 0) {
     const int rt = a.red_slice_dim == 0 ? (a.red_rows + 2 * kBM - 1) / (2 * kBM) : (a.red_cols + kBN - 1) / kBN;

@@ -289,9 +289,11 @@ __device__ __forceinline__ void reduce_rows(const GemmArgs& a, const __nv_bfloat
 }
 
 // Sums the partial tiles of slice `s` that the push group's ranks wrote into this GPU's slots.
-// Work unit: 32 rows x 256 columns of one block; units are dealt round-robin to the aux warps of all
-// CTAs.  Fixed summation order (slot 0, 1, ...): the result does not depend on arrival order.
-__device__ void reduce_slice(const GemmArgs& a, int s, int worker, int n_workers, int lane) {
+// Work unit: 32 rows x 256 columns of one block.  Warps take units from a per-slice counter, so the
+// communication warps start a slice while the tiles of the next one run and the epilogue warps of a
+// CTA that has finished its tiles help with what is left.  Every unit is summed by one warp in fixed
+// order (slot 0, 1, ...): the result does not depend on arrival order nor on who took the unit.
+__device__ __noinline__ void reduce_slice(const GemmArgs& a, int s, int lane) {
   const int RB = a.red_slice_dim == 0 ? 2 * kBM : kBM;
   const int tiles_r = (a.red_rows + RB - 1) / RB;
   const int tiles_c = (a.red_cols + kBN - 1) / kBN;
@@ -304,7 +306,11 @@ __device__ void reduce_slice(const GemmArgs& a, int s, int worker, int n_workers
   const __nv_bfloat16* slots = reinterpret_cast<const __nv_bfloat16*>(a.red_slots);
   const __nv_bfloat16* bias = reinterpret_cast<const __nv_bfloat16*>(a.bias);
   const int64_t slot_stride = (int64_t)a.red_rows * a.red_ld;
-  for (int u = worker; u < n_units; u += n_workers) {
+  for (;;) {
+    int u = 0;
+    if (lane == 0) u = (int)atomicAdd(a.red_work + s, 1u);
+    u = __shfl_sync(0xffffffffu, u, 0);
+    if (u >= n_units) break;
     const int blk = u / sub, part = u - blk * sub;
     const int j = blk / tiles_o, o = blk - j * tiles_o;
     const int cg = j / a.cyc;
@@ -439,7 +445,7 @@ __device__ void aux_warp_main(const GemmArgs& a, int aux) {
         }
       }
       ok = __all_sync(0xffffffffu, ok);
-      if (ok) reduce_slice(a, s, worker, n_workers, lane);
+      if (ok) reduce_slice(a, s, lane);
     }
   }
 }
@@ -859,6 +865,18 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
       }
     }
     if (cur_slice >= 0) flush_counts(cur_slice);
+    // this CTA's tiles are done: help the communication warps with the slot sums that are left
+    if (a.red_n > 0) {
+      for (int s = 0; s < a.n_slices && ok; ++s) {
+        int okw = 1;
+        if (lane == 0 && !wait_flag_geq_sys(a.red_counter + s, a.red_target, 8 * tmo)) {
+          report(a, kTimeoutReduce, s, 0x1000u + warp);
+          okw = 0;
+        }
+        ok = __all_sync(0xffffffffu, okw) != 0;
+        if (ok) reduce_slice(a, s, lane);
+      }
+    }
   } else {
     // ===================== communication / reduce warps =====================
     aux_warp_main(a, warp - 6);

@@ -143,6 +143,7 @@ struct GemmArgs {
   int red_rows, red_cols;
   int64_t red_ld;
   const uint32_t* red_counter; // local per-slice counters
+  uint32_t* red_work;          // local per-slice work counters (zero at launch): next unit of the slot sums
   uint32_t red_target;         // counter value once every partial tile of a slice has arrived
                                // (each tile counts 4: one per epilogue warp of the sender)
   int red_slice_dim;           // 0: slice = block-cyclic row blocks (kBM), 1: column blocks (kBN)

@@ -244,6 +244,11 @@ class FusedGemm:
             d.update(red_n=0, skip_comm=1)
         elif phase == "reduce":
             d.update(no_tiles=1, n_chunks=0, push_n=0, a_flag_mode=0, b_flag_mode=0)
+            if d.get("red_n", 0):
+                # a reduce-only launch of the emulated-rank tests and benches: the arrival counters stay
+                # as the tile phases left them, the work counters start from zero in a buffer of their own
+                self._work = torch.zeros(rt.NCOUNTER, dtype=torch.int32, device="cuda")
+                d["red_work"] = self._work.data_ptr()
         if self.use_barriers:
             d.update(_barrier_fields(self.world, [], exit_barrier, self.grid, self.timeout_ns))
         self.C.gemm_run(d)
@@ -257,7 +262,8 @@ class FusedGemm:
         Kd = mc.C * kl
         if Kd != mc.R * kr:
             raise FusedPlanError("OS: contraction sizes of X and W shards disagree")
-        if kl % 8 or n % 8 or m * Kd * 2 > ws.stage_a_bytes or Kd * n * 2 > ws.stage_b_bytes:
+        # a staging buffer is needed only for an operand that is gathered (a group of one reads in place)
+        if kl % 8 or n % 8 or (mc.C > 1 and m * Kd * 2 > ws.stage_a_bytes) or (mc.R > 1 and Kd * n * 2 > ws.stage_b_bytes):
             raise FusedPlanError("OS: shard does not fit the staging buffers / alignment")
         tiles_m = (m + BM - 1) // BM
         S = pick_slices(tiles_m, n_slices)
@@ -355,7 +361,8 @@ class FusedGemm:
             raise ValueError(f"unknown K-panel order {order!r}")
         if order == "cannon" and mc.R != mc.C:
             raise FusedPlanError("Cannon's schedule needs a square mesh")
-        if kl % 64 or kr % 64 or n % 8 or m * Kd * 2 > ws.stage_a_bytes or Kd * n * 2 > ws.stage_b_bytes:
+        if (kl % 64 or kr % 64 or n % 8 or (mc.C > 1 and m * Kd * 2 > ws.stage_a_bytes)
+                or (mc.R > 1 and Kd * n * 2 > ws.stage_b_bytes)):
             raise FusedPlanError("K-panel OS: shard does not fit the staging buffers / 64-wide k-blocks")
         sub = max(1, sub)
         while sub > 1 and (kl % (sub * 64) or kr % (sub * 64)):
@@ -472,7 +479,7 @@ class FusedGemm:
                  push_base=[self.world.ptr(q, ws.slots) + mc.c * m * nc * 2 for q in peers],
                  push_counter=[self.world.flag_ptr(q, rt.COUNTER0) for q in peers],
                  red_n=mc.C, red_slots=ws.local(ws.slots), red_rows=m, red_cols=nc, red_ld=nc,
-                 red_counter=ws.local(ws.flags + 4 * rt.COUNTER0),
+                 red_counter=ws.local(ws.flags + 4 * rt.COUNTER0), red_work=ws.local(ws.flags + 4 * rt.WORK0),
                  red_target=mc.C * (blocks_own // S) * (m // CTA_M) * 4, red_slice_dim=1,
                  rot=0 if (rot_index is not None and rot_index < 0) else
                  _push_rotation((mc.c if rot_index is None else rot_index) % mc.C, mc.C, tiles_n // S))
@@ -536,7 +543,7 @@ class FusedGemm:
                  push_base=[self.world.ptr(q, ws.slots) + mc.r * mr * n * 2 for q in peers],
                  push_counter=[self.world.flag_ptr(q, rt.COUNTER0) for q in peers],
                  red_n=mc.R, red_slots=ws.local(ws.slots), red_rows=mr, red_cols=n, red_ld=n,
-                 red_counter=ws.local(ws.flags + 4 * rt.COUNTER0),
+                 red_counter=ws.local(ws.flags + 4 * rt.COUNTER0), red_work=ws.local(ws.flags + 4 * rt.WORK0),
                  red_target=mc.R * ((mr // BM) // S) * 2 * tiles_n * 4, red_slice_dim=0,
                  rot=0 if (rot_index is not None and rot_index < 0) else
                  _push_rotation((mc.r if rot_index is None else rot_index) % mc.R, mc.R, tiles_m // S))

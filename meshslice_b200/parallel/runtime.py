@@ -21,7 +21,8 @@ from .. import _native
 ENTRY0, EXIT0, GO, DONE = 0, 8, 16, 17
 RESET0 = 17            # first word cleared before every fused launch
 CHUNK0, NCHUNK = 32, 160
-COUNTER0, NCOUNTER = 192, 64
+COUNTER0, NCOUNTER = 192, 32     # per-slice arrival counters of the push side
+WORK0 = 224                       # per-slice work counters of the slot sums (same count)
 FLAG_WORDS = 256
 RESET_BYTES = (FLAG_WORDS - RESET0) * 4
 
