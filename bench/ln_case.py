@@ -16,8 +16,9 @@ g = torch.ones(cols, device="cuda").bfloat16()
 b = torch.zeros(cols, device="cuda").bfloat16()
 dg = torch.zeros(cols, device="cuda")
 db = torch.zeros(cols, device="cuda")
-h, y, mr = F.ln_full(x, res, g, b, 1e-5)
-F.ln_bwd_full(y, h, g, mr, dg, db, res)
+for _ in range(3):  # warm-up; also lets the caching allocator keep the output buffers of two calls
+    h, y, mr = F.ln_full(x, res, g, b, 1e-5)
+    F.ln_bwd_full(y, h, g, mr, dg, db, res)
 ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
 ev[0].record()
 for _ in range(iters):

@@ -55,20 +55,24 @@ class FabricConstants:
     fabric: str = "ring"
     shared_port: bool = False
     flops_per_chip: float = 242 * 1024 ** 4
+    # rates of the fused GEMM + collective kernel (cost_model.FusedKernelConstants as a dict); when present the
+    # per-layer emulation models that kernel instead of the collective-then-GEMM pipeline
+    fused: Optional[Dict[str, float]] = None
 
     @classmethod
     def from_dict(cls, d):
         b = {k: tuple(v) if isinstance(v, (list, tuple)) else (v, v) for k, v in d["bws"].items()}
         return cls(d["latencies"], b, d["base_overheads"], d.get("fabric", "ring"), d.get("shared_port", False),
-                   d.get("flops_per_chip", 242 * 1024 ** 4))
+                   d.get("flops_per_chip", 242 * 1024 ** 4), d.get("fused"))
 
     @classmethod
     def load(cls, path):
         return cls.from_dict(json.load(open(path)))
 
     def mesh(self, shape, matmul=None) -> DeviceMesh:
+        fused = CostModel.FusedKernelConstants(**self.fused) if self.fused else None
         return DeviceMesh(shape, self.flops_per_chip, self.bws, self.latencies, self.base_overheads,
-                          fabric=self.fabric, shared_port=self.shared_port, matmul=matmul)
+                          fabric=self.fabric, shared_port=self.shared_port, matmul=matmul, fused=fused)
 
 
 class FFLayerModel:
@@ -138,7 +142,10 @@ class FFLayerModel:
 
     def emulate(self, mesh: DeviceMesh, K):
         B, I, O = self.bsize, self.in_dim, self.out_dim
-        OS, LS, RS = CostModel.MeshFlow_OS, CostModel.MeshFlow_LS, CostModel.MeshFlow_RS
+        if getattr(mesh, "fused", None) is not None:
+            OS, LS, RS = CostModel.Fused_OS, CostModel.Fused_LS, CostModel.Fused_RS
+        else:
+            OS, LS, RS = CostModel.MeshFlow_OS, CostModel.MeshFlow_LS, CostModel.MeshFlow_RS
         if not self.transpose:
             if self.dataflow == "os":
                 t = (OS(mesh, B, O, I, K), LS(mesh, B, I, O, K), RS(mesh, I, O, B, K))

@@ -114,8 +114,9 @@ class DeviceMesh:
 
     def __init__(self, device_shape: tuple, flops_per_chip: float, bws_per_direction, link_latencies,
                  base_overheads, fabric: str = "ring", shared_port: bool = False,
-                 matmul: Optional[MatmulEstimator] = None):
+                 matmul: Optional[MatmulEstimator] = None, fused: Optional["FusedKernelConstants"] = None):
         self.reshape(device_shape)
+        self.fused = fused
         self.flops = flops_per_chip
         self.bws = bws_per_direction
         self.link_latencies = link_latencies
@@ -146,6 +147,8 @@ class DeviceMesh:
         """Builds a mesh from the constants fitted by BenchCollectives2D (``--fabric-json``)."""
         d = path_or_dict if isinstance(path_or_dict, dict) else json.load(open(path_or_dict))
         bws = {k: tuple(v) if isinstance(v, (list, tuple)) else (v, v) for k, v in d["bws"].items()}
+        if "fused" in d and "fused" not in kw:
+            kw["fused"] = FusedKernelConstants(**d["fused"])
         return cls(device_shape, d.get("flops_per_chip", 1.38e15), bws, d["latencies"], d["base_overheads"],
                    fabric=d.get("fabric", "switch"), shared_port=d.get("shared_port", True), **kw)
 
@@ -356,6 +359,87 @@ def MeshFlow_RS(mesh, M, N, K, steps=32, precisions=(16, 16, 16)):
     rs_o = estimateReduceScatter(mesh, oshape, 0, precisions[2])
     compute = estimateMatmul(mesh, M, oshape[1], ishape[0], layout="tn") / steps
     return (ag_i + rs_o, compute + max(mesh.combine(ag_i, rs_o), compute) * (steps - 1))
+
+
+# ----------------------------------------------------------------------------------------------
+# models of the fused tcgen05 GEMM + collective kernel (csrc/gemm/sm100_gemm.cu), i.e. of what runs on GPUs
+# ----------------------------------------------------------------------------------------------
+@dataclass
+class FusedKernelConstants:
+    """Rates of the fused kernel, fitted from `bench/BenchGemm2D.py` sweeps by `bench/fit_fused_model.py`.
+
+    The MeshFlow_* models above keep the reference's view (every slice is a collective followed by a
+    GEMM, CostModel.py:214-262).  The kernel that runs differs in four ways that matter for time: one launch
+    per product with a cross-GPU entry and exit barrier; shards are *pushed* by the SMs that also compute, so
+    a gather is faster before the first tile than under tiles; partial tiles are pushed to their owners from
+    the epilogue; the owners' slot sums run beside the tiles and only the last slice's sum is exposed."""
+    launch_overhead: float = 1.0e-4      # s per launch: barriers across GPUs, first-chunk latency, tail
+    gather_bw_alone: float = 560e9       # bytes/s a GPU pushes while none of its tiles run
+    gather_bw_overlap: float = 300e9     # ... while tiles run on the same SMs
+    push_bw: float = 450e9               # bytes/s of partial tiles pushed from the epilogue
+    slot_sum_bw: float = 2.2e12          # bytes/s of slot reads in the per-slice sums
+    tile_eff: float = 0.93               # main-loop rate relative to the matmul estimator
+    matmul_peak: float = 1.3806e15       # FLOP/s of the analytic estimator that tile_eff was fitted against
+
+    def to_dict(self):
+        return dict(self.__dict__)
+
+
+def _fused(mesh) -> FusedKernelConstants:
+    f = getattr(mesh, "fused", None)
+    return f if f is not None else FusedKernelConstants()
+
+
+def _tiles(mesh, M, N, K, layout):
+    f = _fused(mesh)
+    if getattr(mesh, "matmul", None) is not None:          # measured or tabulated GEMM times
+        return mesh.matmul(int(M), int(N), int(K), layout) / f.tile_eff
+    return AnalyticMatmul(peak_flops=f.matmul_peak, eff=1.0)(int(M), int(N), int(K), layout) / f.tile_eff
+
+
+def Fused_OS(mesh, M, N, K, steps=4, precisions=(16, 16, 16)):
+    """Y[M/R, N/C] = gather_cols(X[M/R, K/C]) . gather_rows(W[K/R, N/C]): X travels as `steps` row slices, W as
+    column chunks, interleaved in order of first use; the first tile needs one piece of each."""
+    R, C = mesh.shape
+    f = _fused(mesh)
+    bx = (C - 1) * _size((M // R, K // C), precisions[0])
+    bw = (R - 1) * _size((K // R, N // C), precisions[1])
+    tiles = _tiles(mesh, M // R, N // C, K, "nn")
+    if bx + bw == 0:
+        return (0.0, tiles)
+    first = (bx + bw) / steps / f.gather_bw_alone
+    rest = (bx + bw) * (1.0 - 1.0 / steps) / f.gather_bw_overlap
+    return (f.launch_overhead + first, max(tiles, rest))
+
+
+def _fused_scatter(mesh, gather_bytes, push_bytes, slot_bytes, tiles, steps):
+    f = _fused(mesh)
+    if gather_bytes + push_bytes == 0:
+        return (0.0, tiles)
+    first = gather_bytes / steps / f.gather_bw_alone
+    under = gather_bytes * (1.0 - 1.0 / steps) / f.gather_bw_overlap + push_bytes / f.push_bw
+    tail = slot_bytes / steps / f.slot_sum_bw      # the last slice's slot sum has no tiles left to hide under
+    return (f.launch_overhead + first, max(tiles, under) + tail)
+
+
+def Fused_LS(mesh, M, N, K, steps=4, precisions=(16, 16, 16)):
+    """Y[M/R, N/C] = scatter_cols(X[M/R, K/C] . gather_rows(W[N/R, K/C])^T): output columns are sliced."""
+    R, C = mesh.shape
+    bw = (R - 1) * _size((N // R, K // C), precisions[1])
+    part = _size((M // R, N), precisions[2])
+    push = part * (C - 1) / C
+    slots = part if C > 1 else 0.0
+    return _fused_scatter(mesh, bw, push, slots, _tiles(mesh, M // R, N, K // C, "nt"), steps)
+
+
+def Fused_RS(mesh, M, N, K, steps=4, precisions=(16, 16, 16)):
+    """Y[M/R, N/C] = scatter_rows(gather_cols(X[K/R, M/C])^T . W[K/R, N/C]): output rows are sliced."""
+    R, C = mesh.shape
+    bx = (C - 1) * _size((K // R, M // C), precisions[0])
+    part = _size((M, N // C), precisions[2])
+    push = part * (R - 1) / R
+    slots = part if R > 1 else 0.0
+    return _fused_scatter(mesh, bx, push, slots, _tiles(mesh, M, N // C, K // R, "tn"), steps)
 
 
 def _ring(mesh, shape, M_, N_, K_):

@@ -373,7 +373,8 @@ PYBIND11_MODULE(_C, m) {
   }, py::arg("mode"), py::arg("dy"), py::arg("h"), py::arg("gamma"), py::arg("mean_rstd"), py::arg("dres"),
      py::arg("dx"), py::arg("stats"), py::arg("dgamma"), py::arg("dbeta"), py::arg("rows"), py::arg("cols"),
      py::arg("total_cols"), py::arg("stream"), py::arg("exch") = py::none());
-  m.def("ln_grid", &ln_grid, "CTAs of the LayerNorm kernels for a row count (0: forward, 1: backward)");
+  m.def("ln_grid", &ln_grid, py::arg("backward"), py::arg("rows"), py::arg("cols") = 0,
+        "CTAs of the LayerNorm kernels for a row count and local width (0: forward, 1: backward)");
   m.def("ce_grid", &ce_grid, "CTAs of the cross-entropy kernels for a row count");
   m.def("gelu_fwd", [](uint64_t x, uint64_t y, int64_t n, uint64_t stream) {
     check(gelu_fwd(P<void>(x), P<void>(y), n, S(stream)), "gelu_fwd");

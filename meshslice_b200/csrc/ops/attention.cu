@@ -148,8 +148,12 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_consta
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nblk = a.seq / kBlk;
-  const int i_blk = a.causal ? (nblk - 1 - (int)blockIdx.x) : (int)blockIdx.x;  // heavy tiles first
-  const int h = blockIdx.y, b = blockIdx.z;
+  // Grid = (batch-heads of a group, tiles, groups): blocks are handed to the SMs in block-id order, so a group of
+  // up to 32 batch-heads (whose Q / K / V stay in L2 together) runs its longest causal tiles first and the last
+  // wave of the launch is the short tiles.
+  const int i_blk = a.causal ? (nblk - 1 - (int)blockIdx.y) : (int)blockIdx.y;
+  const int bh = blockIdx.z * gridDim.x + blockIdx.x;
+  const int h = bh % a.heads, b = bh / a.heads;
   const int n_kv = a.causal ? i_blk + 1 : nblk;
   const int row0 = b * a.seq + i_blk * kBlk;
   const int colq = h * 3 * kD;
@@ -491,8 +495,11 @@ attn_bwd2_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_consta
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nblk = a.seq / kBlk;
-  const int blk = kKeyMajor ? (int)blockIdx.x : (a.causal ? nblk - 1 - (int)blockIdx.x : (int)blockIdx.x);
-  const int h = blockIdx.y, b = blockIdx.z;
+  // same block order as the forward kernel: per group of batch-heads the longest tiles first (key block 0 / the
+  // last query block stream the most)
+  const int blk = kKeyMajor ? (int)blockIdx.y : (a.causal ? nblk - 1 - (int)blockIdx.y : (int)blockIdx.y);
+  const int bh = blockIdx.z * gridDim.x + blockIdx.x;
+  const int h = bh % a.heads, b = bh / a.heads;
   // streamed blocks: queries i0 .. nblk-1 for a key block, keys 0 .. blk for a query block
   const int i0 = kKeyMajor && a.causal ? blk : 0;
   const int n_it = kKeyMajor ? nblk - i0 : (a.causal ? blk + 1 : nblk);
@@ -820,11 +827,21 @@ cudaError_t configure_device() {
   return cudaSuccess;
 }
 
+// Batch-heads per block-order group: the largest divisor of batch * heads that is at most 32.
+int bh_group(int batch, int heads) {
+  const int n = batch * heads;
+  int g = 1;
+  for (int d = 1; d <= 32; ++d)
+    if (n % d == 0) g = d;
+  return g;
+}
+
 }  // namespace
 
 cudaError_t attention_fwd(const void* qkv, void* out, float* lse, int batch, int seq, int heads,
                           int causal, float scale, uint32_t* status, cudaStream_t stream) {
-  if (seq % kBlk != 0 || batch <= 0 || heads <= 0) return cudaErrorInvalidValue;
+  if (seq % kBlk != 0 || batch <= 0 || heads <= 0 || (int64_t)batch * heads > 65535 || seq / kBlk > 65535)
+    return cudaErrorInvalidValue;
   {
     cudaError_t e = configure_device();
     if (e != cudaSuccess) return e;
@@ -840,7 +857,8 @@ cudaError_t attention_fwd(const void* qkv, void* out, float* lse, int batch, int
   a.scale = scale;
   a.status = status;
   a.timeout_ns = 2000000000ull;
-  dim3 grid(seq / kBlk, heads, batch);
+  const int grp = bh_group(batch, heads);
+  dim3 grid(grp, seq / kBlk, batch * heads / grp);
   attn_fwd2_kernel<<<grid, 192, kFwd2Smem, stream>>>(tm, a);
   return cudaGetLastError();
 }
@@ -848,7 +866,8 @@ cudaError_t attention_fwd(const void* qkv, void* out, float* lse, int batch, int
 cudaError_t attention_bwd(const void* qkv, const void* out, const void* dout, const float* lse,
                           void* dqkv, float* dq_acc, float* delta, int batch, int seq, int heads,
                           int causal, float scale, uint32_t* status, cudaStream_t stream) {
-  if (seq % kBlk != 0 || batch <= 0 || heads <= 0) return cudaErrorInvalidValue;
+  if (seq % kBlk != 0 || batch <= 0 || heads <= 0 || (int64_t)batch * heads > 65535 || seq / kBlk > 65535)
+    return cudaErrorInvalidValue;
   {
     cudaError_t e0 = configure_device();
     if (e0 != cudaSuccess) return e0;
@@ -878,7 +897,8 @@ cudaError_t attention_bwd(const void* qkv, const void* out, const void* dout, co
   g.scale = scale;
   g.status = status;
   g.timeout_ns = 2000000000ull;
-  dim3 grid2(seq / kBlk, heads, batch);
+  const int grp = bh_group(batch, heads);
+  dim3 grid2(grp, seq / kBlk, batch * heads / grp);
   attn_bwd2_kernel<true><<<grid2, kBwd2Threads, kBwd2Smem, stream>>>(tq, td, g);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return e;

@@ -11,6 +11,7 @@ namespace msb {
 namespace {
 
 constexpr int kLnThreads = 256;
+constexpr int kLnBwdThreads = 512;
 
 // ---- cross-GPU row exchange (see RowExchange in ops.h) ----
 __device__ __forceinline__ void ex_red_release_sys(uint32_t* p, uint32_t v) {
@@ -230,8 +231,12 @@ ln_fwd_kernel(int mode, const uint4* __restrict__ x, const uint4* __restrict__ r
 // ------------------------------------------------------------------------------------------
 // LayerNorm backward
 // ------------------------------------------------------------------------------------------
+// One CTA per row (grid-stride) with up to kLnBwdThreads threads, so that a 4096-wide row is one 16-byte vector per
+// thread: the per-thread dgamma / dbeta accumulators (16 registers per vector) are what limits occupancy, and all
+// three input vectors of a row (dy, h, dres) are requested before anything waits for them.  The rows stay packed
+// in registers between the two passes; gamma is loaded once per CTA.
 template <int MAXV>
-__global__ void __launch_bounds__(kLnThreads)
+__global__ void __launch_bounds__(kLnBwdThreads, MAXV == 1 ? 2 : 1)
 ln_bwd_kernel(int mode, const uint4* __restrict__ dy, const uint4* __restrict__ h,
               const uint4* __restrict__ gamma, const float* __restrict__ mean_rstd,
               const uint4* __restrict__ dres, uint4* __restrict__ dx, float* __restrict__ stats,
@@ -240,35 +245,49 @@ ln_bwd_kernel(int mode, const uint4* __restrict__ dy, const uint4* __restrict__ 
   __shared__ float red[64];
   const int nvec = cols >> 3;
   float accg[MAXV][8], accb[MAXV][8];
+  uint4 pg[MAXV];
 #pragma unroll
-  for (int k = 0; k < MAXV; ++k)
+  for (int k = 0; k < MAXV; ++k) {
 #pragma unroll
     for (int i = 0; i < 8; ++i) { accg[k][i] = 0.f; accb[k][i] = 0.f; }
+    const int v = threadIdx.x + k * blockDim.x;
+    pg[k] = (gamma != nullptr && v < nvec) ? gamma[v] : make_uint4(0x3f803f80u, 0x3f803f80u, 0x3f803f80u, 0x3f803f80u);
+  }
   // exchange of the partial sums with the GPUs of the mesh row: see ln_fwd_kernel
   const bool exchange = ex.n > 0;
   if (exchange && mode == 2 && !ex_wait(ex, 1u)) return;
   const bool want_param_grads = mode != 2 && dgamma != nullptr;
+  const bool want_dres = mode != 1 && dres != nullptr;
 
   for (int row = blockIdx.x; row < rows; row += gridDim.x) {
-    const float mean = mean_rstd[2 * row], rstd = mean_rstd[2 * row + 1];
     const int64_t base = (int64_t)row * nvec;
-    float g[MAXV][8], xh[MAXV][8];
+    uint4 pd[MAXV], ph[MAXV], pr[MAXV];
+#pragma unroll
+    for (int k = 0; k < MAXV; ++k) {
+      const int v = threadIdx.x + k * blockDim.x;
+      if (v < nvec) {
+        pd[k] = __ldcs(dy + base + v);
+        ph[k] = __ldcs(h + base + v);
+        if (want_dres) pr[k] = __ldcs(dres + base + v);
+      }
+    }
+    const float mean = mean_rstd[2 * row], rstd = mean_rstd[2 * row + 1];
     float s1 = 0.f, s2 = 0.f;
 #pragma unroll
     for (int k = 0; k < MAXV; ++k) {
       const int v = threadIdx.x + k * blockDim.x;
       if (v < nvec) {
         float d[8], hv[8], gm[8];
-        unpack8(dy[base + v], d);
-        unpack8(h[base + v], hv);
-        if (gamma != nullptr) unpack8(gamma[v], gm);
+        unpack8(pd[k], d);
+        unpack8(ph[k], hv);
+        unpack8(pg[k], gm);
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-          xh[k][i] = (hv[i] - mean) * rstd;
-          g[k][i] = gamma != nullptr ? d[i] * gm[i] : d[i];
-          s1 += g[k][i];
-          s2 += g[k][i] * xh[k][i];
-          if (want_param_grads) { accg[k][i] += d[i] * xh[k][i]; accb[k][i] += d[i]; }
+          const float xh = (hv[i] - mean) * rstd;
+          const float g = d[i] * gm[i];
+          s1 += g;
+          s2 += g * xh;
+          if (want_param_grads) { accg[k][i] += d[i] * xh; accb[k][i] += d[i]; }
         }
       }
     }
@@ -301,16 +320,19 @@ ln_bwd_kernel(int mode, const uint4* __restrict__ dy, const uint4* __restrict__ 
     for (int k = 0; k < MAXV; ++k) {
       const int v = threadIdx.x + k * blockDim.x;
       if (v < nvec) {
-        float o[8];
+        float d[8], hv[8], gm[8], o[8];
+        unpack8(pd[k], d);
+        unpack8(ph[k], hv);
+        unpack8(pg[k], gm);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) o[i] = rstd * (g[k][i] - m1 - xh[k][i] * m2);
-        if (dres != nullptr) {
+        for (int i = 0; i < 8; ++i) o[i] = rstd * (d[i] * gm[i] - m1 - (hv[i] - mean) * rstd * m2);
+        if (want_dres) {
           float r[8];
-          unpack8(dres[base + v], r);
+          unpack8(pr[k], r);
 #pragma unroll
           for (int i = 0; i < 8; ++i) o[i] += r[i];
         }
-        dx[base + v] = pack8(o);
+        __stcs(dx + base + v, pack8(o));
       }
     }
   }
@@ -605,6 +627,14 @@ inline int ln_threads(int cols) {
   return t;
 }
 
+inline int ln_bwd_threads(int cols) {
+  const int nvec = cols / 8;
+  int t = (nvec + 31) / 32 * 32;
+  if (t < 64) t = 64;
+  if (t > kLnBwdThreads) t = kLnBwdThreads;
+  return t;
+}
+
 inline int grid_for(int64_t n, int threads, int cap = 148 * 16) {
   int64_t g = (n + threads - 1) / threads;
   if (g > cap) g = cap;
@@ -619,8 +649,14 @@ inline int grid_for(int64_t n, int threads, int cap = 148 * 16) {
 // ------------------------------------------------------------------------------------------
 int ce_grid(int rows) { return rows < 148 * 8 ? rows : 148 * 8; }
 
-int ln_grid(int backward, int rows) {
-  const int cap = backward ? 148 * 8 : 148 * 16;
+int ln_grid(int backward, int rows, int cols) {
+  int cap = 148 * 16;
+  if (backward) {
+    // one resident wave (1024 threads per SM at 64 registers): every CTA ends with one atomic per column for
+    // dgamma / dbeta, so CTAs beyond what is resident only add atomics
+    const int t = ln_bwd_threads(cols > 0 ? cols : 8 * kLnBwdThreads);
+    cap = 148 * (1024 / t);
+  }
   return rows < cap ? rows : cap;
 }
 
@@ -629,7 +665,7 @@ cudaError_t ln_fwd(int mode, const void* x, const void* res, void* h_out, void* 
                    int cols, int total_cols, float eps, cudaStream_t stream, const RowExchange* exch) {
   if (cols % 8 != 0 || cols > 8 * kLnThreads * 8) return cudaErrorInvalidValue;
   if (exch != nullptr && mode != 1 && mode != 2) return cudaErrorInvalidValue;
-  const int grid = ln_grid(0, rows);
+  const int grid = ln_grid(0, rows, cols);
   RowExchange ex;
   if (exch != nullptr) ex = *exch; else memset(&ex, 0, sizeof(ex));
   auto X = reinterpret_cast<const uint4*>(x);
@@ -655,9 +691,9 @@ cudaError_t ln_bwd(int mode, const void* dy, const void* h, const void* gamma,
                    const float* mean_rstd, const void* dres, void* dx, float* stats, float* dgamma,
                    float* dbeta, int rows, int cols, int total_cols, cudaStream_t stream,
                    const RowExchange* exch) {
-  if (cols % 8 != 0 || cols > 8 * kLnThreads * 8) return cudaErrorInvalidValue;
+  if (cols % 8 != 0 || cols > 8 * kLnBwdThreads * 4) return cudaErrorInvalidValue;
   if (exch != nullptr && mode != 1 && mode != 2) return cudaErrorInvalidValue;
-  const int grid = ln_grid(1, rows);
+  const int grid = ln_grid(1, rows, cols);
   RowExchange ex;
   if (exch != nullptr) ex = *exch; else memset(&ex, 0, sizeof(ex));
   auto DY = reinterpret_cast<const uint4*>(dy);
@@ -665,16 +701,14 @@ cudaError_t ln_bwd(int mode, const void* dy, const void* h, const void* gamma,
   auto G = reinterpret_cast<const uint4*>(gamma);
   auto DR = reinterpret_cast<const uint4*>(dres);
   auto DX = reinterpret_cast<uint4*>(dx);
-  const int threads = ln_threads(cols);
+  const int threads = ln_bwd_threads(cols);
   const int nvec_per_thread = (cols / 8 + threads - 1) / threads;
   if (nvec_per_thread <= 1)
     ln_bwd_kernel<1><<<grid, threads, 0, stream>>>(mode, DY, H, G, mean_rstd, DR, DX, stats, dgamma, dbeta, rows, cols, total_cols, ex);
   else if (nvec_per_thread <= 2)
     ln_bwd_kernel<2><<<grid, threads, 0, stream>>>(mode, DY, H, G, mean_rstd, DR, DX, stats, dgamma, dbeta, rows, cols, total_cols, ex);
-  else if (nvec_per_thread <= 4)
-    ln_bwd_kernel<4><<<grid, threads, 0, stream>>>(mode, DY, H, G, mean_rstd, DR, DX, stats, dgamma, dbeta, rows, cols, total_cols, ex);
   else
-    ln_bwd_kernel<8><<<grid, threads, 0, stream>>>(mode, DY, H, G, mean_rstd, DR, DX, stats, dgamma, dbeta, rows, cols, total_cols, ex);
+    ln_bwd_kernel<4><<<grid, threads, 0, stream>>>(mode, DY, H, G, mean_rstd, DR, DX, stats, dgamma, dbeta, rows, cols, total_cols, ex);
   return cudaGetLastError();
 }
 

@@ -30,9 +30,9 @@ struct RowExchange {
   uint64_t timeout_ns;
   uint32_t* status;                 // [4]: 20 (LayerNorm fwd) / 21 (bwd) / 22 (cross-entropy), CTA, seen, wanted
 };
-// CTAs the LayerNorm kernels launch for `rows` rows: with an exchange every CTA of the producing
-// pass counts one arrival, so the host needs this number for the consumers' targets.
-int ln_grid(int backward, int rows);
+// CTAs the LayerNorm kernels launch for `rows` rows of `cols` local columns (0: widest case): with an exchange
+// every CTA of the producing pass counts one arrival, so the host needs this number for the consumers' targets.
+int ln_grid(int backward, int rows, int cols = 0);
 
 // ---- LayerNorm over a feature dimension that may be split across the mesh columns --------
 // Replaces ShardedLayerNorm (ShardedLayers.py:123-138) plus the residual adds (:178,:184);

@@ -151,7 +151,7 @@ class ShardedLayerNorm:
         elif self._exchanger(x) is not None:
             # statistics travel inside the two kernels (peer stores + arrival counters): no collective
             (k, xl), = x.shards.items()
-            prod, cons = self._exchange(xl.shape[0], backward=False)
+            prod, cons = self._exchange(xl.shape[0], xl.shape[1], backward=False)
             hl, _ = F.ln_stats(xl, R(k), exch=prod)
             h = ShardedTensor(m, {k: hl})
             outs = {k: F.ln_apply(hl, None, G(k), Bt(k), self.in_dim, self.eps, exch=cons)}
@@ -176,9 +176,9 @@ class ShardedLayerNorm:
             return None
         return ex
 
-    def _exchange(self, rows: int, backward: bool):
+    def _exchange(self, rows: int, cols: int, backward: bool):
         from .. import _native
-        grid = _native.load().ln_grid(1 if backward else 0, rows)
+        grid = _native.load().ln_grid(1 if backward else 0, rows, cols)
         return self.mesh.engine.row_exchange.next(rows, grid)
 
     def backward(self, dy: ShardedTensor, dres: Optional[ShardedTensor] = None) -> ShardedTensor:
@@ -195,7 +195,7 @@ class ShardedLayerNorm:
                                                       DB(k), DR(k)) for k in m.coords()})
         if self._exchanger(dy) is not None:
             (k, dyl), = dy.shards.items()
-            prod, cons = self._exchange(dyl.shape[0], backward=True)
+            prod, cons = self._exchange(dyl.shape[0], dyl.shape[1], backward=True)
             F.ln_bwd_stats(dyl, h.shards[k], G(k), mr.shards[k], DG(k), DB(k), exch=prod)
             return ShardedTensor(m, {k: F.ln_bwd_apply(dyl, h.shards[k], G(k), mr.shards[k], None, self.in_dim,
                                                        DR(k), exch=cons)})

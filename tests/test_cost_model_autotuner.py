@@ -121,3 +121,67 @@ def test_fabric_json_roundtrip_and_cli(tmp_path):
              "--tuned-json", str(out), "--sweep"])
     tuned = json.load(open(out))
     assert tuned["mesh"] in ([1, 8], [2, 4], [4, 2], [8, 1])
+
+
+# ---- model of the fused GEMM + collective kernel ----------------------------------------------
+def _b200_mesh(shape, **consts):
+    fab = AT.FabricConstants.from_dict(AT.B200_NVSWITCH)
+    mesh = fab.mesh(shape)
+    mesh.fused = CM.FusedKernelConstants(**consts)
+    return mesh
+
+
+def test_fused_model_on_one_gpu_is_the_tile_time_only():
+    mesh = _b200_mesh((1, 1))
+    for fn, layout in ((CM.Fused_OS, "nn"), (CM.Fused_LS, "nt"), (CM.Fused_RS, "tn")):
+        pro, steady = fn(mesh, 8192, 8192, 4096, 4)
+        assert pro == 0.0
+        assert steady == pytest.approx(CM.AnalyticMatmul(1.3806e15, 1.0)(8192, 8192, 4096, layout) / 0.93)
+
+
+def test_fused_model_slices_shrink_the_prologue_and_never_beat_the_tiles():
+    mesh = _b200_mesh((2, 4))
+    for fn in (CM.Fused_OS, CM.Fused_LS, CM.Fused_RS):
+        p1, s1 = fn(mesh, 16384, 49152, 12288, 1)
+        p4, s4 = fn(mesh, 16384, 49152, 12288, 4)
+        assert p4 < p1
+        assert p4 >= mesh.fused.launch_overhead
+    # a product whose traffic dominates: the steady part is the transfer under tiles, not the tiles
+    pro, steady = CM.Fused_OS(mesh, 16384, 4096, 4096, 4)
+    tiles = CM.AnalyticMatmul(1.3806e15, 1.0)(16384 // 2, 4096 // 4, 4096, "nn") / 0.93
+    assert steady >= tiles
+    # exposed slot sums: with one slice the whole sum comes after the tiles, with eight an eighth of it
+    (_, a), (_, b) = CM.Fused_LS(mesh, 16384, 16384, 4096, 1), CM.Fused_LS(mesh, 16384, 16384, 4096, 8)
+    assert a > b
+
+
+def test_fused_constants_are_recovered_from_a_synthetic_sweep(tmp_path):
+    import importlib.util
+    import os
+    spec = importlib.util.spec_from_file_location(
+        "fit_fused_model", os.path.join(os.path.dirname(__file__), "..", "bench", "fit_fused_model.py"))
+    fit = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(fit)
+    true = dict(launch_overhead=8e-5, gather_bw_alone=6e11, gather_bw_overlap=2.5e11, push_bw=4e11,
+                slot_sum_bw=1.5e12, tile_eff=0.9)
+    rows = []
+    for shape in ((2, 4), (4, 2), (1, 8), (8, 1)):
+        mesh = _b200_mesh(shape, **true)
+        for (M, K, N) in ((16384, 4096, 16384), (16384, 16384, 4096), (16384, 12288, 49152), (16384, 49152, 12288)):
+            for df, fn in (("os", CM.Fused_OS), ("ls", CM.Fused_LS), ("rs", CM.Fused_RS)):
+                rows.append(dict(M=M, K=K, N=N, mesh=list(shape), dataflow=df,
+                                 fused={str(s): {"ms": sum(fn(mesh, M, N, K, s)) * 1e3} for s in (1, 2, 4, 8)}))
+    src = tmp_path / "sweep.log"
+    src.write_text("noise line\n" + "\n".join(json.dumps(r) for r in rows) + "\n")
+    out = tmp_path / "fabric.json"
+    got = fit.main([str(src), "--out", str(out)])
+    for k, v in true.items():
+        assert getattr(got, k) == pytest.approx(v, rel=0.05), k
+    # the autotuner picks the fused model up from the fabric file
+    fab = AT.FabricConstants.load(str(out))
+    assert fab.fused is not None and fab.mesh((2, 4)).fused.push_bw == pytest.approx(4e11, rel=0.05)
+    layer = AT.FFLayerModel(65536, 4096, 16384, "os")
+    t_fused = layer.emulate(fab.mesh((2, 4)), 4)
+    fab.fused = None
+    t_pipe = layer.emulate(fab.mesh((2, 4)), 4)
+    assert t_fused > 0 and t_pipe > 0 and t_fused != t_pipe

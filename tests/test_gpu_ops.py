@@ -68,6 +68,57 @@ def test_layernorm_two_pass_equals_single_pass():
     assert (torch.cat(outs, 1).float() - y_full.float()).abs().max() < 0.02
 
 
+@pytest.mark.parametrize("affine", [True, False])
+def test_layernorm_backward_two_pass_equals_single_pass(affine):
+    """Backward of the column-sharded path (partial dot products per shard, summed, then applied) against the
+    single-pass kernel on the whole row and against autograd in fp32."""
+    C, st = _C()
+    rows, cols, parts = 96, 4096, 4
+    hbuf = torch.randn(rows, cols, device="cuda").bfloat16()
+    dy = torch.randn(rows, cols, device="cuda").bfloat16()
+    dres = torch.randn(rows, cols, device="cuda").bfloat16()
+    gamma = (1.0 + 0.1 * torch.randn(cols, device="cuda")).bfloat16() if affine else None
+    gp = gamma.data_ptr() if affine else 0
+    mean = hbuf.float().mean(1)
+    rstd = (hbuf.float().var(1, unbiased=False) + 1e-5).rsqrt()
+    mr = torch.stack([mean, rstd], 1).contiguous()
+    dx_full = torch.empty_like(hbuf)
+    dg_full = torch.zeros(cols, device="cuda")
+    db_full = torch.zeros(cols, device="cuda")
+    C.ln_bwd(0, dy.data_ptr(), hbuf.data_ptr(), gp, mr.data_ptr(), dres.data_ptr(), dx_full.data_ptr(), 0,
+             dg_full.data_ptr() if affine else 0, db_full.data_ptr() if affine else 0, rows, cols, cols, st)
+    w = cols // parts
+    # the shards stay referenced until the kernels have run (only raw pointers are passed)
+    cut = lambda t: [t[:, i * w:(i + 1) * w].contiguous() for i in range(parts)]
+    dys, hs, drs = cut(dy), cut(hbuf), cut(dres)
+    gs = [gamma[i * w:(i + 1) * w].contiguous() for i in range(parts)] if affine else [None] * parts
+    stats, dgs, dbs = [], [], []
+    for i in range(parts):
+        t = torch.empty(rows, 2, device="cuda")
+        dg = torch.zeros(w, device="cuda")
+        db = torch.zeros(w, device="cuda")
+        C.ln_bwd(1, dys[i].data_ptr(), hs[i].data_ptr(), gs[i].data_ptr() if affine else 0, mr.data_ptr(), 0, 0,
+                 t.data_ptr(), dg.data_ptr() if affine else 0, db.data_ptr() if affine else 0, rows, w, cols, st)
+        stats.append(t); dgs.append(dg); dbs.append(db)
+    total = sum(stats)
+    outs = []
+    for i in range(parts):
+        dx = torch.empty(rows, w, device="cuda", dtype=torch.bfloat16)
+        C.ln_bwd(2, dys[i].data_ptr(), hs[i].data_ptr(), gs[i].data_ptr() if affine else 0, mr.data_ptr(),
+                 drs[i].data_ptr(), dx.data_ptr(), total.data_ptr(), 0, 0, rows, w, cols, st)
+        outs.append(dx)
+    torch.cuda.synchronize()
+    assert (torch.cat(outs, 1).float() - dx_full.float()).abs().max() < 0.04
+    hh = hbuf.float().requires_grad_(True)
+    g32 = gamma.float().requires_grad_(True) if affine else None
+    torch.nn.functional.layer_norm(hh, (cols,), g32, None, 1e-5).backward(dy.float())
+    assert (dx_full.float() - (hh.grad + dres.float())).abs().max() < 0.06
+    if affine:
+        assert (torch.cat(dgs) - dg_full).abs().max() < 1e-2
+        assert (dg_full - g32.grad).abs().max() < 0.05 * rows ** 0.5
+        assert (torch.cat(dbs) - dy.float().sum(0)).abs().max() < 1e-2
+
+
 def test_gelu_fwd_bwd():
     C, st = _C()
     x = torch.randn(1 << 16, device="cuda").bfloat16()
