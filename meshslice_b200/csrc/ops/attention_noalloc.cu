@@ -8,7 +8,7 @@
 namespace {
 
 constexpr int kHeadDim = 128;
-constexpr size_t kAccFloats = (size_t)MSB_NOALLOC_MAX_ROWS * kHeadDim;  // dQ accumulator
+constexpr size_t kAccFloats = (size_t)MSB_NOALLOC_MAX_ROWS * kHeadDim;  // first scratch array of attention_bwd
 constexpr size_t kDeltaFloats = MSB_NOALLOC_MAX_ROWS;                   // rowsum(dO * O)
 constexpr size_t kStatusFloats = 64;                                    // 4 status words + padding
 
@@ -55,7 +55,7 @@ extern "C" cudaError_t msb_attention_bwd_noalloc(const void* qkv, const void* ou
     e = cudaMemcpyAsync(kernel_status, status, sizeof(uint32_t), cudaMemcpyDeviceToHost, stream);
     if (e != cudaSuccess) return e;
   }
-  // attention_bwd clears the dQ accumulator itself and overwrites delta
+  // attention_bwd overwrites both scratch arrays (log2-domain lse and the scaled row sums) before it reads them
   return msb::attention_bwd(qkv, out, dout, lse, dqkv, acc, delta, batch, seq, heads, causal, scale,
                             status, stream);
 }
