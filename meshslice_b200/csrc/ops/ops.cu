@@ -12,6 +12,7 @@ namespace {
 
 constexpr int kLnThreads = 256;
 constexpr int kLnBwdThreads = 512;
+constexpr int kLnGroupedMaxCols = 2048;   // rows up to this width run several per CTA in ln_bwd_kernel
 
 // ---- cross-GPU row exchange (see RowExchange in ops.h) ----
 __device__ __forceinline__ void ex_red_release_sys(uint32_t* p, uint32_t v) {
@@ -231,26 +232,49 @@ ln_fwd_kernel(int mode, const uint4* __restrict__ x, const uint4* __restrict__ r
 // ------------------------------------------------------------------------------------------
 // LayerNorm backward
 // ------------------------------------------------------------------------------------------
-// One CTA per row (grid-stride) with up to kLnBwdThreads threads, so that a 4096-wide row is one 16-byte vector per
+// Sum of two values over the `gw` consecutive warps that share a row; every thread of the group gets the result.
+__device__ __forceinline__ void group_sum2(float& a, float& b, float* red, int gw) {
+  a = warp_sum(a);
+  b = warp_sum(b);
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+  __syncthreads();
+  if (l == 0) { red[w] = a; red[32 + w] = b; }
+  __syncthreads();
+  const int w0 = w / gw * gw;
+  a = 0.f;
+  b = 0.f;
+  for (int i = 0; i < gw; ++i) { a += red[w0 + i]; b += red[32 + w0 + i]; }
+}
+
+// A CTA of up to kLnBwdThreads threads walks the rows grid-stride.  A 4096-wide row is one 16-byte vector per
 // thread: the per-thread dgamma / dbeta accumulators (16 registers per vector) are what limits occupancy, and all
 // three input vectors of a row (dy, h, dres) are requested before anything waits for them.  The rows stay packed
 // in registers between the two passes; gamma is loaded once per CTA.
-template <int MAXV>
+// GROUPED (rows of at most 256 vectors, e.g. column shards): the CTA works on blockDim.x / tpr rows at a time,
+// `tpr` threads (whole warps) per row, and adds the row groups' dgamma / dbeta in shared memory before its one
+// atomic per column, so that narrow rows neither idle most of a CTA nor multiply the atomics.
+template <int MAXV, bool GROUPED>
 __global__ void __launch_bounds__(kLnBwdThreads, MAXV == 1 ? 2 : 1)
 ln_bwd_kernel(int mode, const uint4* __restrict__ dy, const uint4* __restrict__ h,
               const uint4* __restrict__ gamma, const float* __restrict__ mean_rstd,
               const uint4* __restrict__ dres, uint4* __restrict__ dx, float* __restrict__ stats,
               float* __restrict__ dgamma, float* __restrict__ dbeta, int rows, int cols,
-              int total_cols, const __grid_constant__ RowExchange ex) {
+              int total_cols, int tpr_arg, const __grid_constant__ RowExchange ex) {
+  static_assert(!GROUPED || MAXV == 1, "grouped rows are one vector per thread");
   __shared__ float red[64];
+  __shared__ float comb[GROUPED ? 2 * kLnGroupedMaxCols : 1];
   const int nvec = cols >> 3;
+  const int tpr = GROUPED ? tpr_arg : (int)blockDim.x;            // threads per row
+  const int sub = GROUPED ? (int)threadIdx.x / tpr : 0;           // which of the CTA's rows
+  const int tx = GROUPED ? (int)threadIdx.x - sub * tpr : (int)threadIdx.x;
+  const int rows_per_cta = GROUPED ? (int)blockDim.x / tpr : 1;
   float accg[MAXV][8], accb[MAXV][8];
   uint4 pg[MAXV];
 #pragma unroll
   for (int k = 0; k < MAXV; ++k) {
 #pragma unroll
     for (int i = 0; i < 8; ++i) { accg[k][i] = 0.f; accb[k][i] = 0.f; }
-    const int v = threadIdx.x + k * blockDim.x;
+    const int v = tx + k * tpr;
     pg[k] = (gamma != nullptr && v < nvec) ? gamma[v] : make_uint4(0x3f803f80u, 0x3f803f80u, 0x3f803f80u, 0x3f803f80u);
   }
   // exchange of the partial sums with the GPUs of the mesh row: see ln_fwd_kernel
@@ -259,24 +283,28 @@ ln_bwd_kernel(int mode, const uint4* __restrict__ dy, const uint4* __restrict__ 
   const bool want_param_grads = mode != 2 && dgamma != nullptr;
   const bool want_dres = mode != 1 && dres != nullptr;
 
-  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+  for (int r0 = blockIdx.x * rows_per_cta; r0 < rows; r0 += gridDim.x * rows_per_cta) {
+    const int row = r0 + sub;
+    const bool live = row < rows;          // the last rows of a grouped CTA may be missing; barriers stay uniform
     const int64_t base = (int64_t)row * nvec;
     uint4 pd[MAXV], ph[MAXV], pr[MAXV];
 #pragma unroll
     for (int k = 0; k < MAXV; ++k) {
-      const int v = threadIdx.x + k * blockDim.x;
-      if (v < nvec) {
+      const int v = tx + k * tpr;
+      pd[k] = make_uint4(0u, 0u, 0u, 0u);
+      ph[k] = make_uint4(0u, 0u, 0u, 0u);
+      if (live && v < nvec) {
         pd[k] = __ldcs(dy + base + v);
         ph[k] = __ldcs(h + base + v);
         if (want_dres) pr[k] = __ldcs(dres + base + v);
       }
     }
-    const float mean = mean_rstd[2 * row], rstd = mean_rstd[2 * row + 1];
+    const float mean = live ? mean_rstd[2 * row] : 0.f, rstd = live ? mean_rstd[2 * row + 1] : 0.f;
     float s1 = 0.f, s2 = 0.f;
 #pragma unroll
     for (int k = 0; k < MAXV; ++k) {
-      const int v = threadIdx.x + k * blockDim.x;
-      if (v < nvec) {
+      const int v = tx + k * tpr;
+      if (live && v < nvec) {
         float d[8], hv[8], gm[8];
         unpack8(pd[k], d);
         unpack8(ph[k], hv);
@@ -292,18 +320,21 @@ ln_bwd_kernel(int mode, const uint4* __restrict__ dy, const uint4* __restrict__ 
       }
     }
     if (mode == 2) {
-      if (exchange) {
-        s1 = 0.f;
-        s2 = 0.f;
-        for (int q = 0; q < ex.n; ++q) { s1 += ex_get(ex, q, row, 2, 0); s2 += ex_get(ex, q, row, 2, 1); }
-      } else {
-        s1 = stats[2 * row];
-        s2 = stats[2 * row + 1];
+      if (live) {
+        if (exchange) {
+          s1 = 0.f;
+          s2 = 0.f;
+          for (int q = 0; q < ex.n; ++q) { s1 += ex_get(ex, q, row, 2, 0); s2 += ex_get(ex, q, row, 2, 1); }
+        } else {
+          s1 = stats[2 * row];
+          s2 = stats[2 * row + 1];
+        }
       }
     } else {
-      block_sum2(s1, s2, red);
+      if (GROUPED) group_sum2(s1, s2, red, tpr >> 5);
+      else block_sum2(s1, s2, red);
       if (mode == 1) {
-        if (threadIdx.x == 0) {
+        if (tx == 0 && live) {
           if (exchange) {
             const float v2[2] = {s1, s2};
             ex_put<2>(ex, row, v2);
@@ -318,8 +349,8 @@ ln_bwd_kernel(int mode, const uint4* __restrict__ dy, const uint4* __restrict__ 
     const float m1 = s1 / (float)total_cols, m2 = s2 / (float)total_cols;
 #pragma unroll
     for (int k = 0; k < MAXV; ++k) {
-      const int v = threadIdx.x + k * blockDim.x;
-      if (v < nvec) {
+      const int v = tx + k * tpr;
+      if (live && v < nvec) {
         float d[8], hv[8], gm[8], o[8];
         unpack8(pd[k], d);
         unpack8(ph[k], hv);
@@ -338,14 +369,31 @@ ln_bwd_kernel(int mode, const uint4* __restrict__ dy, const uint4* __restrict__ 
   }
   if (exchange && mode == 1) ex_signal(ex);
   if (want_param_grads) {
-#pragma unroll
-    for (int k = 0; k < MAXV; ++k) {
-      const int v = threadIdx.x + k * blockDim.x;
-      if (v < nvec) {
+    if (GROUPED) {
+      for (int i = threadIdx.x; i < 2 * cols; i += blockDim.x) comb[i] = 0.f;
+      __syncthreads();
+      if (tx < nvec) {
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-          atomicAdd(dgamma + v * 8 + i, accg[k][i]);
-          if (dbeta != nullptr) atomicAdd(dbeta + v * 8 + i, accb[k][i]);
+          atomicAdd(comb + tx * 8 + i, accg[0][i]);
+          atomicAdd(comb + cols + tx * 8 + i, accb[0][i]);
+        }
+      }
+      __syncthreads();
+      for (int i = threadIdx.x; i < cols; i += blockDim.x) {
+        atomicAdd(dgamma + i, comb[i]);
+        if (dbeta != nullptr) atomicAdd(dbeta + i, comb[cols + i]);
+      }
+    } else {
+#pragma unroll
+      for (int k = 0; k < MAXV; ++k) {
+        const int v = tx + k * tpr;
+        if (v < nvec) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            atomicAdd(dgamma + v * 8 + i, accg[k][i]);
+            if (dbeta != nullptr) atomicAdd(dbeta + v * 8 + i, accb[k][i]);
+          }
         }
       }
     }
@@ -627,12 +675,18 @@ inline int ln_threads(int cols) {
   return t;
 }
 
-inline int ln_bwd_threads(int cols) {
+// Launch shape of ln_bwd_kernel for a local width: threads per CTA, threads per row, rows per CTA, vectors per thread.
+struct LnBwdShape { int threads, tpr, rows_per_cta, maxv; };
+inline LnBwdShape ln_bwd_shape(int cols) {
   const int nvec = cols / 8;
-  int t = (nvec + 31) / 32 * 32;
-  if (t < 64) t = 64;
-  if (t > kLnBwdThreads) t = kLnBwdThreads;
-  return t;
+  int tpr = (nvec + 31) / 32 * 32;
+  if (tpr < 32) tpr = 32;
+  if (cols <= kLnGroupedMaxCols) {
+    const int g = kLnBwdThreads / tpr;
+    return {g * tpr, tpr, g, 1};
+  }
+  if (tpr > kLnBwdThreads) tpr = kLnBwdThreads;
+  return {tpr, tpr, 1, (nvec + tpr - 1) / tpr};
 }
 
 inline int grid_for(int64_t n, int threads, int cap = 148 * 16) {
@@ -654,8 +708,10 @@ int ln_grid(int backward, int rows, int cols) {
   if (backward) {
     // one resident wave (1024 threads per SM at 64 registers): every CTA ends with one atomic per column for
     // dgamma / dbeta, so CTAs beyond what is resident only add atomics
-    const int t = ln_bwd_threads(cols > 0 ? cols : 8 * kLnBwdThreads);
-    cap = 148 * (1024 / t);
+    const LnBwdShape sh = ln_bwd_shape(cols > 0 ? cols : 8 * kLnBwdThreads);
+    cap = 148 * (1024 / sh.threads);
+    const int groups = (rows + sh.rows_per_cta - 1) / sh.rows_per_cta;
+    return groups < cap ? groups : cap;
   }
   return rows < cap ? rows : cap;
 }
@@ -701,14 +757,15 @@ cudaError_t ln_bwd(int mode, const void* dy, const void* h, const void* gamma,
   auto G = reinterpret_cast<const uint4*>(gamma);
   auto DR = reinterpret_cast<const uint4*>(dres);
   auto DX = reinterpret_cast<uint4*>(dx);
-  const int threads = ln_bwd_threads(cols);
-  const int nvec_per_thread = (cols / 8 + threads - 1) / threads;
-  if (nvec_per_thread <= 1)
-    ln_bwd_kernel<1><<<grid, threads, 0, stream>>>(mode, DY, H, G, mean_rstd, DR, DX, stats, dgamma, dbeta, rows, cols, total_cols, ex);
-  else if (nvec_per_thread <= 2)
-    ln_bwd_kernel<2><<<grid, threads, 0, stream>>>(mode, DY, H, G, mean_rstd, DR, DX, stats, dgamma, dbeta, rows, cols, total_cols, ex);
+  const LnBwdShape sh = ln_bwd_shape(cols);
+  if (sh.rows_per_cta > 1 || cols <= kLnGroupedMaxCols)
+    ln_bwd_kernel<1, true><<<grid, sh.threads, 0, stream>>>(mode, DY, H, G, mean_rstd, DR, DX, stats, dgamma, dbeta, rows, cols, total_cols, sh.tpr, ex);
+  else if (sh.maxv <= 1)
+    ln_bwd_kernel<1, false><<<grid, sh.threads, 0, stream>>>(mode, DY, H, G, mean_rstd, DR, DX, stats, dgamma, dbeta, rows, cols, total_cols, sh.tpr, ex);
+  else if (sh.maxv <= 2)
+    ln_bwd_kernel<2, false><<<grid, sh.threads, 0, stream>>>(mode, DY, H, G, mean_rstd, DR, DX, stats, dgamma, dbeta, rows, cols, total_cols, sh.tpr, ex);
   else
-    ln_bwd_kernel<4><<<grid, threads, 0, stream>>>(mode, DY, H, G, mean_rstd, DR, DX, stats, dgamma, dbeta, rows, cols, total_cols, ex);
+    ln_bwd_kernel<4, false><<<grid, sh.threads, 0, stream>>>(mode, DY, H, G, mean_rstd, DR, DX, stats, dgamma, dbeta, rows, cols, total_cols, sh.tpr, ex);
   return cudaGetLastError();
 }
 

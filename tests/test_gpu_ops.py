@@ -10,10 +10,11 @@ def _C():
     return _native.load(), _native.stream_ptr()
 
 
-@pytest.mark.parametrize("cols", [1024, 4096, 12288])
-def test_layernorm_fwd_bwd_single_pass(cols):
+@pytest.mark.parametrize("cols,rows", [(1024, 301), (768, 43), (64, 1000), (2048, 300), (4096, 300), (12288, 300)])
+def test_layernorm_fwd_bwd_single_pass(cols, rows):
+    """Widths up to 2048 run several rows per CTA in the backward kernel (row counts that leave the last CTA
+    partly empty included); wider rows one row per CTA with one, two or four vectors per thread."""
     C, st = _C()
-    rows = 300
     x = torch.randn(rows, cols, device="cuda").bfloat16()
     res = torch.randn(rows, cols, device="cuda").bfloat16()
     gamma = (1 + 0.1 * torch.randn(cols, device="cuda")).bfloat16()
@@ -73,7 +74,7 @@ def test_layernorm_backward_two_pass_equals_single_pass(affine):
     """Backward of the column-sharded path (partial dot products per shard, summed, then applied) against the
     single-pass kernel on the whole row and against autograd in fp32."""
     C, st = _C()
-    rows, cols, parts = 96, 4096, 4
+    rows, cols, parts = 97, 4096, 4
     hbuf = torch.randn(rows, cols, device="cuda").bfloat16()
     dy = torch.randn(rows, cols, device="cuda").bfloat16()
     dres = torch.randn(rows, cols, device="cuda").bfloat16()
