@@ -1,10 +1,10 @@
 // Persistent, warp-specialised tcgen05 GEMM for sm_100a with fused mesh collectives.
 // See sm100_gemm.h for the interface and the role of each argument.
 //
-// CTA pairs (clusters of two, 224 threads per CTA, one CTA per SM, static round-robin schedule of
+// CTA pairs (clusters of two, 256 threads per CTA, one CTA per SM, static round-robin schedule of
 // 256x256 cluster tiles; each CTA holds 128 rows of A and 128 columns of B of the pair's tile):
 //   warp 0      TMA producer (both CTAs): waits for the chunk / panel flags a tile depends on, then
-//               fills a six-stage ring of (A 128x64, B 128x64) bf16 tiles in 128-byte-swizzled smem;
+//               fills a ring of kStages (A 128x64, B 128x64) bf16 tiles in 128-byte-swizzled smem;
 //               the loads complete on the leader CTA's mbarrier
 //   warp 1      MMA issuer (leader CTA): one elected thread issues tcgen05.mma.cta_group::2
 //               (M=256, N=256, K=16) into one of two 256-column fp32 accumulators in TMEM
@@ -12,7 +12,7 @@
 //               either bias / GeLU and a store to local memory, or the push of the bf16 partial tile
 //               into the owner GPU's slot (staged in smem, written with coalesced 16-byte stores or
 //               2-D TMA tensor stores) with one arrival count per slice and owner
-//   warps 6..9  communication and reduction (kAuxWarps of them; warp 6 of CTA 0 also runs the
+//   warps 6..7  communication and reduction (kAuxWarps of them; warp 6 of CTA 0 also runs the
 //               cross-GPU entry / exit barrier).  Gather side: the warps of all CTAs share the pieces
 //               of the LOCAL shard; a piece is read once with coalesced 16-byte loads (several per
 //               lane in flight) and written with 16-byte stores to every GPU of the group (posted

@@ -2,13 +2,14 @@
 //
 // One kernel computes  C[M,N] = op(A) * op(B)  (bf16 inputs, fp32 accumulation in TMEM) and,
 // when asked to, also moves the data of the surrounding 2-D tensor-parallel collectives:
-//   * gather side (all-gather -> GEMM): a communication warp in every CTA reads chunks of this
-//     GPU's shard and writes them into the staging buffers of all GPUs of the group with posted
-//     bulk stores over NVLink, then bumps one flag per chunk on each of them; the TMA producer
+//   * gather side (all-gather -> GEMM): the communication warps of every CTA read pieces of this
+//     GPU's shard and write them into the staging buffers of all GPUs of the group with 16-byte
+//     peer stores over NVLink, then bump one flag per chunk on each of them; the TMA producer
 //     warp waits for the flag of the chunk a tile needs.
 //   * "push" side (GEMM -> reduce-scatter): the epilogue stores each partial tile straight
-//     into the slot buffer of the GPU that owns it (peer stores over NVLink), bumps a
-//     per-slice counter there, and a trailing phase on the owner sums the slots.
+//     into the slot buffer of the GPU that owns it (peer stores over NVLink) and bumps a
+//     per-slice counter there; the owner's communication warps (and epilogue warps that have
+//     run out of tiles) sum the slots of a slice as soon as its counter is complete.
 // This covers the three MeshSlice dataflows of the reference (TensorParallel.py:153-214):
 // OS = gather A and B, LS = gather B and push over columns, RS = gather A and push over rows.
 #pragma once

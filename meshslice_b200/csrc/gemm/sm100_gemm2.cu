@@ -2,7 +2,7 @@
 // neighbouring SMs computes one 256 x 256 tile with tcgen05.mma.cta_group::2.
 //
 // Each CTA loads 128 rows of A and 128 of the 256 B columns per k-block (32 KiB instead of 48 KiB
-// per stage, so six stages fit) and owns the 128 accumulator rows that land in its own TMEM.  Only
+// per stage, so seven stages fit) and owns the 128 accumulator rows that land in its own TMEM.  Only
 // the leader CTA (even rank) issues MMAs; it reads both CTAs' shared memory.  Synchronisation:
 //   full[stage]    lives in the leader; both CTAs' TMA loads complete on it (the .cta_group::2
 //                  load form with the leader barrier's cluster address); two arrivals: the leader's
