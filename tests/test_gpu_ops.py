@@ -213,3 +213,69 @@ def test_sumsq():
     C.sumsq(x.data_ptr(), 0, x.numel(), out.data_ptr(), st)
     torch.cuda.synchronize()
     assert abs(out.item() - (x.float() ** 2).sum().item()) / out.item() < 1e-4
+
+
+def _emulated_exchange(n, rows, grid):
+    """Descriptors of one row exchange among n emulated ranks that all live on this GPU: rank q's slot area and
+    arrival counter are plain tensors.  The caller runs every rank's producer before any consumer, so no kernel
+    waits for one that has not run; the consumers' waits are then satisfied on entry."""
+    from meshslice_b200 import _native
+    width = 4
+    stride = rows * width
+    slots = [torch.zeros(n * stride, device="cuda") for _ in range(n)]
+    counters = [torch.zeros(16, dtype=torch.int32, device="cuda") for _ in range(n)]
+    descs = []
+    for q in range(n):
+        descs.append(dict(n=n, me=q, dst=[slots[p].data_ptr() + q * stride * 4 for p in range(n)],
+                          slots=slots[q].data_ptr(), stride=stride,
+                          counter=[counters[p].data_ptr() for p in range(n)], my_counter=counters[q].data_ptr(),
+                          target=(n - 1) * grid, timeout_ns=50_000_000, status=_native.status().dev))
+    return descs, (slots, counters)
+
+
+@pytest.mark.parametrize("n,w,rows", [(4, 1024, 203), (2, 4096, 64), (2, 256, 1000)])
+def test_layernorm_row_exchange_emulated_ranks(n, w, rows):
+    """LayerNorm forward and backward over a feature dimension split among n ranks, the partial row sums travelling
+    through the in-kernel exchange (slots + arrival counters), against the single-device kernels on the whole rows.
+    Narrow shards take the several-rows-per-CTA form of the backward kernel."""
+    from meshslice_b200 import _native
+    from meshslice_b200.ops import functional as F
+    C, st = _C()
+    cols = n * w
+    cut = lambda t: [t[:, q * w:(q + 1) * w].contiguous() for q in range(n)]
+    x = torch.randn(rows, cols, device="cuda").bfloat16()
+    res = torch.randn(rows, cols, device="cuda").bfloat16()
+    gamma = (1 + 0.1 * torch.randn(cols, device="cuda")).bfloat16()
+    beta = (0.1 * torch.randn(cols, device="cuda")).bfloat16()
+    h_ref, y_ref, mr_ref = F.ln_full(x, res, gamma, beta, 1e-5)
+    xs, rs = cut(x), cut(res)
+    gs = [gamma[q * w:(q + 1) * w].contiguous() for q in range(n)]
+    bs = [beta[q * w:(q + 1) * w].contiguous() for q in range(n)]
+    descs, keep = _emulated_exchange(n, rows, C.ln_grid(0, rows, w))
+    hs = [F.ln_stats(xs[q], rs[q], exch=descs[q])[0] for q in range(n)]
+    outs = [F.ln_apply(hs[q], None, gs[q], bs[q], cols, 1e-5, exch=descs[q]) for q in range(n)]
+    _native.check_status()
+    assert torch.equal(torch.cat(hs, 1), h_ref)
+    assert (torch.cat([o[0] for o in outs], 1).float() - y_ref.float()).abs().max() < 0.02
+    for q in range(n):
+        assert (outs[q][1] - mr_ref).abs().max() < 1e-3
+    # backward
+    dy = torch.randn(rows, cols, device="cuda").bfloat16()
+    dres = torch.randn(rows, cols, device="cuda").bfloat16()
+    dg_ref = torch.zeros(cols, device="cuda")
+    db_ref = torch.zeros(cols, device="cuda")
+    dx_ref = F.ln_bwd_full(dy, h_ref, gamma, mr_ref, dg_ref, db_ref, dres)
+    dys, drs = cut(dy), cut(dres)
+    dgs = [torch.zeros(w, device="cuda") for _ in range(n)]
+    dbs = [torch.zeros(w, device="cuda") for _ in range(n)]
+    descs, keep2 = _emulated_exchange(n, rows, C.ln_grid(1, rows, w))
+    for q in range(n):
+        F.ln_bwd_stats(dys[q], hs[q], gs[q], mr_ref, dgs[q], dbs[q], exch=descs[q])
+    dxs = [F.ln_bwd_apply(dys[q], hs[q], gs[q], mr_ref, None, cols, drs[q], exch=descs[q]) for q in range(n)]
+    _native.check_status()
+    assert (torch.cat(dxs, 1).float() - dx_ref.float()).abs().max() < 0.04
+    assert (torch.cat(dgs) - dg_ref).abs().max() < 1e-2 * rows ** 0.5
+    assert (torch.cat(dbs) - db_ref).abs().max() < 1e-2 * rows ** 0.5
+    # every rank's counter has seen exactly the other ranks' CTAs
+    for q in range(n):
+        assert int(keep2[1][q][0]) == (n - 1) * C.ln_grid(1, rows, w)
