@@ -219,6 +219,10 @@ void gemm_run(const py::dict& d) {
   a.status = b.status;
   a.timeout_ns = b.timeout_ns;
   if (a.status == nullptr) throw std::runtime_error("gemm: status pointer required");
+  a.trace = P<void>(getp(d, "trace"));
+  a.trace_cap = (int)geti(d, "trace_cap", 0);
+  if (a.trace != nullptr && (a.trace_cap <= 0 || (getp(d, "trace") & 15)))
+    throw std::runtime_error("gemm: the timeline buffer needs trace_cap > 0 and 16-byte alignment");
 
   CUtensorMap ta, tb;
   int r;

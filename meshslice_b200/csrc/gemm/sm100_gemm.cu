@@ -132,6 +132,21 @@ __device__ __forceinline__ void report(const GemmArgs& a, uint32_t code, uint32_
   }
 }
 
+// Timeline of one launch (kernel instantiated with kTrace only): events are 16-byte records
+// {globaltimer low, high, kind, argument} in a per-CTA area of a.trace whose first record is the event count.
+// The untraced instantiation contains none of this.
+template <bool kTrace>
+__device__ __forceinline__ void trace_event(const GemmArgs& a, uint32_t kind, uint32_t arg) {
+  if constexpr (kTrace) {
+    uint4* area = reinterpret_cast<uint4*>(a.trace) + (size_t)blockIdx.x * (size_t)(a.trace_cap + 1);
+    const uint32_t i = atomicAdd(reinterpret_cast<uint32_t*>(area), 1u);
+    if (i < (uint32_t)a.trace_cap) {
+      const uint64_t t = globaltimer_ns();
+      area[1 + i] = make_uint4((uint32_t)t, (uint32_t)(t >> 32), kind, arg);
+    }
+  }
+}
+
 __device__ __forceinline__ float gelu_tanh(float x) {
   const float k0 = 0.7978845608028654f, k1 = 0.044715f;
   float u = k0 * (x + k1 * x * x * x);
@@ -338,6 +353,7 @@ __device__ __noinline__ void reduce_slice(const GemmArgs& a, int s, int lane) {
   }
 }
 
+template <bool kTrace>
 __device__ void aux_warp_main(const GemmArgs& a, int aux) {
   const int lane = threadIdx.x & 31;
   const uint64_t tmo = a.timeout_ns;
@@ -409,6 +425,7 @@ __device__ void aux_warp_main(const GemmArgs& a, int aux) {
       __syncwarp();
       if (lane < (int)cd.n_sig) red_add_release_sys(cd.sig[lane], 1u);
       __syncwarp();
+      if (lane == 0) trace_event<kTrace>(a, kTraceChunkSent, (uint32_t)c);
     }
   }
 
@@ -445,7 +462,11 @@ __device__ void aux_warp_main(const GemmArgs& a, int aux) {
         }
       }
       ok = __all_sync(0xffffffffu, ok);
-      if (ok) reduce_slice(a, s, lane);
+      if (ok) {
+        if (lane == 0) trace_event<kTrace>(a, kTraceSumBegin, (uint32_t)s);
+        reduce_slice(a, s, lane);
+        if (lane == 0) trace_event<kTrace>(a, kTraceSumEnd, (uint32_t)s);
+      }
     }
   }
 }
@@ -511,6 +532,7 @@ __device__ __forceinline__ void store_row32(const GemmArgs& a, void* base, int64
 // ------------------------------------------------------------------------------------------
 // kernel
 // ------------------------------------------------------------------------------------------
+template <bool kTrace>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
 sm100_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                   const __grid_constant__ PushMaps pmaps, const __grid_constant__ GemmArgs a) {
@@ -591,6 +613,7 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
             break;
           }
           if (seen != before || a.n_chunks > 64) fence_proxy_async();
+          trace_event<kTrace>(a, kTraceOperandsReady, (uint32_t)t);
         }
         const int row_a = (2 * tc.m_blk + (int)rank) * kBM;        // this CTA's 128 rows of A
         const int col_b = tc.n_blk * kBN + (int)rank * (kBN / 2);  // this CTA's 128 columns of B
@@ -737,6 +760,7 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
       }
       mbar_wait(tfull_bar + acc, acc_phase, tmo);  // already complete: orders this lane's reads
       tc_fence_after_sync();
+      if (warp == 2 && lane == 0) trace_event<kTrace>(a, kTraceTileComputed, (uint32_t)t);
       if (a.push_n > 0 && tc.slice != cur_slice) {
         if (cur_slice >= 0) flush_counts(cur_slice);
         cur_slice = tc.slice;
@@ -831,6 +855,7 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
           }
         }
         if (lane == 0) cnt[owner] += 1;
+        if (warp == 2 && lane == 0) trace_event<kTrace>(a, kTraceTilePushed, (uint32_t)t);
       } else {
 #pragma unroll 1
         for (int c = 0; c < kBN / 32; ++c) {
@@ -879,7 +904,7 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
     }
   } else {
     // ===================== communication / reduce warps =====================
-    aux_warp_main(a, warp - 6);
+    aux_warp_main<kTrace>(a, warp - 6);
   }
 
   // ---- all roles of both CTAs of the pair are done with TMEM, barriers and the pipeline
@@ -905,12 +930,20 @@ cudaError_t launch_sm100_gemm(const CUtensorMap& tma_a, const CUtensorMap& tma_b
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return e;
   if (dev < 64 && !configured[dev]) {
-    e = cudaFuncSetAttribute(sm100_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    e = cudaFuncSetAttribute(sm100_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)kSmemAlloc);
+    if (e != cudaSuccess) return e;
+    e = cudaFuncSetAttribute(sm100_gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              (int)kSmemAlloc);
     if (e != cudaSuccess) return e;
     configured[dev] = true;
   }
-  sm100_gemm_kernel<<<grid, kGemmThreads, kSmemAlloc, stream>>>(tma_a, tma_b, push_maps, args);
+  if (args.trace != nullptr) {
+    if (args.trace_cap <= 0 || (reinterpret_cast<uintptr_t>(args.trace) & 15)) return cudaErrorInvalidValue;
+    sm100_gemm_kernel<true><<<grid, kGemmThreads, kSmemAlloc, stream>>>(tma_a, tma_b, push_maps, args);
+  } else {
+    sm100_gemm_kernel<false><<<grid, kGemmThreads, kSmemAlloc, stream>>>(tma_a, tma_b, push_maps, args);
+  }
   return cudaGetLastError();
 }
 

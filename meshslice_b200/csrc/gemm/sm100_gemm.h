@@ -164,6 +164,22 @@ struct GemmArgs {
   // ---- status ----
   uint32_t* status;            // [4]: code, blockIdx, detail, detail2
   uint64_t timeout_ns;
+  // ---- timeline (optional) ----
+  // When non-null the launch runs the traced instantiation of the fused kernel: every CTA appends 16-byte
+  // events {globaltimer ns low, high, TraceKind, argument} to its area of (trace_cap + 1) records, the first
+  // of which holds the event count (zero before the launch).  16-byte aligned, gridDim.x areas.
+  void* trace;
+  int trace_cap;
+};
+
+// Events of the timeline: which tile, chunk or slice the argument names is given per kind.
+enum TraceKind : uint32_t {
+  kTraceOperandsReady = 1,   // producer: the gathered chunks that tile `arg` reads have arrived
+  kTraceTileComputed = 2,    // epilogue: the accumulator of tile `arg` is complete
+  kTraceTilePushed = 3,      // epilogue: the partial tile `arg` has been handed to its owner (push side)
+  kTraceChunkSent = 4,       // communication warp: its share of chunk `arg` is stored and signalled everywhere
+  kTraceSumBegin = 5,        // communication warp: slot sums of slice `arg` begin (all partial tiles arrived)
+  kTraceSumEnd = 6,          // ... and no unit of the slice is left for this warp
 };
 
 // Launch on `stream` (grid even: CTA pairs).  Tensor maps must describe A and B with 128-byte

@@ -116,6 +116,11 @@ def _barrier_fields(world: rt.World, ranks: List[int], exit_barrier: bool, grid:
         exit_barrier=1 if exit_barrier else 0, timeout_ns=timeout_ns)
 
 
+# event kinds of the fused kernel's timeline (TraceKind in csrc/gemm/sm100_gemm.h)
+TRACE_KINDS = {1: "operands_ready", 2: "tile_computed", 3: "tile_pushed", 4: "chunk_sent", 5: "sum_begin",
+               6: "sum_end"}
+
+
 class FusedGemm:
     """Builds and launches fused dataflows for one rank.
 
@@ -142,6 +147,8 @@ class FusedGemm:
         self.push_bufs = int(os.environ.get("MSB_PUSH_BUFS", "1"))
         # how partial tiles reach their owner: 0 = 2-D TMA tensor stores, 1 = ordinary 16-byte stores
         self.push_mode = int(os.environ.get("MSB_PUSH_MODE", "1"))
+        self._trace = None          # timeline buffer of the next launches (enable_trace)
+        self._trace_cap = 0
 
     # ------------------------------------------------------------------ helpers
     def _reset_flags(self, stream):
@@ -227,6 +234,39 @@ class FusedGemm:
     def _chunk_flag(self, rank: int, idx: int) -> int:
         return self.world.flag_ptr(rank, rt.CHUNK0 + idx)
 
+    # ------------------------------------------------------------------ timeline
+    def enable_trace(self, events_per_cta: int = 512) -> None:
+        """The following launches run the traced instantiation of the kernel: every CTA records when the
+        gathered chunks of a tile had arrived, when the tile's accumulator was complete, when the partial tile
+        had been pushed, when a communication warp had sent its share of a chunk and when the slot sums of a
+        slice began and ended (``%globaltimer`` stamps; the per-slice overlap timeline).  ``read_trace``
+        returns and clears them; ``disable_trace`` goes back to the untraced kernel."""
+        self._trace_cap = int(events_per_cta)
+        self._trace = torch.zeros(self.grid * (self._trace_cap + 1) * 4, dtype=torch.int32, device="cuda")
+
+    def disable_trace(self) -> None:
+        self._trace, self._trace_cap = None, 0
+
+    def read_trace(self) -> List[dict]:
+        """Events since the last call, sorted by time: dicts with ``t_ns`` (relative to the first event),
+        ``cta``, ``kind`` (name) and ``arg`` (tile, chunk or slice index)."""
+        if self._trace is None:
+            return []
+        torch.cuda.synchronize()
+        raw = self._trace.view(self.grid, self._trace_cap + 1, 4).cpu().numpy().astype("int64") & 0xffffffff
+        self._trace.zero_()
+        out = []
+        for cta in range(self.grid):
+            n = min(int(raw[cta, 0, 0]), self._trace_cap)
+            for lo, hi, kind, arg in raw[cta, 1:1 + n]:
+                out.append(dict(t_ns=int(lo) | (int(hi) << 32), cta=cta,
+                                kind=TRACE_KINDS.get(int(kind), str(int(kind))), arg=int(arg)))
+        out.sort(key=lambda e: e["t_ns"])
+        t0 = out[0]["t_ns"] if out else 0
+        for e in out:
+            e["t_ns"] -= t0
+        return out
+
     def _launch(self, d, exit_barrier, phase="all", reset=True):
         """phases 'comm' (gather only), 'gemm' (tiles only) and 'reduce' (slot sums only) split one
         launch in three; together with reset=False this lets a test run several emulated ranks
@@ -251,6 +291,8 @@ class FusedGemm:
                 d["red_work"] = self._work.data_ptr()
         if self.use_barriers:
             d.update(_barrier_fields(self.world, [], exit_barrier, self.grid, self.timeout_ns))
+        if self._trace is not None:
+            d.update(trace=self._trace.data_ptr(), trace_cap=self._trace_cap)
         self.C.gemm_run(d)
 
     # ------------------------------------------------------------------ OS

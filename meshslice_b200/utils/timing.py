@@ -60,3 +60,55 @@ def trace(path: Optional[str]):
     with profile(activities=acts) as prof:
         yield prof
     prof.export_chrome_trace(path)
+
+
+# ----------------------------------------------------------------------------------------------
+# timeline of the fused GEMM + collective kernel (events of FusedGemm.read_trace)
+# ----------------------------------------------------------------------------------------------
+def fused_timeline_summary(events) -> dict:
+    """Where the phases of one fused launch lie in time (ns from the first event).
+
+    ``overlap_chunks`` is the share of the gather (first to last ``chunk_sent``) that ran after the first tile
+    was complete, ``overlap_sums`` the share of the slot-sum time (``sum_begin`` .. ``sum_end`` per warp) spent
+    before the last tile of the launch was complete: both are 0 for a launch that does its phases one after
+    another and approach 1 when the transfers hide under the tensor-core work."""
+    by = {}
+    for e in events:
+        by.setdefault(e["kind"], []).append(e)
+    span = lambda k: (min(e["t_ns"] for e in by[k]), max(e["t_ns"] for e in by[k])) if k in by else None
+    out = {k: dict(first_ns=span(k)[0], last_ns=span(k)[1], count=len(by[k])) for k in by}
+    tiles = span("tile_computed")
+    chunks = span("chunk_sent")
+    if tiles and chunks and chunks[1] > chunks[0]:
+        out["overlap_chunks"] = max(0, chunks[1] - max(chunks[0], tiles[0])) / (chunks[1] - chunks[0])
+    if tiles and "sum_begin" in by and "sum_end" in by:
+        begins = {}
+        total = hidden = 0
+        for e in sorted(by["sum_begin"] + by["sum_end"], key=lambda e: e["t_ns"]):
+            key = (e["cta"], e["arg"])
+            if e["kind"] == "sum_begin":
+                begins.setdefault(key, []).append(e["t_ns"])
+            elif begins.get(key):
+                b = begins[key].pop(0)
+                total += e["t_ns"] - b
+                hidden += max(0, min(e["t_ns"], tiles[1]) - b)
+        if total > 0:
+            out["overlap_sums"] = hidden / total
+    return out
+
+
+def fused_timeline_to_chrome(events, path: str) -> None:
+    """Writes the events as a Chrome trace (one process per CTA; slot sums as spans, the rest as instants)."""
+    import json
+    recs, open_sums = [], {}
+    for e in sorted(events, key=lambda e: e["t_ns"]):
+        ts = e["t_ns"] / 1e3
+        if e["kind"] == "sum_begin":
+            open_sums.setdefault((e["cta"], e["arg"]), []).append(ts)
+        elif e["kind"] == "sum_end" and open_sums.get((e["cta"], e["arg"])):
+            b = open_sums[(e["cta"], e["arg"])].pop(0)
+            recs.append(dict(name=f"slot sums, slice {e['arg']}", ph="X", ts=b, dur=ts - b, pid=e["cta"], tid=1))
+        else:
+            recs.append(dict(name=f"{e['kind']} {e['arg']}", ph="i", s="t", ts=ts, pid=e["cta"], tid=0))
+    with open(path, "w") as f:
+        json.dump({"traceEvents": recs, "displayTimeUnit": "ns"}, f)

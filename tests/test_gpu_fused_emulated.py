@@ -109,6 +109,52 @@ def test_ls_gathers_weights_pushes_over_row(mesh, slices):
         _close(out, ref[r * m:(r + 1) * m, c * nc:(c + 1) * nc], Kd)
 
 
+def test_timeline_of_a_traced_ls_launch_and_identical_results():
+    """The traced instantiation of the kernel records chunk, tile, push and slot-sum events for every emulated
+    rank and computes bit-for-bit what the untraced one computes."""
+    from meshslice_b200 import _native
+    from meshslice_b200.utils.timing import fused_timeline_summary
+    R, C, slices = 2, 2, 2
+    M, Kd, N = 512 * R, 128 * C, 1024 * R * C
+    X = torch.randn(M, Kd, device="cuda").bfloat16()
+    W = torch.randn(N, Kd, device="cuda").bfloat16()
+    m, kl, nr, nc = M // R, Kd // C, N // R, N // C
+    xs = {(r, c): X[r * m:(r + 1) * m, c * kl:(c + 1) * kl].contiguous() for r in range(R) for c in range(C)}
+    wsd = {(r, c): W[r * nr:(r + 1) * nr, c * kl:(c + 1) * kl].contiguous() for r in range(R) for c in range(C)}
+    results = []
+    for traced in (False, True):
+        ops, _ = _setup(R, C, 16, N * kl * 2, C * m * nc * 2)
+        outs = {k: torch.empty(m, nc, device="cuda", dtype=torch.bfloat16) for k in ops}
+        for op in ops.values():
+            op._reset_flags(_native.stream_ptr())
+            if traced:
+                op.enable_trace(256)
+        for phase in ("comm", "gemm", "reduce"):
+            for (r, c), op in ops.items():
+                op.ls(xs[(r, c)], [wsd[(rr, c)].data_ptr() for rr in range(R)], m, kl, nr, outs[(r, c)],
+                      n_slices=slices, phase=phase, reset=False)
+                _native.check_status()
+        results.append(outs)
+        if traced:
+            tiles_per_rank = ((m + 255) // 256) * ((N + 255) // 256)
+            for op in ops.values():
+                ev = op.read_trace()
+                kinds = {}
+                for e in ev:
+                    kinds[e["kind"]] = kinds.get(e["kind"], 0) + 1
+                # one event per cluster tile from each CTA of the pair that computed it
+                assert kinds.get("tile_computed", 0) == 2 * tiles_per_rank, kinds
+                assert kinds.get("tile_pushed", 0) == 2 * tiles_per_rank, kinds
+                assert kinds.get("operands_ready", 0) == 2 * tiles_per_rank, kinds
+                assert kinds.get("chunk_sent", 0) > 0 and kinds.get("sum_begin", 0) == kinds.get("sum_end", 0) > 0
+                assert all(a["t_ns"] <= b["t_ns"] for a, b in zip(ev, ev[1:]))
+                s = fused_timeline_summary(ev)
+                assert s["tile_computed"]["last_ns"] >= s["chunk_sent"]["first_ns"]
+                assert op.read_trace() == []          # cleared
+    for k in results[0]:
+        assert torch.equal(results[0][k], results[1][k])
+
+
 @pytest.mark.parametrize("mesh,slices,cyc", [((2, 2), 2, 1), ((2, 2), 1, 2), ((4, 2), 2, 2)])
 def test_rs_gathers_inputs_pushes_over_column(mesh, slices, cyc):
     from meshslice_b200 import _native

@@ -90,3 +90,25 @@ def test_logical_mesh_of_the_transformer_bench_maps_to_a_physical_one():
         bt.physical_mesh(3, 3, 8)
     with pytest.raises(SystemExit):
         bt.physical_mesh(4, 4, 8, "8x1")
+
+
+def test_fused_timeline_summary_and_chrome_export(tmp_path):
+    """A synthetic launch: the gather runs from 0 to 100 us, tiles complete from 40 to 200 us, the slot sums of
+    slice 0 run under the tiles and those of slice 1 after the last tile."""
+    import json
+    from meshslice_b200.utils.timing import fused_timeline_summary, fused_timeline_to_chrome
+    ev = []
+    for c in range(5):
+        ev.append(dict(t_ns=c * 25_000, cta=c % 2, kind="chunk_sent", arg=c))
+    for t in range(9):
+        ev.append(dict(t_ns=40_000 + t * 20_000, cta=t % 2, kind="tile_computed", arg=t))
+    ev += [dict(t_ns=120_000, cta=0, kind="sum_begin", arg=0), dict(t_ns=160_000, cta=0, kind="sum_end", arg=0),
+           dict(t_ns=200_000, cta=0, kind="sum_begin", arg=1), dict(t_ns=240_000, cta=0, kind="sum_end", arg=1)]
+    s = fused_timeline_summary(ev)
+    assert s["tile_computed"]["count"] == 9 and s["chunk_sent"]["last_ns"] == 100_000
+    assert s["overlap_chunks"] == 0.6          # 40..100 us of the 100 us gather lie after the first tile
+    assert s["overlap_sums"] == 0.5            # slice 0 hidden, slice 1 exposed
+    path = tmp_path / "timeline.json"
+    fused_timeline_to_chrome(ev, str(path))
+    recs = json.load(open(path))["traceEvents"]
+    assert sum(r["ph"] == "X" for r in recs) == 2 and sum(r["ph"] == "i" for r in recs) == 14
