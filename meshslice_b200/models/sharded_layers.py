@@ -221,9 +221,15 @@ class ShardedAttention:
     communication (ShardedLayers.py:141-159).  The reference is non-causal; ``causal=True`` adds
     the decoder mask.  The score matrix is never written to HBM on the GPU path."""
 
-    def __init__(self, mesh: Mesh, n_heads: int, seqlen: int, causal: bool = False, allow_fallback: bool = False):
+    def __init__(self, mesh: Mesh, n_heads: int, seqlen: int, causal: bool = False, allow_fallback: bool = False,
+                 seq_shard: bool = False):
         """``allow_fallback``: shapes the attention kernel does not cover (head_dim != 128 or
-        seq % 128 != 0) run the eager formulation on the GPU instead of raising."""
+        seq % 128 != 0) run the eager formulation on the GPU instead of raising.
+        ``seq_shard``: sequences split over the mesh rows (ring attention).  The reference keeps whole
+        sequences per mesh row (ShardedLayers.py:152) and so does this layer; the flag exists so that callers
+        can ask and get a clear answer instead of wrong numerics."""
+        if seq_shard:
+            raise NotImplementedError("sequences are kept whole per mesh row; shard the batch over rows instead")
         if n_heads % mesh.C:
             raise ValueError("heads must divide over the mesh columns")
         self.mesh, self.seqlen, self.causal, self.allow_fallback = mesh, seqlen, causal, allow_fallback
