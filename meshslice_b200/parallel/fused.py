@@ -121,6 +121,10 @@ TRACE_KINDS = {1: "operands_ready", 2: "tile_computed", 3: "tile_pushed", 4: "ch
                6: "sum_end"}
 
 
+class FlagProtocolError(RuntimeError):
+    """A flag or arrival counter of a finished fused launch does not stand at its target."""
+
+
 class FusedGemm:
     """Builds and launches fused dataflows for one rank.
 
@@ -234,6 +238,46 @@ class FusedGemm:
     def _chunk_flag(self, rank: int, idx: int) -> int:
         return self.world.flag_ptr(rank, rt.CHUNK0 + idx)
 
+    # ------------------------------------------------------------------ flag protocol
+    def verify_flags(self) -> None:
+        """Host-side check of the flag protocol after the last launch has finished: every chunk or panel flag
+        that the tiles waited on stands exactly at its target (less: a sender was not counted; more: a flag was
+        not cleared or a chunk was signalled twice) and so does every per-slice arrival counter of the slot
+        sums.  Synchronises the device; meant for tests and debugging, not for the training loop."""
+        d = getattr(self, "_last", None)
+        if d is None or d.get("phase") not in ("all", "reduce", "gemm"):
+            return
+        ws = self.world.mine
+        torch.cuda.synchronize()
+        words = ws.heap.bytes_view(ws.flags, rt.FLAG_WORDS * 4).view(torch.int32).cpu().numpy().astype("int64") & 0xffffffff
+        bad = []
+
+        def expect(word, target, what):
+            if int(words[word]) != int(target):
+                bad.append(f"{what}: {int(words[word])} != {int(target)}")
+
+        kblocks = (d.get("K", 0) + 63) // 64
+        for op in ("a", "b"):
+            mode, base = d.get(f"{op}_flag_mode", 0), d.get(f"{op}_flag_base", 0)
+            if mode == 1:
+                idx, target = range(base, base + d.get("n_slices", 1)), d.get(f"{op}_flag_target", 0)
+            elif mode in (2, 4):
+                idx, target = range(base, base + d.get(f"{op}_flag_count", 0)), d.get(f"{op}_flag_target", 0)
+            elif mode == 3:
+                per = max(1, d.get(f"{op}_kpanel", 1))
+                idx, target = range(base, base + (kblocks + per - 1) // per), d.get("kp_target", 0)
+            else:
+                continue
+            if d.get("no_tiles", 0):
+                continue          # a launch without tiles waits for nothing
+            for i in idx:
+                expect(rt.CHUNK0 + i, target, f"flag {i} of operand {op.upper()}")
+        if d.get("red_n", 0):
+            for sl in range(d.get("n_slices", 1)):
+                expect(rt.COUNTER0 + sl, d.get("red_target", 0), f"arrival counter of slice {sl}")
+        if bad:
+            raise FlagProtocolError("; ".join(bad[:8]))
+
     # ------------------------------------------------------------------ timeline
     def enable_trace(self, events_per_cta: int = 512) -> None:
         """The following launches run the traced instantiation of the kernel: every CTA records when the
@@ -293,6 +337,7 @@ class FusedGemm:
             d.update(_barrier_fields(self.world, [], exit_barrier, self.grid, self.timeout_ns))
         if self._trace is not None:
             d.update(trace=self._trace.data_ptr(), trace_cap=self._trace_cap)
+        self._last = dict(d, phase=phase)
         self.C.gemm_run(d)
 
     # ------------------------------------------------------------------ OS

@@ -54,6 +54,8 @@ def test_os_gathers_both_operands(mesh, slices):
             op.os([xs[(r, cc)].data_ptr() for cc in range(C)], [wsd[(rr, c)].data_ptr() for rr in range(R)],
                   m, kl, kr, n, outs[(r, c)], n_slices=slices, phase=phase, reset=False)
             _native.check_status()
+            if phase != "comm":
+                op.verify_flags()
     for (r, c), out in outs.items():
         _close(out, ref[r * m:(r + 1) * m, c * n:(c + 1) * n], Kd)
 
@@ -81,6 +83,8 @@ def test_os_k_panel_schedules(mesh, order, sub):
             op.os_kpanel([xs[(r, cc)].data_ptr() for cc in range(C)], [wsd[(rr, c)].data_ptr() for rr in range(R)],
                          m, kl, kr, n, outs[(r, c)], order=order, sub=sub, phase=phase, reset=False)
             _native.check_status()
+            if phase != "comm":
+                op.verify_flags()
     for (r, c), out in outs.items():
         _close(out, ref[r * m:(r + 1) * m, c * n:(c + 1) * n], Kd)
 
@@ -105,6 +109,8 @@ def test_ls_gathers_weights_pushes_over_row(mesh, slices):
             op.ls(xs[(r, c)], [wsd[(rr, c)].data_ptr() for rr in range(R)], m, kl, nr, outs[(r, c)],
                   n_slices=slices, phase=phase, reset=False)
             _native.check_status()
+            if phase != "comm":
+                op.verify_flags()
     for (r, c), out in outs.items():
         _close(out, ref[r * m:(r + 1) * m, c * nc:(c + 1) * nc], Kd)
 
@@ -134,6 +140,8 @@ def test_timeline_of_a_traced_ls_launch_and_identical_results():
                 op.ls(xs[(r, c)], [wsd[(rr, c)].data_ptr() for rr in range(R)], m, kl, nr, outs[(r, c)],
                       n_slices=slices, phase=phase, reset=False)
                 _native.check_status()
+                if phase != "comm":
+                    op.verify_flags()
         results.append(outs)
         if traced:
             tiles_per_rank = ((m + 255) // 256) * ((N + 255) // 256)
@@ -175,6 +183,8 @@ def test_rs_gathers_inputs_pushes_over_column(mesh, slices, cyc):
             op.rs([xs[(r, cc)].data_ptr() for cc in range(C)], wsd[(r, c)], kr, ml, n, outs[(r, c)],
                   n_slices=slices, cyc=cyc, phase=phase, reset=False)
             _native.check_status()
+            if phase != "comm":
+                op.verify_flags()
     for (r, c), out in outs.items():
         _close(out, ref[r * mr:(r + 1) * mr, c * n:(c + 1) * n], Kd)
 
