@@ -40,7 +40,10 @@ B200_NVSWITCH = dict(
     latencies={"allgather": 3e-6, "reducescatter": 3e-6, "sendrecv": 3e-6},
     bws={"allgather": (700e9, 700e9), "reducescatter": (600e9, 600e9), "sendrecv": (700e9, 700e9)},
     base_overheads={"allgather": 6e-6, "reducescatter": 8e-6, "sendrecv": 5e-6},
-    fabric="switch", shared_port=True, flops_per_chip=1.38e15)
+    fabric="switch", shared_port=True, flops_per_chip=1.38e15,
+    # rates of the fused GEMM + collective kernel fitted to a 2-D GeMM sweep on 8 GPUs (bench/fit_fused_model.py)
+    fused=dict(launch_overhead=6.27e-5, gather_bw_alone=7.66e11, gather_bw_overlap=3.04e11, push_bw=5.43e11,
+               slot_sum_bw=7.23e11, tile_eff=0.872, matmul_peak=1.3806e15))
 
 latencies = TPUV4["latencies"]
 bws = TPUV4["bws"]
