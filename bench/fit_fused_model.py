@@ -4,7 +4,7 @@
     python bench/fit_fused_model.py sweep.log [more.json ...] [--fabric-json in.json] [--out out.json]
 
 Input: what `bench/BenchGemm2D.py` prints or writes with `--json` (one record per global shape, mesh and
-dataflow, with the fused kernel's time per slice count).  The six rate constants of
+dataflow, with the fused kernel's time per slice count).  The seven constants of
 `meshslice_b200.cost_model.FusedKernelConstants` are fitted by least squares on log(predicted / measured)
 over all (shape, mesh, dataflow, slices) points; the result is printed with the per-point ratios and, with
 `--out`, written as the `fused` section of a fabric JSON that `run_autotune.py --fabric-json` reads.
@@ -22,9 +22,10 @@ sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 from meshslice_b200 import cost_model as cm  # noqa: E402
 from meshslice_b200.autotuner import B200_NVSWITCH, FabricConstants  # noqa: E402
 
-NAMES = ["launch_overhead", "gather_bw_alone", "gather_bw_overlap", "push_bw", "slot_sum_bw", "tile_eff"]
-LOWER = [1e-5, 1e11, 5e10, 5e10, 2e11, 0.5]
-UPPER = [5e-4, 9e11, 9e11, 9e11, 7e12, 1.3]
+NAMES = ["launch_overhead", "gather_bw_alone", "gather_bw_overlap", "push_bw", "slot_sum_bw", "tile_eff",
+         "slice_overhead"]
+LOWER = [1e-5, 1e11, 5e10, 5e10, 2e11, 0.5, 1e-8]
+UPPER = [5e-4, 9e11, 9e11, 9e11, 7e12, 1.3, 1e-4]
 
 
 def read_rows(paths):
@@ -81,7 +82,7 @@ def main(argv=None):
         c = consts_of(x)
         return [math.log(predict(fabric, c, p) / p[-1]) for p in pts]
 
-    x0 = [math.log(getattr(cm.FusedKernelConstants(), n)) for n in NAMES]
+    x0 = [math.log(max(getattr(cm.FusedKernelConstants(), n), lo)) for n, lo in zip(NAMES, LOWER)]
     fit = least_squares(resid, x0, bounds=(np.log(LOWER), np.log(UPPER)))
     c = consts_of(fit.x)
     ratios = np.exp(np.array(resid(fit.x)))

@@ -41,9 +41,9 @@ B200_NVSWITCH = dict(
     bws={"allgather": (700e9, 700e9), "reducescatter": (600e9, 600e9), "sendrecv": (700e9, 700e9)},
     base_overheads={"allgather": 6e-6, "reducescatter": 8e-6, "sendrecv": 5e-6},
     fabric="switch", shared_port=True, flops_per_chip=1.38e15,
-    # rates of the fused GEMM + collective kernel fitted to a 2-D GeMM sweep on 8 GPUs (bench/fit_fused_model.py)
-    fused=dict(launch_overhead=6.27e-5, gather_bw_alone=7.66e11, gather_bw_overlap=3.04e11, push_bw=5.43e11,
-               slot_sum_bw=7.23e11, tile_eff=0.872, matmul_peak=1.3806e15))
+    # rates of the fused GEMM + collective kernel fitted to 2-D GeMM sweeps on 8 and 2 GPUs (bench/fit_fused_model.py)
+    fused=dict(launch_overhead=1.82e-05, gather_bw_alone=6.1e+11, gather_bw_overlap=3.08e+11, push_bw=5.88e+11,
+               slot_sum_bw=5.81e+11, tile_eff=0.951, slice_overhead=8.51e-06, matmul_peak=1.3806e15))
 
 latencies = TPUV4["latencies"]
 bws = TPUV4["bws"]
@@ -427,6 +427,9 @@ def main(argv=None):
                         "(a file, or the name of one shipped with the simulator)")
     p.add_argument("--netsim-topology", type=str, default="crossbar", help="crossbar or torus (one ring per mesh axis)")
     p.add_argument("--tuned-json", type=str, default="", help="write the decision here")
+    p.add_argument("--meshes", type=str, nargs="*", default=[],
+                   help="candidate mesh shapes RxC (default: every factorisation of nrows x ncols); one shape tunes "
+                        "dataflows and slice counts for that mesh")
     p.add_argument("--blocksize", type=int, default=64)
     p.add_argument("--measure-matmul", action="store_true", help="time the tcgen05 GEMM instead of the analytic model")
     a = p.parse_args(argv)
@@ -442,7 +445,9 @@ def main(argv=None):
         fabric = (FabricConstants.load(a.fabric_json) if a.fabric_json else
                   FabricConstants.from_dict(B200_NVSWITCH if a.fabric == "b200" else TPUV4))
     matmul = CostModel.MeasuredMatmul() if a.measure_matmul else None
-    shapes = candidate_shapes(n)
+    shapes = [tuple(int(v) for v in m.lower().split("x")) for m in a.meshes] or candidate_shapes(n)
+    if any(len(sh) != 2 or sh[0] * sh[1] != n for sh in shapes):
+        p.error(f"every --meshes entry must be RxC with R * C = {n}")
     print(shapes)
     tuner = Autotuner(graph, shapes, fabric=fabric, blocksize=a.blocksize, matmul=matmul,
                       klist=[1, 2, 4, 8] if a.fabric == "b200" and not a.fabric_json and not a.netsim_config else None)

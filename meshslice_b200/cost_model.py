@@ -379,6 +379,7 @@ class FusedKernelConstants:
     push_bw: float = 450e9               # bytes/s of partial tiles pushed from the epilogue
     slot_sum_bw: float = 2.2e12          # bytes/s of slot reads in the per-slice sums
     tile_eff: float = 0.93               # main-loop rate relative to the matmul estimator
+    slice_overhead: float = 0.0          # s per slice: flag waits, fences and counter updates at slice boundaries
     matmul_peak: float = 1.3806e15       # FLOP/s of the analytic estimator that tile_eff was fitted against
 
     def to_dict(self):
@@ -409,7 +410,7 @@ def Fused_OS(mesh, M, N, K, steps=4, precisions=(16, 16, 16)):
         return (0.0, tiles)
     first = (bx + bw) / steps / f.gather_bw_alone
     rest = (bx + bw) * (1.0 - 1.0 / steps) / f.gather_bw_overlap
-    return (f.launch_overhead + first, max(tiles, rest))
+    return (f.launch_overhead + first, max(tiles, rest) + steps * f.slice_overhead)
 
 
 def _fused_scatter(mesh, gather_bytes, push_bytes, slot_bytes, tiles, steps):
@@ -419,7 +420,7 @@ def _fused_scatter(mesh, gather_bytes, push_bytes, slot_bytes, tiles, steps):
     first = gather_bytes / steps / f.gather_bw_alone
     under = gather_bytes * (1.0 - 1.0 / steps) / f.gather_bw_overlap + push_bytes / f.push_bw
     tail = slot_bytes / steps / f.slot_sum_bw      # the last slice's slot sum has no tiles left to hide under
-    return (f.launch_overhead + first, max(tiles, under) + tail)
+    return (f.launch_overhead + first, max(tiles, under) + tail + steps * f.slice_overhead)
 
 
 def Fused_LS(mesh, M, N, K, steps=4, precisions=(16, 16, 16)):

@@ -163,7 +163,7 @@ def test_fused_constants_are_recovered_from_a_synthetic_sweep(tmp_path):
     fit = importlib.util.module_from_spec(spec)
     spec.loader.exec_module(fit)
     true = dict(launch_overhead=8e-5, gather_bw_alone=6e11, gather_bw_overlap=2.5e11, push_bw=4e11,
-                slot_sum_bw=1.5e12, tile_eff=0.9)
+                slot_sum_bw=1.5e12, tile_eff=0.9, slice_overhead=5e-6)
     rows = []
     for shape in ((2, 4), (4, 2), (1, 8), (8, 1)):
         mesh = _b200_mesh(shape, **true)
