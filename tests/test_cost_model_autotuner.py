@@ -185,3 +185,14 @@ def test_fused_constants_are_recovered_from_a_synthetic_sweep(tmp_path):
     fab.fused = None
     t_pipe = layer.emulate(fab.mesh((2, 4)), 4)
     assert t_fused > 0 and t_pipe > 0 and t_fused != t_pipe
+
+
+def test_cli_meshes_restricts_the_candidates(tmp_path, capsys):
+    out = tmp_path / "tuned.json"
+    tuner = AT.main(["--nrows", "2", "--ncols", "4", "--batchsize", "16", "--nheads", "96", "--meshes", "4x2",
+                     "--tuned-json", str(out)])
+    assert tuple(tuner.bestshape) == (4, 2)
+    d = json.load(open(out))
+    assert d["mesh"] == [4, 2] and len(d["layers"]) == 4 and all(l["ksplit"] >= 1 for l in d["layers"])
+    with pytest.raises(SystemExit):
+        AT.main(["--nrows", "2", "--ncols", "4", "--meshes", "3x3"])
