@@ -248,7 +248,8 @@ class FusedGemm:
         if d is None or d.get("phase") not in ("all", "reduce", "gemm"):
             return
         ws = self.world.mine
-        torch.cuda.synchronize()
+        if torch.cuda.is_available():
+            torch.cuda.synchronize()
         words = ws.heap.bytes_view(ws.flags, rt.FLAG_WORDS * 4).view(torch.int32).cpu().numpy().astype("int64") & 0xffffffff
         bad = []
 
@@ -296,7 +297,8 @@ class FusedGemm:
         ``cta``, ``kind`` (name) and ``arg`` (tile, chunk or slice index)."""
         if self._trace is None:
             return []
-        torch.cuda.synchronize()
+        if torch.cuda.is_available():
+            torch.cuda.synchronize()
         raw = self._trace.view(self.grid, self._trace_cap + 1, 4).cpu().numpy().astype("int64") & 0xffffffff
         self._trace.zero_()
         out = []

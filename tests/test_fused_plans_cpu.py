@@ -407,3 +407,64 @@ def test_tile_order_matches_the_gather_chunks_and_the_arrival_targets(mesh, slic
             for mb, nb_, s_ in sched:
                 counts[(mb * BMc // mr, s_)] = counts.get((mb * BMc // mr, s_), 0) + 8
             assert all(v * R == d["red_target"] for v in counts.values())
+
+
+def _fg_with_flags(words):
+    """A FusedGemm whose workspace flag block is a CPU tensor (what verify_flags reads after a launch)."""
+    import torch
+    flags = torch.zeros(rt.FLAG_WORDS, dtype=torch.int32)
+    for k, v in words.items():
+        flags[k] = v
+    heap = type("H", (), {"bytes_view": lambda self, off, n: flags.view(torch.uint8)[off:off + n]})()
+    ws = type("W", (), {"heap": heap, "flags": 0})()
+    fg = fz.FusedGemm.__new__(fz.FusedGemm)
+    fg.world = type("World", (), {"mine": ws})()
+    return fg
+
+
+def test_verify_flags_accepts_complete_flags_and_names_the_first_bad_one():
+    last = dict(phase="all", K=512, n_slices=3, a_flag_mode=1, a_flag_base=2, a_flag_target=592,
+                b_flag_mode=4, b_flag_base=0, b_flag_count=2, b_flag_target=1184, red_n=4, red_target=64)
+    good = {rt.CHUNK0 + 0: 1184, rt.CHUNK0 + 1: 1184, rt.CHUNK0 + 2: 592, rt.CHUNK0 + 3: 592, rt.CHUNK0 + 4: 592,
+            rt.COUNTER0 + 0: 64, rt.COUNTER0 + 1: 64, rt.COUNTER0 + 2: 64}
+    fg = _fg_with_flags(good)
+    fg._last = last
+    fg.verify_flags()
+    # a sender that was not counted, a flag signalled twice, a slice whose tiles did not all arrive
+    for word, value, text in ((rt.CHUNK0 + 3, 591, "flag 3 of operand A"), (rt.CHUNK0 + 1, 2368, "flag 1 of operand B"),
+                              (rt.COUNTER0 + 2, 60, "arrival counter of slice 2")):
+        fg = _fg_with_flags({**good, word: value})
+        fg._last = last
+        with pytest.raises(fz.FlagProtocolError, match=text):
+            fg.verify_flags()
+    # K panels: one flag per panel of the contraction dimension, all at the panel target
+    fg = _fg_with_flags({rt.CHUNK0 + 4 + i: 296 for i in range(4)})
+    fg._last = dict(phase="gemm", K=1024, a_flag_mode=3, a_flag_base=4, a_kpanel=4, kp_target=296)
+    fg.verify_flags()
+    fg._last["K"] = 1280          # a fifth panel whose flag is still zero
+    with pytest.raises(fz.FlagProtocolError, match="flag 8 of operand A"):
+        fg.verify_flags()
+    # a gather-only launch waits for nothing
+    fg._last = dict(phase="comm", a_flag_mode=1, a_flag_base=0, n_slices=2, a_flag_target=5)
+    fg.verify_flags()
+
+
+def test_read_trace_decodes_and_clears_the_per_cta_event_areas():
+    import torch
+    fg = fz.FusedGemm.__new__(fz.FusedGemm)
+    fg.grid, fg._trace_cap = 3, 4
+    buf = torch.zeros(3, 5, 4, dtype=torch.int64)
+    t0 = (7 << 32) + 0xfffffff0          # a timer value whose low word has the top bit set
+    buf[0, 0, 0] = 2
+    buf[0, 1] = torch.tensor([(t0 + 50) & 0xffffffff, (t0 + 50) >> 32, 2, 11])
+    buf[0, 2] = torch.tensor([(t0 + 90) & 0xffffffff, (t0 + 90) >> 32, 6, 1])
+    buf[2, 0, 0] = 9                     # more events than the area holds: only the stored ones come back
+    for i in range(4):
+        buf[2, 1 + i] = torch.tensor([(t0 + 10 * i) & 0xffffffff, (t0 + 10 * i) >> 32, 4, i])
+    # the device buffer holds the 32-bit words as int32: wrap the values above 2^31
+    fg._trace = torch.where(buf >= (1 << 31), buf - (1 << 32), buf).to(torch.int32).reshape(-1)
+    ev = fg.read_trace()
+    assert [e["t_ns"] for e in ev] == [0, 10, 20, 30, 50, 90]
+    assert ev[0] == dict(t_ns=0, cta=2, kind="chunk_sent", arg=0)
+    assert ev[4] == dict(t_ns=50, cta=0, kind="tile_computed", arg=11) and ev[5]["kind"] == "sum_end"
+    assert fg.read_trace() == []
