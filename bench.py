@@ -211,6 +211,12 @@ def main():
                "clocks": clocks, "gpu_launches": int(launches)}
         if e2e is not None:
             out["e2e"] = e2e
+        try:   # library / eager paths taken instead of the package's own kernels (0 unless a fallback was allowed)
+            from meshslice_b200.ops import functional as _F
+            out["fallbacks"] = int(getattr(getattr(trainer, "engine", None), "fallbacks", 0) or 0) + \
+                int(sum(_F.FALLBACKS.values()))
+        except Exception:
+            pass
         print(json.dumps(out), flush=True)
     if world > 1:
         dist.barrier()
