@@ -63,6 +63,26 @@ class TrainConfig:
     timeout_ns: int = 20_000_000_000
 
 
+def workspace_bytes(cfg, micro_batch: int, R: int, C: int):
+    """Staging (gathered A / B operands) and slot (pushed partial tiles) bytes that the fused
+    kernels of one micro-batch need, over the forward, dX and dW products of every linear layer
+    under its dataflow (m = tokens per mesh row and micro-batch).  Returns (stage_a, stage_b, slots)."""
+    m = micro_batch * cfg.seq
+    d, f, V = cfg.d_model, cfg.ffn, cfg.vocab_padded
+    lin = [(d, 3 * d, cfg.dataflows[0]), (d, d, cfg.dataflows[1]), (d, f, cfg.dataflows[2]),
+           (f, d, cfg.dataflows[3]), (d, V, "os")]
+    sa = sb = sl = 0
+    for i, o, df in lin:
+        if df == "os":      # OS(x, w), LS(dy, w), RS(x, dy)
+            a, b, s_ = m * i, i * o // C, max(m * i, i * o // C)
+        elif df == "ls":    # LS(x, w), OS(dy, w), RS(dy, x)
+            a, b, s_ = m * o, o * i // C, max(m * o, o * i // C)
+        else:               # RS(x^T, w), LS(w, dy), OS(x^T, dy): the token dimension is gathered whole
+            a, b, s_ = m * i, max(i * o // C, m * R * o // C), max(m * i, m * R * o // C)
+        sa, sb, sl = max(sa, a), max(sb, b), max(sl, s_)
+    return 2 * sa, 2 * sb, 2 * sl
+
+
 class Trainer:
     def __init__(self, cfg: GPTConfig, tcfg: TrainConfig, mesh_shape: Optional[Tuple[int, int]] = None,
                  device: Optional[torch.device] = None):
@@ -117,24 +137,7 @@ class Trainer:
 
     # ------------------------------------------------------------------ sizing
     def _workspace_bytes(self):
-        """Staging (gathered A / B operands) and slot (pushed partial tiles) bytes that the fused
-        kernels of one micro-batch need, over the forward, dX and dW products of every linear layer
-        under its dataflow (m = tokens per mesh row and micro-batch)."""
-        cfg, R, C = self.cfg, self.R, self.C
-        m = self.tcfg.micro_batch * cfg.seq
-        d, f, V = cfg.d_model, cfg.ffn, cfg.vocab_padded
-        lin = [(d, 3 * d, cfg.dataflows[0]), (d, d, cfg.dataflows[1]), (d, f, cfg.dataflows[2]),
-               (f, d, cfg.dataflows[3]), (d, V, "os")]
-        sa = sb = sl = 0
-        for i, o, df in lin:
-            if df == "os":      # OS(x, w), LS(dy, w), RS(x, dy)
-                a, b, s_ = m * i, i * o // C, max(m * i, i * o // C)
-            elif df == "ls":    # LS(x, w), OS(dy, w), RS(dy, x)
-                a, b, s_ = m * o, o * i // C, max(m * o, o * i // C)
-            else:               # RS(x^T, w), LS(w, dy), OS(x^T, dy): the token dimension is gathered whole
-                a, b, s_ = m * i, max(i * o // C, m * R * o // C), max(m * i, m * R * o // C)
-            sa, sb, sl = max(sa, a), max(sb, b), max(sl, s_)
-        return 2 * sa, 2 * sb, 2 * sl
+        return workspace_bytes(self.cfg, self.tcfg.micro_batch, self.R, self.C)
 
     # ------------------------------------------------------------------ data
     def rows_of_global_batch(self, ids_global: torch.Tensor) -> torch.Tensor:

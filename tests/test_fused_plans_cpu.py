@@ -468,3 +468,55 @@ def test_read_trace_decodes_and_clears_the_per_cta_event_areas():
     assert ev[0] == dict(t_ns=0, cta=2, kind="chunk_sent", arg=0)
     assert ev[4] == dict(t_ns=50, cta=0, kind="tile_computed", arg=11) and ev[5]["kind"] == "sum_end"
     assert fg.read_trace() == []
+
+
+@pytest.mark.parametrize("mesh", [(1, 2), (2, 1), (2, 2), (2, 4), (4, 2), (1, 8), (8, 1)])
+@pytest.mark.parametrize("model", ["gpt3-6.7b", "gpt3-175b-width"])
+def test_trainer_workspace_fits_every_product_of_the_model(mesh, model):
+    """The staging and slot buffers that the trainer allocates (`workspace_bytes`) hold the gathered operands and
+    the pushed partial tiles of every forward, data-gradient and weight-gradient product of the block's four
+    linears and of the LM head, for the 6.7B-shaped model and the 175B-width stack on every mesh shape."""
+    from meshslice_b200.models.gpt import GPTConfig
+    from meshslice_b200.trainer import workspace_bytes
+    R, C = mesh
+    if model == "gpt3-6.7b":
+        cfg, gb = GPTConfig(), 32
+    else:
+        cfg, gb = GPTConfig(n_layers=4, d_model=12288, n_heads=96, ffn=49152), 16
+    mb = max(1, min(gb // R, 16 if model == "gpt3-6.7b" else 8))
+    sa, sb, sl = workspace_bytes(cfg, mb, R, C)
+    m = mb * cfg.seq
+    d, f, V = cfg.d_model, cfg.ffn, cfg.vocab_padded
+    lin = [(d, 3 * d, cfg.dataflows[0]), (d, d, cfg.dataflows[1]), (d, f, cfg.dataflows[2]), (f, d, cfg.dataflows[3]),
+           (d, V, "os")]
+    assert set(cfg.dataflows) <= {"os", "ls"}
+
+    def sized_world(n, me):
+        w = FakeWorld(n, me)
+        for ws in w.wss:
+            ws.stage_a_bytes, ws.stage_b_bytes, ws.slot_bytes = sa, sb, sl
+        return w
+
+    for i, o, df in lin:
+        for r in range(R):
+            for c in range(C):
+                mc = fz.MeshCoord(R, C, r, c)
+                fg = fz.FusedGemm.__new__(fz.FusedGemm)
+                fg.mesh, fg.world, fg.grid, fg.timeout_ns, fg.use_barriers = mc, sized_world(R * C, mc.rank), 148, 1, False
+                fg._cache, fg.signals = {}, 296
+                fg._jobs = lambda key, builder: (builder(), type("T", (), {"data_ptr": lambda s: 1})(),
+                                                 type("T", (), {"data_ptr": lambda s: 2})(), 1)[1:]
+                launched = []
+                fg._launch = lambda d_, exit_barrier, phase="all", reset=True: launched.append(d_)
+                fg._common = lambda out_, acc, stream: {}
+                if df == "os":
+                    fg.os([10 ** 9] * C, [2 * 10 ** 9] * R, m, i // C, i // R, o // C, None, n_slices=4)
+                    fg.ls(FakeT(5, o // C), [3 * 10 ** 9] * R, m, o // C, i // R, None, n_slices=4)
+                    fg.rs([7 * 10 ** 9] * C, FakeT(6, o // C), m, i // C, o // C, None, n_slices=4)
+                else:
+                    fg.ls(FakeT(5, i // C), [3 * 10 ** 9] * R, m, i // C, o // R, None, n_slices=4)
+                    fg.os([10 ** 9] * C, [2 * 10 ** 9] * R, m, o // C, o // R, i // C, None, n_slices=4)
+                    fg.rs([7 * 10 ** 9] * C, FakeT(6, i // C), m, o // C, i // C, None, n_slices=4)
+                assert len(launched) == 3
+    # what the 175B-width stack asks of one GPU stays far below its memory
+    assert sa + sb + sl < 24 << 30
